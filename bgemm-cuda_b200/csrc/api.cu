@@ -1,0 +1,200 @@
+// extern "C" surface of libbgemm_b200.so: argument validation, workspace carving, launch order.
+// Declared and documented in include/bgemm_b200.h.
+#include <atomic>
+
+#include "internal.h"
+
+namespace bgemm {
+
+static std::atomic<uint64_t> g_launches{0};
+void count_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
+
+static bool aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) % a) == 0; }
+static bool valid_dtype(int d) { return d >= BGEMM_DT_F16 && d <= BGEMM_DT_I8; }
+static size_t dt_size(int d) { return d == BGEMM_DT_F32 ? 4 : (d == BGEMM_DT_I8 ? 1 : 2); }
+
+constexpr long long kMaxDim = 1LL << 24;      // keeps every int32 accumulator and index computation exact
+constexpr int kMaxSplitK = 64;
+constexpr size_t kCounterBytesMin = 4096;
+
+static size_t counter_bytes(long long tiles) { return align_up((size_t)tiles * 4 > kCounterBytesMin ? (size_t)tiles * 4 : kCounterBytesMin, 256); }
+
+static int resolve_split_k(long long M, long long N, long long K, long long batch, int split_k) {
+    const long long kblocks = (K + 255) / 256;
+    if (split_k >= 1) return (int)(split_k > kblocks ? kblocks : split_k);
+    // auto: aim at ~2 CTAs per SM worth of tiles, keep at least 2 K blocks per partition
+    const int NT = gemm_tile_n(N);
+    const long long tiles = ((M + 127) / 128) * ((N + NT - 1) / NT) * batch;
+    const long long target = 148LL * (NT <= 128 ? 2 : 1);
+    long long s = target / (tiles > 0 ? tiles : 1);
+    if (s < 1) s = 1;
+    if (s > kblocks / 2) s = kblocks / 2;
+    if (s < 1) s = 1;
+    if (s > kMaxSplitK) s = kMaxSplitK;
+    return (int)s;
+}
+
+}  // namespace bgemm
+
+using namespace bgemm;
+
+extern "C" {
+
+size_t bgemm_plane_bytes(int64_t M, int64_t K) {
+    if (M < 1 || K < 1) return 0;
+    return (size_t)((M + 127) / 128) * (size_t)((K + 255) / 256) * 4096;
+}
+int64_t bgemm_act_ld(int64_t K) { return K < 1 ? 0 : (K + 255) / 256 * 256; }
+
+int bgemm_version(void) { return 100; }
+uint64_t bgemm_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
+
+const char* bgemm_status_string(int status) {
+    switch (status) {
+        case BGEMM_OK: return "ok";
+        case BGEMM_ERR_NULL: return "a required pointer is NULL";
+        case BGEMM_ERR_SHAPE: return "M, N, K, batch or a leading dimension is out of range";
+        case BGEMM_ERR_ALIGN: return "a pointer or leading dimension breaks an alignment rule";
+        case BGEMM_ERR_ENUM: return "unknown dtype / op / out_kind / layout value";
+        case BGEMM_ERR_WORKSPACE: return "workspace missing or too small";
+        case BGEMM_ERR_UNSUPPORTED: return "request not supported by this build";
+        case BGEMM_ERR_DRIVER: return "CUDA driver entry point for tensor maps unavailable or rejected the map";
+        case BGEMM_ERR_TOO_LARGE: return "size beyond the fixed capacity of this entry point";
+        default: return status > 0 ? cudaGetErrorString((cudaError_t)status) : "unknown status";
+    }
+}
+
+int bgemm_pack_rowmajor_msb(void* stream, const void* src, int src_dtype, int64_t rows, int64_t K, int64_t ld, uint32_t* dst) {
+    if (!src || !dst) return BGEMM_ERR_NULL;
+    if (!valid_dtype(src_dtype)) return BGEMM_ERR_ENUM;
+    if (rows < 1 || K < 32 || K % 32 != 0 || ld < K || rows > kMaxDim || K > kMaxDim) return BGEMM_ERR_SHAPE;
+    return launch_pack_rowmajor_msb((cudaStream_t)stream, src, src_dtype, rows, K, ld, dst);
+}
+
+int bgemm_retile_rowmajor_msb(void* stream, const uint32_t* src_words, int64_t M, int64_t K, int invert, void* plane) {
+    if (!src_words || !plane) return BGEMM_ERR_NULL;
+    if (M < 1 || K < 32 || K % 32 != 0 || M > kMaxDim || K > kMaxDim) return BGEMM_ERR_SHAPE;
+    if (!aligned(plane, 16)) return BGEMM_ERR_ALIGN;
+    return launch_retile((cudaStream_t)stream, src_words, M, K, invert ? 1 : 0, plane);
+}
+
+int bgemm_pack_weights(void* stream, const void* src, int src_dtype, int64_t M, int64_t K, int64_t ld, int wbit_mode, void* plane,
+                       int32_t* rowpop, void* alpha, int64_t batch, int64_t src_batch_stride) {
+    if (!src || !plane) return BGEMM_ERR_NULL;
+    if (!valid_dtype(src_dtype) || wbit_mode < 0 || wbit_mode > 1) return BGEMM_ERR_ENUM;
+    if (M < 1 || K < 1 || ld < K || batch < 1 || batch > 65535 || M > kMaxDim || K > kMaxDim) return BGEMM_ERR_SHAPE;
+    if (batch > 1 && src_batch_stride < 0) return BGEMM_ERR_SHAPE;
+    if (!aligned(plane, 16) || !aligned(src, dt_size(src_dtype))) return BGEMM_ERR_ALIGN;
+    return launch_pack_weights((cudaStream_t)stream, src, src_dtype, M, K, ld, wbit_mode, plane, rowpop, alpha, batch, src_batch_stride);
+}
+
+int bgemm_prepare_acts(void* stream, const void* src, int src_dtype, int64_t N, int64_t K, int64_t ld, int act_mode, int transpose,
+                       int8_t* dst, int32_t* colsum, int64_t batch, int64_t src_batch_stride) {
+    if (!src || !dst || !colsum) return BGEMM_ERR_NULL;
+    if (!valid_dtype(src_dtype) || act_mode < 0 || act_mode > 2) return BGEMM_ERR_ENUM;
+    if (N < 1 || K < 1 || batch < 1 || batch > 65535 || N > kMaxDim || K > kMaxDim) return BGEMM_ERR_SHAPE;
+    if (ld < (transpose ? N : K)) return BGEMM_ERR_SHAPE;
+    if (!aligned(dst, 16) || !aligned(src, dt_size(src_dtype))) return BGEMM_ERR_ALIGN;
+    return launch_prepare_acts((cudaStream_t)stream, src, src_dtype, N, K, ld, act_mode, transpose ? 1 : 0, dst, colsum, batch,
+                               src_batch_stride);
+}
+
+int bgemm_gemm_auto_split_k(int64_t M, int64_t N, int64_t K, int64_t batch) {
+    if (M < 1 || N < 1 || K < 1 || batch < 1) return 1;
+    return resolve_split_k(M, N, K, batch, 0);
+}
+
+size_t bgemm_gemm_workspace_bytes(int64_t M, int64_t N, int64_t K, int split_k, int64_t batch) {
+    if (M < 1 || N < 1 || K < 1 || batch < 1) return 0;
+    const int s = resolve_split_k(M, N, K, batch, split_k);
+    if (s <= 1) return 0;
+    const int NT = gemm_tile_n(N);
+    const long long tiles = ((M + 127) / 128) * ((N + NT - 1) / NT) * batch;
+    return counter_bytes(tiles) + (size_t)tiles * (size_t)s * (size_t)NT * 128 * 4;
+}
+
+int bgemm_gemm(void* stream, const void* plane, int64_t M, int64_t K, const int8_t* acts, const int32_t* colsum, int64_t N, int op,
+               void* out, int out_kind, int out_layout, const void* alpha, int split_k, void* workspace, size_t workspace_bytes,
+               int64_t batch) {
+    if (!plane || !acts || !colsum || !out) return BGEMM_ERR_NULL;
+    if (op < BGEMM_OP_AND || op > BGEMM_OP_BWTA || out_kind < BGEMM_OUT_I32 || out_kind > BGEMM_OUT_F16_SCALED ||
+        out_layout < BGEMM_LAYOUT_NM || out_layout > BGEMM_LAYOUT_MN)
+        return BGEMM_ERR_ENUM;
+    if (out_kind == BGEMM_OUT_F16_SCALED && !alpha) return BGEMM_ERR_NULL;
+    if (M < 1 || N < 1 || K < 1 || batch < 1 || batch > 65535 || M > kMaxDim || N > kMaxDim || K > kMaxDim || split_k < 0 ||
+        split_k > kMaxSplitK)
+        return BGEMM_ERR_SHAPE;
+    if (!aligned(plane, 16) || !aligned(acts, 16) || !aligned(colsum, 4) || !aligned(out, out_kind == BGEMM_OUT_I32 ? 4 : 2))
+        return BGEMM_ERR_ALIGN;
+    const int s = resolve_split_k(M, N, K, batch, split_k);
+    const long long mtiles = (M + 127) / 128;
+    if (mtiles * s > 65535) return BGEMM_ERR_SHAPE;
+
+    GemmParams p{};
+    p.plane = static_cast<const uint8_t*>(plane);
+    p.colsum = colsum;
+    p.out = out;
+    p.alpha = static_cast<const __half*>(alpha);
+    p.status = nullptr;
+    p.M = (int)M; p.N = (int)N; p.K = (int)K;
+    p.kblocks = (int)((K + 255) / 256);
+    p.mtiles = (int)mtiles;
+    p.split_k = s;
+    p.epi = (op == BGEMM_OP_XOR || op == BGEMM_OP_BWTA) ? 1 : 0;
+    p.out_kind = out_kind;
+    p.out_layout = out_layout;
+    p.plane_batch_bytes = (long long)bgemm_plane_bytes(M, K);
+    if (s > 1) {
+        const size_t need = bgemm_gemm_workspace_bytes(M, N, K, s, batch);
+        if (!workspace || workspace_bytes < need) return BGEMM_ERR_WORKSPACE;
+        if (!aligned(workspace, 256)) return BGEMM_ERR_ALIGN;
+        const int NT = gemm_tile_n(N);
+        const long long tiles = mtiles * ((N + NT - 1) / NT) * batch;
+        p.ws_counters = static_cast<unsigned int*>(workspace);
+        p.ws_partial = reinterpret_cast<int32_t*>(static_cast<char*>(workspace) + counter_bytes(tiles));
+    }
+    return launch_gemm((cudaStream_t)stream, p, acts, bgemm_act_ld(K), batch);
+}
+
+// Workspace of the unpacked-operand entry point: [gemm workspace][plane][acts int8][colsum].
+static void linear_ws_layout(int64_t M, int64_t N, int64_t K, int s, size_t* off_plane, size_t* off_acts, size_t* off_colsum,
+                             size_t* total) {
+    size_t o = align_up(bgemm_gemm_workspace_bytes(M, N, K, s, 1), 256);
+    *off_plane = o; o += align_up(bgemm_plane_bytes(M, K), 256);
+    *off_acts = o;  o += align_up((size_t)N * (size_t)bgemm_act_ld(K), 256);
+    *off_colsum = o; o += align_up((size_t)N * 4, 256);
+    *total = o;
+}
+
+size_t bgemm_linear_workspace_bytes(int64_t M, int64_t N, int64_t K, int split_k) {
+    if (M < 1 || N < 1 || K < 1) return 0;
+    const int s = resolve_split_k(M, N, K, 1, split_k);
+    size_t a, b, c, total;
+    linear_ws_layout(M, N, K, s, &a, &b, &c, &total);
+    return total;
+}
+
+int bgemm_linear_forward(void* stream, const void* weight_f16, const void* acts_f16, void* out, int64_t M, int64_t N, int64_t K, int op,
+                         int out_kind, int out_layout, const void* alpha, int split_k, void* workspace, size_t workspace_bytes) {
+    if (!weight_f16 || !acts_f16 || !out || !workspace) return weight_f16 && acts_f16 && out ? BGEMM_ERR_WORKSPACE : BGEMM_ERR_NULL;
+    if (op < BGEMM_OP_AND || op > BGEMM_OP_BWTA) return BGEMM_ERR_ENUM;
+    if (M < 1 || N < 1 || K < 1 || M > kMaxDim || N > kMaxDim || K > kMaxDim || split_k < 0 || split_k > kMaxSplitK) return BGEMM_ERR_SHAPE;
+    if (!aligned(workspace, 256)) return BGEMM_ERR_ALIGN;
+    const int s = resolve_split_k(M, N, K, 1, split_k);
+    size_t off_plane, off_acts, off_colsum, total;
+    linear_ws_layout(M, N, K, s, &off_plane, &off_acts, &off_colsum, &total);
+    if (workspace_bytes < total) return BGEMM_ERR_WORKSPACE;
+    char* ws = static_cast<char*>(workspace);
+    const int wbit = op == BGEMM_OP_ATTN ? BGEMM_WBIT_NONNEGATIVE : BGEMM_WBIT_NEGATIVE;
+    const int amode = op == BGEMM_OP_AND ? BGEMM_ACT_NEG01 : (op == BGEMM_OP_BWTA ? BGEMM_ACT_TERNARY : BGEMM_ACT_SIGN);
+    int rc = bgemm_pack_weights(stream, weight_f16, BGEMM_DT_F16, M, K, K, wbit, ws + off_plane, nullptr, nullptr, 1, 0);
+    if (rc) return rc;
+    rc = bgemm_prepare_acts(stream, acts_f16, BGEMM_DT_F16, N, K, K, amode, 0, reinterpret_cast<int8_t*>(ws + off_acts),
+                            reinterpret_cast<int32_t*>(ws + off_colsum), 1, 0);
+    if (rc) return rc;
+    return bgemm_gemm(stream, ws + off_plane, M, K, reinterpret_cast<const int8_t*>(ws + off_acts),
+                      reinterpret_cast<const int32_t*>(ws + off_colsum), N, op, out, out_kind, out_layout, alpha, s, ws,
+                      bgemm_gemm_workspace_bytes(M, N, K, s, 1), 1);
+}
+
+}  // extern "C"

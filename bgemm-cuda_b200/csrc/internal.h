@@ -1,0 +1,44 @@
+// Declarations shared by the translation units of libbgemm_b200.so (not part of the public ABI).
+#pragma once
+#include <cstddef>
+#include <cstdint>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include "../../include/bgemm_b200.h"
+
+namespace bgemm {
+
+struct GemmParams {
+    const uint8_t* plane;         // tiled weight-slot bits
+    const int32_t* colsum;        // [batch][N]
+    void* out;
+    const __half* alpha;          // [batch][M] or null
+    int32_t* ws_partial;          // split-K slabs [tile][split][NT][128], null when split_k == 1
+    unsigned int* ws_counters;    // split-K arrival counters [tile]
+    int* status;                  // device status word (0 = fine), may be null
+    int M, N, K;
+    int kblocks;                  // ceil(K / 256)
+    int mtiles, ntiles;
+    int split_k;
+    int epi;                      // 0: result = D, 1: result = colsum[n] - 2 D
+    int out_kind, out_layout;
+    long long plane_batch_bytes;
+};
+
+void count_launch();
+int* device_status_word();        // per-device status word, lazily created (cudaGetSymbolAddress)
+
+int gemm_tile_n(long long N);
+int launch_gemm(cudaStream_t stream, GemmParams p, const int8_t* acts, long long act_ld, long long batch);
+
+int launch_pack_weights(cudaStream_t stream, const void* src, int dtype, long long M, long long K, long long ld, int wbit_mode,
+                        void* plane, int32_t* rowpop, void* alpha, long long batch, long long src_batch_stride);
+int launch_prepare_acts(cudaStream_t stream, const void* src, int dtype, long long N, long long K, long long ld, int act_mode,
+                        int transpose, int8_t* dst, int32_t* colsum, long long batch, long long src_batch_stride);
+int launch_pack_rowmajor_msb(cudaStream_t stream, const void* src, int dtype, long long rows, long long K, long long ld, uint32_t* dst);
+int launch_retile(cudaStream_t stream, const uint32_t* src_words, long long M, long long K, int invert, void* plane);
+
+inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+}  // namespace bgemm

@@ -1,0 +1,366 @@
+// Operand preparation kernels: weight-slot matrices -> tiled 1-bit planes, activation-slot matrices ->
+// zero-padded int8 rows + column sums, plus the reference-compatible row-major MSB-first prepack.
+//
+// Replaces the reference's CPU prepack bin_matrix_prepacking_to_uint32
+// (lowbit_kernel/csrc/utils/weight_prepacking.h:181-230), its never-implemented GPU twin
+// binary_weight_prepacking_cuda (lowbit_kernel/csrc/fp6_linear.cu:519-542) and the on-the-fly sign
+// extraction inside the GEMM (SIGN_32_HALF_TO_UINT32, include/ptx_mma.cuh:341-399).
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include <cmath>
+#include <cstring>
+
+#include "internal.h"
+
+namespace bgemm {
+
+// ---- element decoding ----------------------------------------------------------------------------------
+template <typename T> struct Elem;
+template <> struct Elem<__half> {
+    static __host__ __device__ __forceinline__ int neg(const __half& v) { return (reinterpret_cast<const uint16_t&>(v) >> 15) & 1; }
+    static __host__ __device__ __forceinline__ int zero(const __half& v) { return (reinterpret_cast<const uint16_t&>(v) & 0x7fffu) == 0; }
+    static __device__ __forceinline__ float mag(const __half& v) { return fabsf(__half2float(v)); }
+};
+template <> struct Elem<__nv_bfloat16> {
+    static __host__ __device__ __forceinline__ int neg(const __nv_bfloat16& v) { return (reinterpret_cast<const uint16_t&>(v) >> 15) & 1; }
+    static __host__ __device__ __forceinline__ int zero(const __nv_bfloat16& v) { return (reinterpret_cast<const uint16_t&>(v) & 0x7fffu) == 0; }
+    static __device__ __forceinline__ float mag(const __nv_bfloat16& v) { return fabsf(__bfloat162float(v)); }
+};
+template <> struct Elem<float> {
+    static __host__ __device__ __forceinline__ int neg(const float& v) { return (reinterpret_cast<const uint32_t&>(v) >> 31) & 1; }
+    static __host__ __device__ __forceinline__ int zero(const float& v) { return (reinterpret_cast<const uint32_t&>(v) & 0x7fffffffu) == 0; }
+    static __device__ __forceinline__ float mag(const float& v) { return fabsf(v); }
+};
+template <> struct Elem<int8_t> {
+    static __host__ __device__ __forceinline__ int neg(const int8_t& v) { return v < 0; }
+    static __host__ __device__ __forceinline__ int zero(const int8_t& v) { return v == 0; }
+    static __device__ __forceinline__ float mag(const int8_t& v) { return fabsf((float)v); }
+};
+
+// Byte offset of word c (0..7) of row r (0..127) inside a 4096-byte tile: two 2 KB halves, each holding
+// four words of every row, so that a warp's 16-byte reads of consecutive rows are contiguous.
+__host__ __device__ __forceinline__ int tile_word_offset(int r, int c) { return (c >> 2) * 2048 + r * 16 + (c & 3) * 4; }
+
+// ---- weights -> tiled plane (+ rowpop, alpha) ---------------------------------------------------------------
+// One warp per row of the padded matrix. Lane L reads elements k = 256 kb + 8 L + e (e = 0..7): slice
+// j = L / 4, words c = 2 (L % 4) + e / 4, byte b = e % 4 -> bit 8 b + j. Words are completed by OR-ing
+// across the eight lanes that share L % 4.
+template <typename T>
+__global__ void __launch_bounds__(256) pack_weights_kernel(const T* __restrict__ src, long long M, long long K, long long ld, int invert,
+                                                           uint8_t* __restrict__ plane, int32_t* __restrict__ rowpop,
+                                                           __half* __restrict__ alpha, long long src_batch_stride,
+                                                           long long plane_batch_bytes) {
+    const int lane = threadIdx.x & 31;
+    const long long row = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    const long long batch = blockIdx.y;
+    const long long mtiles = (M + 127) / 128, kblocks = (K + 255) / 256;
+    if (row >= mtiles * 128) return;
+    src += batch * src_batch_stride;
+    plane += batch * plane_batch_bytes;
+    const bool live = row < M;
+    const T* rp = src + row * ld;
+    const int j = lane >> 2;
+    int pop = 0;
+    float mag = 0.f;
+    uint8_t* tile_row = plane + (row / 128) * kblocks * 4096;
+    const int r = (int)(row % 128);
+    const bool vec_ok = (sizeof(T) == 2) && ((reinterpret_cast<uintptr_t>(rp) & 15) == 0);
+    for (long long kb = 0; kb < kblocks; kb++) {
+        uint32_t w0 = 0, w1 = 0;
+        const long long k0 = kb * 256 + lane * 8;
+        if (live && k0 < K) {
+            T v[8];
+            if (vec_ok && k0 + 8 <= K) {
+                *reinterpret_cast<uint4*>(v) = *reinterpret_cast<const uint4*>(rp + k0);
+            } else {
+#pragma unroll
+                for (int e = 0; e < 8; e++) v[e] = (k0 + e < K) ? rp[k0 + e] : T();
+            }
+#pragma unroll
+            for (int e = 0; e < 8; e++) {
+                if (k0 + e < K) {
+                    const uint32_t bit = (uint32_t)(Elem<T>::neg(v[e]) ^ invert);
+                    if (e < 4) w0 |= bit << (8 * e + j); else w1 |= bit << (8 * (e - 4) + j);
+                    if (alpha) mag += Elem<T>::mag(v[e]);
+                }
+            }
+        }
+#pragma unroll
+        for (int off = 4; off < 32; off <<= 1) {
+            w0 |= __shfl_xor_sync(0xffffffffu, w0, off);
+            w1 |= __shfl_xor_sync(0xffffffffu, w1, off);
+        }
+        if (lane < 4) {
+            pop += __popc(w0) + __popc(w1);
+            *reinterpret_cast<uint2*>(tile_row + kb * 4096 + tile_word_offset(r, 2 * lane)) = make_uint2(w0, w1);
+        }
+    }
+    if (live && (rowpop || alpha)) {
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) {
+            pop += __shfl_xor_sync(0xffffffffu, pop, off);
+            mag += __shfl_xor_sync(0xffffffffu, mag, off);
+        }
+        if (lane == 0) {
+            if (rowpop) rowpop[batch * M + row] = pop;
+            if (alpha) alpha[batch * M + row] = __float2half_rn(mag / (float)K);
+        }
+    }
+}
+
+// ---- activations -> int8 rows + colsum ----------------------------------------------------------------------
+template <typename T>
+__device__ __forceinline__ int8_t act_value(const T& v, int mode) {
+    const int neg = Elem<T>::neg(v);
+    if (mode == BGEMM_ACT_SIGN) return (int8_t)(1 - 2 * neg);
+    if (mode == BGEMM_ACT_TERNARY) return Elem<T>::zero(v) ? (int8_t)0 : (int8_t)(1 - 2 * neg);
+    return (int8_t)neg;
+}
+
+// One warp per row; lane handles 8 consecutive elements per step and writes them as one 8-byte store.
+template <typename T>
+__global__ void __launch_bounds__(256) prepare_acts_kernel(const T* __restrict__ src, long long N, long long K, long long ld, int mode,
+                                                           int8_t* __restrict__ dst, int32_t* __restrict__ colsum,
+                                                           long long src_batch_stride) {
+    const int lane = threadIdx.x & 31;
+    const long long row = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    const long long batch = blockIdx.y;
+    if (row >= N) return;
+    const long long kld = (K + 255) / 256 * 256;
+    const T* rp = src + batch * src_batch_stride + row * ld;
+    int8_t* dp = dst + (batch * N + row) * kld;
+    const bool vec_ok = (sizeof(T) == 2) && ((reinterpret_cast<uintptr_t>(rp) & 15) == 0);
+    int sum = 0;
+    for (long long k0 = lane * 8; k0 < kld; k0 += 256) {
+        int8_t o[8];
+        if (k0 < K) {
+            T v[8];
+            if (vec_ok && k0 + 8 <= K) {
+                *reinterpret_cast<uint4*>(v) = *reinterpret_cast<const uint4*>(rp + k0);
+            } else {
+#pragma unroll
+                for (int e = 0; e < 8; e++) v[e] = (k0 + e < K) ? rp[k0 + e] : T();
+            }
+#pragma unroll
+            for (int e = 0; e < 8; e++) {
+                o[e] = (k0 + e < K) ? act_value<T>(v[e], mode) : (int8_t)0;
+                sum += o[e];
+            }
+        } else {
+#pragma unroll
+            for (int e = 0; e < 8; e++) o[e] = 0;
+        }
+        *reinterpret_cast<uint2*>(dp + k0) = *reinterpret_cast<const uint2*>(o);
+    }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, off);
+    if (lane == 0) colsum[batch * N + row] = sum;
+}
+
+// Transposing variant: source is [K, N]; a block owns 32 output rows (n) and walks K in 32-wide tiles.
+template <typename T>
+__global__ void __launch_bounds__(256) prepare_acts_t_kernel(const T* __restrict__ src, long long N, long long K, long long ld, int mode,
+                                                             int8_t* __restrict__ dst, int32_t* __restrict__ colsum,
+                                                             long long src_batch_stride) {
+    __shared__ int8_t tile[32][33];
+    __shared__ int part[8][32];
+    const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+    const long long n0 = (long long)blockIdx.x * 32;
+    const long long batch = blockIdx.y;
+    const long long kld = (K + 255) / 256 * 256;
+    const T* sp = src + batch * src_batch_stride;
+    int8_t* dp = dst + batch * N * kld;
+    int sum = 0;
+    for (long long k0 = 0; k0 < kld; k0 += 32) {
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            const long long k = k0 + ty + 8 * i, n = n0 + tx;
+            int8_t v = 0;
+            if (k < K && n < N) v = act_value<T>(sp[k * ld + n], mode);
+            sum += v;
+            tile[ty + 8 * i][tx] = v;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            const long long n = n0 + ty + 8 * i;
+            if (n < N) dp[n * kld + k0 + tx] = tile[tx][ty + 8 * i];
+        }
+        __syncthreads();
+    }
+    part[ty][tx] = sum;
+    __syncthreads();
+    if (ty == 0 && n0 + tx < N) {
+        int s = 0;
+#pragma unroll
+        for (int i = 0; i < 8; i++) s += part[i][tx];
+        colsum[batch * N + n0 + tx] = s;
+    }
+}
+
+// ---- reference-compatible row-major prepack: element k -> bit 31 - k % 32 of word k / 32 --------------------
+template <typename T>
+__global__ void __launch_bounds__(256) pack_rowmajor_msb_kernel(const T* __restrict__ src, long long rows, long long K, long long ld,
+                                                                uint32_t* __restrict__ dst) {
+    const int lane = threadIdx.x & 31;
+    const long long words = K / 32;
+    const long long warp_id = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    const long long nwarps = (long long)gridDim.x * (blockDim.x >> 5);
+    for (long long w = warp_id; w < rows * words; w += nwarps) {
+        const long long r = w / words, c = w % words;
+        const int neg = Elem<T>::neg(src[r * ld + c * 32 + lane]);
+        const uint32_t ballot = __ballot_sync(0xffffffffu, neg);
+        if (lane == 0) dst[w] = __brev(ballot);
+    }
+}
+
+// Row-major MSB-first words -> tiled plane. One thread per (row, 256-column block).
+__global__ void __launch_bounds__(256) retile_kernel(const uint32_t* __restrict__ src, long long M, long long K, int invert,
+                                                     uint8_t* __restrict__ plane) {
+    const long long mtiles = (M + 127) / 128, kblocks = (K + 255) / 256, words = K / 32;
+    const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= mtiles * 128 * kblocks) return;
+    const long long row = idx / kblocks, kb = idx % kblocks;
+    uint32_t out[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    if (row < M) {
+        for (int j = 0; j < 8; j++) {
+            const long long wi = kb * 8 + j;
+            if (wi >= words) break;
+            uint32_t s = src[row * words + wi];
+            if (invert) s = ~s;
+            for (int t = 0; t < 32; t++) {   // element k = 32 j + t sits at bit 31 - t; t = 4 c + b
+                const uint32_t bit = (s >> (31 - t)) & 1u;
+                out[t >> 2] |= bit << (8 * (t & 3) + j);
+            }
+        }
+    }
+    uint8_t* tile = plane + ((row / 128) * kblocks + kb) * 4096;
+    const int r = (int)(row % 128);
+    *reinterpret_cast<uint4*>(tile + tile_word_offset(r, 0)) = make_uint4(out[0], out[1], out[2], out[3]);
+    *reinterpret_cast<uint4*>(tile + tile_word_offset(r, 4)) = make_uint4(out[4], out[5], out[6], out[7]);
+}
+
+// ---- launchers --------------------------------------------------------------------------------------------
+#define BGEMM_DISPATCH_DTYPE(dtype, ...)                                            \
+    switch (dtype) {                                                                \
+        case BGEMM_DT_F16: { using T = __half; __VA_ARGS__; break; }                \
+        case BGEMM_DT_BF16: { using T = __nv_bfloat16; __VA_ARGS__; break; }        \
+        case BGEMM_DT_F32: { using T = float; __VA_ARGS__; break; }                 \
+        case BGEMM_DT_I8: { using T = int8_t; __VA_ARGS__; break; }                 \
+        default: return BGEMM_ERR_ENUM;                                             \
+    }
+
+int launch_pack_weights(cudaStream_t stream, const void* src, int dtype, long long M, long long K, long long ld, int wbit_mode,
+                        void* plane, int32_t* rowpop, void* alpha, long long batch, long long src_batch_stride) {
+    const long long rows = (M + 127) / 128 * 128;
+    dim3 grid((unsigned)((rows + 7) / 8), (unsigned)batch);
+    const long long pbytes = (long long)bgemm_plane_bytes(M, K);
+    BGEMM_DISPATCH_DTYPE(dtype, (pack_weights_kernel<T><<<grid, 256, 0, stream>>>(
+                                    static_cast<const T*>(src), M, K, ld, wbit_mode == BGEMM_WBIT_NONNEGATIVE ? 1 : 0,
+                                    static_cast<uint8_t*>(plane), rowpop, static_cast<__half*>(alpha), src_batch_stride, pbytes)));
+    count_launch();
+    return (int)cudaGetLastError();
+}
+
+int launch_prepare_acts(cudaStream_t stream, const void* src, int dtype, long long N, long long K, long long ld, int act_mode,
+                        int transpose, int8_t* dst, int32_t* colsum, long long batch, long long src_batch_stride) {
+    if (transpose) {
+        dim3 grid((unsigned)((N + 31) / 32), (unsigned)batch);
+        BGEMM_DISPATCH_DTYPE(dtype, (prepare_acts_t_kernel<T><<<grid, 256, 0, stream>>>(static_cast<const T*>(src), N, K, ld, act_mode,
+                                                                                       dst, colsum, src_batch_stride)));
+    } else {
+        dim3 grid((unsigned)((N + 7) / 8), (unsigned)batch);
+        BGEMM_DISPATCH_DTYPE(dtype, (prepare_acts_kernel<T><<<grid, 256, 0, stream>>>(static_cast<const T*>(src), N, K, ld, act_mode, dst,
+                                                                                     colsum, src_batch_stride)));
+    }
+    count_launch();
+    return (int)cudaGetLastError();
+}
+
+int launch_pack_rowmajor_msb(cudaStream_t stream, const void* src, int dtype, long long rows, long long K, long long ld, uint32_t* dst) {
+    const long long total = rows * (K / 32);
+    long long blocks = (total + 7) / 8;
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    if (blocks < 1) blocks = 1;
+    BGEMM_DISPATCH_DTYPE(dtype, (pack_rowmajor_msb_kernel<T><<<(unsigned)blocks, 256, 0, stream>>>(static_cast<const T*>(src), rows, K, ld, dst)));
+    count_launch();
+    return (int)cudaGetLastError();
+}
+
+int launch_retile(cudaStream_t stream, const uint32_t* src_words, long long M, long long K, int invert, void* plane) {
+    const long long total = (M + 127) / 128 * 128 * ((K + 255) / 256);
+    retile_kernel<<<(unsigned)((total + 255) / 256), 256, 0, stream>>>(src_words, M, K, invert, static_cast<uint8_t*>(plane));
+    count_launch();
+    return (int)cudaGetLastError();
+}
+
+// ---- CPU twins (host pointers) ------------------------------------------------------------------------------
+template <typename T> static int host_neg(const T* p) { return Elem<T>::neg(*p); }
+static float host_mag(const void* p, int dtype) {
+    switch (dtype) {
+        case BGEMM_DT_F16: return fabsf(__half2float(*static_cast<const __half*>(p)));
+        case BGEMM_DT_BF16: return fabsf(__bfloat162float(*static_cast<const __nv_bfloat16*>(p)));
+        case BGEMM_DT_F32: return fabsf(*static_cast<const float*>(p));
+        default: return fabsf((float)*static_cast<const int8_t*>(p));
+    }
+}
+static int host_neg_any(const void* p, int dtype) {
+    switch (dtype) {
+        case BGEMM_DT_F16: return host_neg(static_cast<const __half*>(p));
+        case BGEMM_DT_BF16: return host_neg(static_cast<const __nv_bfloat16*>(p));
+        case BGEMM_DT_F32: return host_neg(static_cast<const float*>(p));
+        default: return host_neg(static_cast<const int8_t*>(p));
+    }
+}
+static size_t dtype_size(int dtype) { return dtype == BGEMM_DT_F32 ? 4 : (dtype == BGEMM_DT_I8 ? 1 : 2); }
+
+}  // namespace bgemm
+
+using namespace bgemm;
+
+extern "C" int bgemm_pack_weights_host(const void* src, int dtype, int64_t M, int64_t K, int64_t ld, int wbit_mode, void* plane,
+                                       int32_t* rowpop, void* alpha) {
+    if (!src || !plane) return BGEMM_ERR_NULL;
+    if (M < 1 || K < 1 || ld < K) return BGEMM_ERR_SHAPE;
+    if (dtype < 0 || dtype > 3 || wbit_mode < 0 || wbit_mode > 1) return BGEMM_ERR_ENUM;
+    const int64_t kblocks = (K + 255) / 256;
+    std::memset(plane, 0, bgemm_plane_bytes(M, K));
+    const size_t es = dtype_size(dtype);
+    const char* s = static_cast<const char*>(src);
+    for (int64_t m = 0; m < M; m++) {
+        int pop = 0;
+        double mag = 0.0;
+        uint8_t* tile_row = static_cast<uint8_t*>(plane) + (m / 128) * kblocks * 4096;
+        const int r = (int)(m % 128);
+        for (int64_t k = 0; k < K; k++) {
+            const void* e = s + (size_t)(m * ld + k) * es;
+            const int bit = host_neg_any(e, dtype) ^ (wbit_mode == BGEMM_WBIT_NONNEGATIVE ? 1 : 0);
+            if (alpha) mag += host_mag(e, dtype);
+            if (!bit) continue;
+            pop++;
+            const int64_t kb = k / 256;
+            const int kk = (int)(k % 256), j = kk / 32, c = (kk % 32) / 4, b = kk % 4;
+            uint32_t* w = reinterpret_cast<uint32_t*>(tile_row + kb * 4096 + tile_word_offset(r, c));
+            *w |= 1u << (8 * b + j);
+        }
+        if (rowpop) rowpop[m] = pop;
+        if (alpha) static_cast<__half*>(alpha)[m] = __float2half_rn((float)(mag / (double)K));
+    }
+    return BGEMM_OK;
+}
+
+extern "C" int bgemm_pack_rowmajor_msb_host(const void* src, int dtype, int64_t rows, int64_t K, int64_t ld, uint32_t* dst) {
+    if (!src || !dst) return BGEMM_ERR_NULL;
+    if (rows < 1 || K < 32 || K % 32 != 0 || ld < K) return BGEMM_ERR_SHAPE;
+    if (dtype < 0 || dtype > 3) return BGEMM_ERR_ENUM;
+    const size_t es = dtype_size(dtype);
+    const char* s = static_cast<const char*>(src);
+    for (int64_t r = 0; r < rows; r++)
+        for (int64_t w = 0; w < K / 32; w++) {
+            uint32_t v = 0;
+            for (int t = 0; t < 32; t++) v |= (uint32_t)host_neg_any(s + (size_t)(r * ld + w * 32 + t) * es, dtype) << (31 - t);
+            dst[r * (K / 32) + w] = v;
+        }
+    return BGEMM_OK;
+}

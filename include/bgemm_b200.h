@@ -1,0 +1,170 @@
+/*
+ * bgemm_b200.h -- C ABI of libbgemm_b200.so: binary / ternary GEMM for NVIDIA B200 (sm_100a).
+ *
+ * The library replaces the 1-bit hot path of yifu-ding/BGEMM-CUDA (reference paths below are relative
+ * to that project):
+ *   - the C++ launcher  bin_pack_linear_kernel()        lowbit_kernel/csrc/fp6_linear.cu:275-337
+ *   - the device kernel PACK_BGEMM_Kernel               lowbit_kernel/csrc/include/kernel_matmul.cuh:370-547
+ *   - the split-K pass  SplitK_Reduction                lowbit_kernel/csrc/include/kernel_reduction.cuh:29-48
+ *   - the binary prepack bin_matrix_prepacking_to_uint32 lowbit_kernel/csrc/utils/weight_prepacking.h:181-230
+ *     and its torch wrappers (one of them an empty stub) lowbit_kernel/csrc/fp6_linear.cu:463-542
+ * and adds what the reference only has as torch code: the binary-weight x ternary-activation (BWTA)
+ * product (tests/python/bgemm_linear.py:246-275), a per-output-channel fp16 scale epilogue
+ * (the reference multiplies in Python afterwards, bgemm_linear.py:378,482,512), arbitrary M/N/K,
+ * and a batched {0,1} x {-1,+1} attention product (bgemm_linear.py:45-62 loops heads in Python).
+ *
+ * Conventions
+ *   - Every pointer is a DEVICE pointer unless the name ends in _host. The library never allocates,
+ *     frees or synchronises; the caller owns all buffers and passes a workspace where one is needed.
+ *   - `stream` is a cudaStream_t passed as void* (NULL = the legacy default stream).
+ *   - Every entry point returns an int: 0 = success, < 0 = BGEMM_ERR_* (bad argument; nothing was
+ *     launched), > 0 = a cudaError_t from the CUDA runtime.
+ *   - Binary value of an element: -1 if its sign bit is set, else +1 (so +0.0 -> +1, -0.0 -> -1), as in
+ *     the reference device code (ptx_mma.cuh:341-399). Ternary value: -1, 0, +1 = torch.sign().
+ *   - Result matrices are int32-exact internally; `out_kind` selects how they are stored.
+ */
+#ifndef BGEMM_B200_H_
+#define BGEMM_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- status codes ------------------------------------------------------------------------------ */
+#define BGEMM_OK                 0
+#define BGEMM_ERR_NULL          -1   /* a required pointer is NULL                                   */
+#define BGEMM_ERR_SHAPE         -2   /* M, N, K, batch or a leading dimension is out of range        */
+#define BGEMM_ERR_ALIGN         -3   /* a pointer or leading dimension breaks an alignment rule      */
+#define BGEMM_ERR_ENUM          -4   /* unknown dtype / op / out_kind / layout value                 */
+#define BGEMM_ERR_WORKSPACE     -5   /* workspace missing or smaller than bgemm_*_workspace_bytes()  */
+#define BGEMM_ERR_UNSUPPORTED   -6   /* valid request that this build cannot serve                   */
+#define BGEMM_ERR_DRIVER        -7   /* the CUDA driver entry point for tensor maps is unavailable   */
+#define BGEMM_ERR_TOO_LARGE     -8   /* size beyond the fixed capacity of an entry point             */
+
+/* ---- element types of unpacked sources --------------------------------------------------------- */
+#define BGEMM_DT_F16   0
+#define BGEMM_DT_BF16  1
+#define BGEMM_DT_F32   2
+#define BGEMM_DT_I8    3
+
+/* ---- the operation; values 0..2 are the reference's INSTR argument (include/configs.h:70-72) ---- */
+#define BGEMM_OP_AND   0   /* C[n,m] = #k where w and x are both negative  (ptx_mma.cuh:180-210)       */
+#define BGEMM_OP_XOR   1   /* C[n,m] = sum_k sgn(w) sgn(x), both in {-1,+1}  (ptx_mma.cuh:212-250)     */
+#define BGEMM_OP_ATTN  2   /* C[n,m] = sum_k [w >= 0] sgn(x): w-slot is a {0,1} mask (ptx_mma.cuh:252-337) */
+#define BGEMM_OP_BWTA  3   /* C[n,m] = sum_k sgn(w) t(x), t = torch.sign in {-1,0,+1} (bgemm_linear.py:241,270-272) */
+
+/* ---- how a weight-slot row is turned into a bit (bgemm_pack_weights mode) ----------------------- */
+#define BGEMM_WBIT_NEGATIVE     0   /* bit = sign bit            (ops AND, XOR, BWTA)                   */
+#define BGEMM_WBIT_NONNEGATIVE  1   /* bit = !sign bit           (op ATTN: 1 where the mask is "1")     */
+
+/* ---- how an activation-slot element is turned into an int8 (bgemm_prepare_acts mode) ------------ */
+#define BGEMM_ACT_SIGN      0   /* -1 if sign bit else +1          (ops XOR, ATTN)                     */
+#define BGEMM_ACT_TERNARY   1   /* -1 / 0 / +1 = torch.sign        (op BWTA)                           */
+#define BGEMM_ACT_NEG01     2   /* 1 if sign bit else 0            (op AND)                            */
+
+/* ---- how the int32 result is stored ------------------------------------------------------------- */
+#define BGEMM_OUT_I32         0   /* int32 accumulators, untouched                                     */
+#define BGEMM_OUT_F16         1   /* fp16 = round-to-nearest-even(acc)   (kernel_matmul.cuh:540)       */
+#define BGEMM_OUT_F16_SCALED  2   /* fp16 = rne(float(acc) * float(alpha[m])), alpha = per-row scale   */
+
+/* ---- result matrix orientation ------------------------------------------------------------------ */
+#define BGEMM_LAYOUT_NM  0   /* C is [N, M], M contiguous: the reference's linear output (kernel_matmul.cuh:534-546) */
+#define BGEMM_LAYOUT_MN  1   /* C is [M, N], N contiguous: what bgemm_attn_matmul returns after its .T (bgemm_linear.py:60) */
+
+/* ---- packed-plane geometry ------------------------------------------------------------------------
+ * A weight-slot matrix [M, K] is stored as ONE bit per element in tiles of 128 rows x 256 columns.
+ * Tile (mt, kb) covers rows [128 mt, 128 mt + 128) and columns [256 kb, 256 kb + 256); tiles are
+ * stored kb-fastest, each tile is 4096 contiguous bytes. A row owns 8 little-endian uint32 words:
+ * element k = 256 kb + 32 j + 4 c + b (j in 0..7, c in 0..7, b in 0..3) is bit (8 b + j) of word c,
+ * and word c of row r sits at byte (c / 4) * 2048 + r * 16 + (c % 4) * 4 of the tile (two 2 KB halves,
+ * so 32 consecutive rows read 16 bytes each as one contiguous 512-byte access). Slice j of a tile is
+ * thus a 128 x 32 operand whose 4-element groups are selected by one mask 0x01010101 << j.
+ * Rows >= M and columns >= K hold 0 bits.
+ *
+ * bgemm_plane_bytes(M, K)  = ceil(M/128) * ceil(K/256) * 4096
+ * bgemm_act_ld(K)          = ceil(K/256) * 256        (bytes per prepared activation row)
+ */
+size_t  bgemm_plane_bytes(int64_t M, int64_t K);
+int64_t bgemm_act_ld(int64_t K);
+
+/* Reference-compatible row-major prepack: uint32 [rows, K/32], element k of a row is bit 31-(k%32) of
+ * word k/32 -- bit for bit what bin_matrix_prepacking_to_uint32 (weight_prepacking.h:203-230) writes.
+ * Requires K % 32 == 0. `src` is rows x K with leading dimension `ld` elements. Runs on the GPU
+ * (the reference's binary_weight_prepacking_cuda, fp6_linear.cu:519-542, never launched a kernel).   */
+int bgemm_pack_rowmajor_msb(void* stream, const void* src, int src_dtype, int64_t rows, int64_t K,
+                            int64_t ld, uint32_t* dst);
+/* The same on the CPU with HOST pointers (binary_matrix_prepacking_cpu, fp6_linear.cu:463-485).       */
+int bgemm_pack_rowmajor_msb_host(const void* src_host, int src_dtype, int64_t rows, int64_t K,
+                                 int64_t ld, uint32_t* dst_host);
+
+/* Convert a reference-format row-major plane (above) into the tiled plane the GEMM consumes.          */
+int bgemm_retile_rowmajor_msb(void* stream, const uint32_t* src_words, int64_t M, int64_t K,
+                              int invert, void* plane);
+
+/* Weight prepack: unpacked [M, K] (leading dimension ld elements) -> tiled bit plane.
+ *   wbit_mode  BGEMM_WBIT_*
+ *   plane      bgemm_plane_bytes(M, K) bytes, 16-byte aligned; fully written (padding included)
+ *   rowpop     optional int32 [M]: number of 1 bits in each row
+ *   alpha      optional fp16 [M]: mean(|w[m, :]|), the per-channel scale of a sign-binarised layer
+ * `batch` independent matrices are packed in one call: matrix i starts at src + i*src_batch_stride
+ * elements and writes plane + i*bgemm_plane_bytes(M,K) (rowpop/alpha + i*M).                          */
+int bgemm_pack_weights(void* stream, const void* src, int src_dtype, int64_t M, int64_t K, int64_t ld,
+                       int wbit_mode, void* plane, int32_t* rowpop, void* alpha,
+                       int64_t batch, int64_t src_batch_stride);
+/* CPU twin with HOST pointers (same bytes out).                                                        */
+int bgemm_pack_weights_host(const void* src_host, int src_dtype, int64_t M, int64_t K, int64_t ld,
+                            int wbit_mode, void* plane_host, int32_t* rowpop_host, void* alpha_host);
+
+/* Activation prepare: unpacked [N, K] (leading dimension ld) -> int8 [N, bgemm_act_ld(K)] (zero padded)
+ * plus colsum int32 [N] = sum_k of the int8 row. act_mode BGEMM_ACT_*. Batched like the weights:
+ * matrix i reads src + i*src_batch_stride and writes dst + i*N*bgemm_act_ld(K), colsum + i*N.
+ * If `transpose` is non-zero the source matrix is [K, N] (ld = its row pitch) and is transposed on the
+ * fly: this is value.transpose(-1,-2).contiguous() of bgemm_attn_matmul (bgemm_linear.py:60).          */
+int bgemm_prepare_acts(void* stream, const void* src, int src_dtype, int64_t N, int64_t K, int64_t ld,
+                       int act_mode, int transpose, int8_t* dst, int32_t* colsum,
+                       int64_t batch, int64_t src_batch_stride);
+
+/* The GEMM on prepared operands.
+ *   plane     tiled weight-slot bits of an [M, K] matrix (bgemm_pack_weights)
+ *   acts      int8 [N, bgemm_act_ld(K)] and colsum int32 [N] (bgemm_prepare_acts with the mode of `op`)
+ *   out       BGEMM_LAYOUT_NM: [N, M]; BGEMM_LAYOUT_MN: [M, N]; element type per out_kind
+ *   alpha     fp16 [M], required for BGEMM_OUT_F16_SCALED, else may be NULL
+ *   split_k   >= 1 forces that many K partitions, 0 lets the library choose
+ *   workspace needed when the chosen split_k > 1: bgemm_gemm_workspace_bytes() bytes, 256-byte aligned.
+ *             Zero it once after allocating it; the library restores the part that must be zero
+ *             (arrival counters at its start) before each call returns.
+ *   batch     number of independent problems (A x V heads); problem i uses plane + i*plane_bytes,
+ *             acts + i*N*act_ld, colsum + i*N, out + i*M*N elements, alpha + i*M.
+ * Replaces bin_pack_linear_kernel + PACK_BGEMM_Kernel + SplitK_Reduction (see file header).           */
+int bgemm_gemm(void* stream, const void* plane, int64_t M, int64_t K,
+               const int8_t* acts, const int32_t* colsum, int64_t N,
+               int op, void* out, int out_kind, int out_layout, const void* alpha,
+               int split_k, void* workspace, size_t workspace_bytes, int64_t batch);
+size_t bgemm_gemm_workspace_bytes(int64_t M, int64_t N, int64_t K, int split_k, int64_t batch);
+/* The split_k the library would pick for split_k = 0.                                                 */
+int bgemm_gemm_auto_split_k(int64_t M, int64_t N, int64_t K, int64_t batch);
+
+/* Literal drop-in for bin_pack_linear_kernel(stream, Weight, B, C, M, N, K, workspace, Split_K, INSTR)
+ * (fp6_linear.cu:275-337): unpacked fp16 weights [M, K] and activations [N, K] in, fp16 [N, M] out
+ * (BGEMM_OUT_F16). Unlike the reference M, N, K are unrestricted, split_k may be 0 (auto) and the
+ * workspace (bgemm_linear_workspace_bytes) also holds the packed operands. Same zero-once rule.
+ * out_kind / out_layout / alpha as in bgemm_gemm so callers can fuse the scale.                       */
+int bgemm_linear_forward(void* stream, const void* weight_f16, const void* acts_f16, void* out,
+                         int64_t M, int64_t N, int64_t K, int op, int out_kind, int out_layout,
+                         const void* alpha, int split_k, void* workspace, size_t workspace_bytes);
+size_t bgemm_linear_workspace_bytes(int64_t M, int64_t N, int64_t K, int split_k);
+
+/* Text for a status returned by any entry point (static storage).                                     */
+const char* bgemm_status_string(int status);
+/* Library version: major*10000 + minor*100 + patch.                                                   */
+int bgemm_version(void);
+/* Number of kernels this library has launched in this process (for launch accounting in benchmarks). */
+uint64_t bgemm_launch_count(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* BGEMM_B200_H_ */

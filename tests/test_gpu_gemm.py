@@ -1,0 +1,238 @@
+"""GPU parity tests: every result of libbgemm_b200.so (called through its C ABI) against the CPU oracle.
+
+Integer results are compared bit for bit; fp16-scaled results within 1e-3 relative (they are in fact
+produced by the same fp32-multiply + round-to-nearest-even and are also checked for exact equality).
+"""
+import numpy as np
+import pytest
+import torch
+
+import oracle as O
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def B():
+    import bgemm_b200
+
+    return bgemm_b200
+
+
+def _rand_w(M, K, g, kind="pm1"):
+    if kind == "pm1":
+        return O.rand_pm1((M, K), g)
+    return torch.randn(M, K, generator=g).to(torch.float16)
+
+
+def _acts_for(op, N, K, g):
+    if op == O.OP_BWTA:
+        return O.rand_ternary((N, K), g)
+    x = torch.randn(N, K, generator=g).to(torch.float16)
+    x[0, 0] = 0.0          # +0 -> +1
+    if K > 1:
+        x[0, 1] = -0.0     # -0 -> -1 (sign bit)
+    return x
+
+
+def _run(B, w, x, op, split_k=0, out_kind=O.OUT_I32, layout=0, alpha=None):
+    wd, xd = w.cuda(), x.cuda()
+    plane, _, _ = B.pack_weights(wd, B.WBIT_OF_OP[op])
+    acts, colsum = B.prepare_acts(xd, B.ACT_MODE_OF_OP[op])
+    return B.gemm(plane, w.shape[0], w.shape[1], acts, colsum, op, out_kind, layout,
+                  None if alpha is None else alpha.cuda(), split_k).cpu()
+
+
+@pytest.mark.parametrize("M,K", [(128, 256), (200, 300), (10, 4096), (257, 1000), (1024, 1024)])
+@pytest.mark.parametrize("mode", [0, 1])
+def test_pack_weights_matches_layout_definition(B, M, K, mode):
+    g = O._gen(M * 7 + K)
+    w = torch.randn(M, K, generator=g).to(torch.float16)
+    w[0, 0] = 0.0
+    w[M - 1, K - 1] = -0.0
+    plane, rowpop, alpha = B.pack_weights(w.cuda(), mode, want_rowpop=True, want_alpha=True)
+    ref_plane, ref_pop = O.np_pack_weights(w, mode)
+    assert plane.numel() == O.plane_bytes(M, K)
+    assert np.array_equal(plane.cpu().numpy(), ref_plane)
+    assert np.array_equal(rowpop.cpu().numpy(), ref_pop)
+    ref_alpha = O.c_rowmeanabs_f16(w).astype(np.float32)
+    got = alpha.cpu().float().numpy()
+    assert np.all(np.abs(got - ref_alpha) <= 1e-3 * np.abs(ref_alpha) + 1e-7)
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16, torch.float32, torch.int8])
+def test_pack_weights_dtypes_and_host_twin(B, dtype):
+    import ctypes
+
+    g = O._gen(5)
+    M, K = 130, 520
+    base = torch.randint(-3, 4, (M, K), generator=g)
+    w = base.to(dtype)
+    plane, rowpop, _ = B.pack_weights(w.cuda(), 0, want_rowpop=True)
+    ref_plane, ref_pop = O.np_pack_weights(base.float() - 0.0, 0)   # zero -> +0 -> bit 0, like int8 0
+    assert np.array_equal(plane.cpu().numpy(), ref_plane)
+    assert np.array_equal(rowpop.cpu().numpy(), ref_pop)
+    # CPU twin writes the same bytes
+    host_plane = np.zeros(O.plane_bytes(M, K), dtype=np.uint8)
+    host_pop = np.zeros(M, dtype=np.int32)
+    wc = w.contiguous()
+    rc = B.lib.bgemm_pack_weights_host(wc.data_ptr(), B.dtype_code(wc), M, K, K, 0, host_plane.ctypes.data, host_pop.ctypes.data, None)
+    assert rc == 0
+    assert np.array_equal(host_plane, ref_plane) and np.array_equal(host_pop, ref_pop)
+
+
+@pytest.mark.parametrize("mode", [0, 1, 2])
+@pytest.mark.parametrize("N,K", [(1, 256), (5, 300), (64, 4096), (33, 1000)])
+def test_prepare_acts(B, mode, N, K):
+    g = O._gen(N + K + mode)
+    x = O.rand_ternary((N, K), g) if mode == 1 else torch.randn(N, K, generator=g).to(torch.float16)
+    x[0, 0] = -0.0
+    acts, colsum = B.prepare_acts(x.cuda(), mode)
+    ref_a, ref_c = O.np_prepare_acts(x, mode)
+    assert np.array_equal(acts.cpu().numpy(), ref_a)
+    assert np.array_equal(colsum.cpu().numpy(), ref_c)
+    # transposed source gives the same result
+    acts_t, colsum_t = B.prepare_acts(x.t().contiguous().cuda(), mode, transpose=True)
+    assert np.array_equal(acts_t.cpu().numpy(), ref_a)
+    assert np.array_equal(colsum_t.cpu().numpy(), ref_c)
+
+
+def test_rowmajor_msb_prepack_matches_reference_format(B):
+    g = O._gen(11)
+    M, K = 96, 512
+    w = torch.randn(M, K, generator=g).to(torch.float16)
+    w[3, 5] = -0.0
+    dst = torch.empty((M, K // 32), dtype=torch.int32, device="cuda")
+    B.check(B.lib.bgemm_pack_rowmajor_msb(None, w.cuda().data_ptr(), B.DT_F16, M, K, K, dst.data_ptr()), "pack_rowmajor")
+    torch.cuda.synchronize()
+    got = dst.cpu().numpy().view(np.uint32)
+    assert np.array_equal(got, O.c_pack_rowmajor_msb(w))
+    if O.reflib() is not None:
+        assert np.array_equal(got, O.ref_pack_rowmajor_msb(w))
+    # retiling the reference format gives the same plane as packing directly
+    plane = torch.empty(O.plane_bytes(M, K), dtype=torch.uint8, device="cuda")
+    B.check(B.lib.bgemm_retile_rowmajor_msb(None, dst.data_ptr(), M, K, 0, plane.data_ptr()), "retile")
+    direct, _, _ = B.pack_weights(w.cuda(), 0)
+    assert torch.equal(plane, direct)
+
+
+OPS = [O.OP_AND, O.OP_XOR, O.OP_ATTN, O.OP_BWTA]
+
+
+@pytest.mark.parametrize("op", OPS)
+@pytest.mark.parametrize("N", [1, 7, 16, 17, 32, 33, 64, 100, 128, 200, 256, 300, 520])
+def test_gemm_all_tile_widths(B, op, N):
+    g = O._gen(100 + N + op)
+    M, K = 256, 512
+    w = _rand_w(M, K, g, "randn")
+    x = _acts_for(op, N, K, g)
+    got = _run(B, w, x, op, split_k=1)
+    assert torch.equal(got, O.ref_acc(w, x, op))
+
+
+@pytest.mark.parametrize("M,K", [(128, 256), (130, 384), (10, 4096), (257, 1000), (640, 129), (1, 1), (300, 8192)])
+@pytest.mark.parametrize("N", [3, 24, 64, 130])
+@pytest.mark.parametrize("split_k", [1, 0, 3])
+def test_gemm_ragged_shapes_and_split_k(B, M, K, N, split_k):
+    g = O._gen(M + K + N)
+    for op in (O.OP_XOR, O.OP_BWTA):
+        w = _rand_w(M, K, g, "randn")
+        x = _acts_for(op, N, K, g)
+        got = _run(B, w, x, op, split_k=split_k)
+        assert torch.equal(got, O.ref_acc(w, x, op)), (op, M, K, N, split_k)
+
+
+def test_gemm_known_answers(B):
+    M, N, K = 128, 16, 512
+    ones = torch.ones(M, K, dtype=torch.float16)
+    xs = torch.ones(N, K, dtype=torch.float16)
+    assert torch.all(_run(B, ones, xs, O.OP_XOR) == K)
+    assert torch.all(_run(B, -ones, xs, O.OP_XOR) == -K)
+    assert torch.all(_run(B, -ones, -xs, O.OP_AND) == K)
+    assert torch.all(_run(B, ones, -xs, O.OP_AND) == 0)
+    assert torch.all(_run(B, ones, -xs, O.OP_ATTN) == -K)        # mask all ones, values all -1
+    assert torch.all(_run(B, -ones, xs, O.OP_ATTN) == 0)         # mask all zeros
+    assert torch.all(_run(B, ones, torch.zeros(N, K, dtype=torch.float16), O.OP_BWTA) == 0)
+    alt = torch.ones(M, K, dtype=torch.float16)
+    alt[:, 1::2] = -1
+    assert torch.all(_run(B, alt, xs, O.OP_XOR) == 0)
+    # single element set: only column k0 of x is non-zero -> result is sign(w[:, k0])
+    e = torch.zeros(N, K, dtype=torch.float16)
+    e[:, 77] = 1
+    g = O._gen(3)
+    w = O.rand_pm1((M, K), g)
+    got = _run(B, w, e, O.OP_BWTA)
+    assert torch.equal(got, w[:, 77].to(torch.int32).unsqueeze(0).expand(N, M))
+
+
+@pytest.mark.parametrize("layout", [0, 1])
+@pytest.mark.parametrize("split_k", [1, 4])
+def test_output_kinds(B, layout, split_k):
+    cfg = O.config2(M=384, K=2048, N=40)
+    w, x, alpha = cfg["w"], cfg["x"], cfg["alpha"]
+    acc = O.ref_acc(w, x, O.OP_BWTA)
+    want = {O.OUT_I32: acc, O.OUT_F16: O.ref_out(acc, O.OUT_F16), O.OUT_F16_SCALED: O.ref_out(acc, O.OUT_F16_SCALED, alpha)}
+    for kind in (O.OUT_I32, O.OUT_F16, O.OUT_F16_SCALED):
+        got = _run(B, w, x, O.OP_BWTA, split_k=split_k, out_kind=kind, layout=layout, alpha=alpha)
+        ref = want[kind] if layout == 0 else want[kind].t()
+        assert got.shape == ref.shape
+        if kind == O.OUT_I32:
+            assert torch.equal(got, ref)
+        else:
+            assert torch.allclose(got.float(), ref.float(), rtol=1e-3, atol=0)
+            assert torch.equal(got, ref)          # same arithmetic -> same bits
+    # C restatement of the store conversions agrees too
+    assert np.array_equal(O.c_store_f16_scaled(acc.numpy(), alpha.numpy()).view(np.uint16), want[O.OUT_F16_SCALED].numpy().view(np.uint16))
+
+
+def test_f16_rounding_above_2048(B):
+    """|acc| > 2048 is not representable in fp16: the store must round to nearest even like __int2half_rn."""
+    M, N, K = 128, 16, 8192
+    w = torch.ones(M, K, dtype=torch.float16)
+    x = torch.ones(N, K, dtype=torch.float16)
+    x[:, :5] = -1                                     # acc = 8192 - 10 = 8182: a tie between 8180 and 8184 -> even
+    got = _run(B, w, x, O.OP_XOR, out_kind=O.OUT_F16)
+    assert torch.all(got == O.ref_out(O.ref_acc(w, x, O.OP_XOR), O.OUT_F16))
+    assert float(got[0, 0]) == 8184.0
+
+
+@pytest.mark.parametrize("op", OPS)
+@pytest.mark.parametrize("M,N,K", [(256, 32, 512), (100, 5, 300), (512, 96, 1280)])
+def test_linear_forward_dropin(B, op, M, N, K):
+    g = O._gen(op + M)
+    w = _rand_w(M, K, g, "randn")
+    x = _acts_for(op, N, K, g)
+    got = B.linear_forward(w.cuda(), x.cuda(), op, out_kind=B.OUT_F16).cpu()
+    assert torch.equal(got, O.ref_out(O.ref_acc(w, x, op), O.OUT_F16))
+    got32 = B.linear_forward(w.cuda(), x.cuda(), op, out_kind=B.OUT_I32, split_k=2).cpu()
+    assert torch.equal(got32, O.ref_acc(w, x, op))
+    if K % 128 == 0:
+        # packed-bit restatement of the reference PTX agrees with the dense definition
+        if op != O.OP_BWTA:
+            bits = O.c_bgemm_bits(O.c_pack_rowmajor_msb(w), O.c_pack_rowmajor_msb(x), K, op)
+            assert np.array_equal(bits, got32.numpy())
+
+
+def test_batched_attention_heads(B):
+    cfg = O.config3(heads=6, S=256, d=64)
+    a, v = cfg["attn"], cfg["v"]
+    H, S, d = v.shape
+    # the reference encodes the {0,1} mask in the sign bit: "1" = sign bit clear
+    plane, _, _ = B.pack_weights((2 * a - 1).cuda(), B.WBIT_NONNEGATIVE)
+    acts, colsum = B.prepare_acts(v.cuda(), B.ACT_SIGN, transpose=True)       # V^T: [H, d, S]
+    got = B.gemm(plane, S, S, acts, colsum, B.OP_ATTN, B.OUT_I32, B.LAYOUT_MN).cpu()
+    assert got.shape == (H, S, d)
+    assert torch.equal(got, O.ref_attn_heads(a, v))
+
+
+def test_argument_errors(B):
+    x = torch.zeros(4, 256, dtype=torch.float16, device="cuda")
+    assert B.lib.bgemm_pack_weights(None, None, 0, 4, 256, 256, 0, x.data_ptr(), None, None, 1, 0) == -1
+    assert B.lib.bgemm_pack_weights(None, x.data_ptr(), 9, 4, 256, 256, 0, x.data_ptr(), None, None, 1, 0) == -4
+    assert B.lib.bgemm_pack_weights(None, x.data_ptr(), 0, 0, 256, 256, 0, x.data_ptr(), None, None, 1, 0) == -2
+    assert B.lib.bgemm_gemm(None, x.data_ptr(), 4, 256, x.data_ptr(), x.data_ptr(), 4, 1, x.data_ptr(), 2, 0, None, 1, None, 0, 1) == -1
+    # split-K without a workspace is refused before anything is launched
+    assert B.lib.bgemm_gemm(None, x.data_ptr(), 4, 1024, x.data_ptr(), x.data_ptr(), 4, 1, x.data_ptr(), 0, 0, None, 2, None, 0, 1) == -5
+    assert b"workspace" in B.lib.bgemm_status_string(-5)
+    with pytest.raises(ValueError):
+        B.pack_weights(torch.zeros(4, 256, dtype=torch.float16))
