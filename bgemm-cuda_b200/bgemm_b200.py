@@ -24,7 +24,7 @@ lib = ctypes.CDLL(str(_LIB_PATH))
 # ---- constants of include/bgemm_b200.h ----
 DT_F16, DT_BF16, DT_F32, DT_I8 = 0, 1, 2, 3
 OP_AND, OP_XOR, OP_ATTN, OP_BWTA = 0, 1, 2, 3
-WBIT_NEGATIVE, WBIT_NONNEGATIVE = 0, 1
+WBIT_NEGATIVE, WBIT_NONNEGATIVE, WBIT_NONZERO, WBIT_NEGATIVE_NZ = 0, 1, 2, 3
 ACT_SIGN, ACT_TERNARY, ACT_NEG01 = 0, 1, 2
 OUT_I32, OUT_F16, OUT_F16_SCALED = 0, 1, 2
 LAYOUT_NM, LAYOUT_MN = 0, 1

@@ -9,28 +9,54 @@ namespace bgemm {
 static std::atomic<uint64_t> g_launches{0};
 void count_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
 
+static long long* g_prof = nullptr;
+long long* debug_profile_buffer() { return g_prof; }
+
+// Device status word: kernels record here which bounded wait ran out (0 = never). One word per device,
+// addressed through cudaGetSymbolAddress with that device current.
+__device__ int g_status_word = 0;
+int* device_status_word() {
+    static int* cache[64] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+    if (!cache[dev]) {
+        void* ptr = nullptr;
+        if (cudaGetSymbolAddress(&ptr, g_status_word) != cudaSuccess) return nullptr;
+        cache[dev] = static_cast<int*>(ptr);
+    }
+    return cache[dev];
+}
+
 static bool aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) % a) == 0; }
 static bool valid_dtype(int d) { return d >= BGEMM_DT_F16 && d <= BGEMM_DT_I8; }
 static size_t dt_size(int d) { return d == BGEMM_DT_F32 ? 4 : (d == BGEMM_DT_I8 ? 1 : 2); }
 
 constexpr long long kMaxDim = 1LL << 24;      // keeps every int32 accumulator and index computation exact
 constexpr int kMaxSplitK = 64;
-constexpr size_t kCounterBytesMin = 4096;
+constexpr int kMaxClusterSplit = 8;           // portable thread-block cluster size
+// Split-K beyond the cluster limit keeps one arrival counter per output tile in a FIXED-size prefix of the
+// workspace, so that a workspace shared by calls of different shapes never has partial sums where a later
+// call expects zeroed counters.
+constexpr size_t kCounterBytes = 64 * 1024;
+constexpr long long kMaxCounterTiles = kCounterBytes / 4;
 
-static size_t counter_bytes(long long tiles) { return align_up((size_t)tiles * 4 > kCounterBytesMin ? (size_t)tiles * 4 : kCounterBytesMin, 256); }
+static size_t counter_bytes(long long) { return kCounterBytes; }
 
 static int resolve_split_k(long long M, long long N, long long K, long long batch, int split_k) {
     const long long kblocks = (K + 255) / 256;
-    if (split_k >= 1) return (int)(split_k > kblocks ? kblocks : split_k);
-    // auto: aim at ~2 CTAs per SM worth of tiles, keep at least 2 K blocks per partition
     const int NT = gemm_tile_n(N);
     const long long tiles = ((M + 127) / 128) * ((N + NT - 1) / NT) * batch;
+    if (split_k >= 1) {
+        if (split_k > kMaxClusterSplit && tiles > kMaxCounterTiles) split_k = kMaxClusterSplit;
+        return (int)(split_k > kblocks ? kblocks : split_k);
+    }
+    // auto: aim at ~2 CTAs per SM worth of tiles, keep at least 2 K blocks per partition
     const long long target = 148LL * (NT <= 128 ? 2 : 1);
     long long s = target / (tiles > 0 ? tiles : 1);
     if (s < 1) s = 1;
     if (s > kblocks / 2) s = kblocks / 2;
     if (s < 1) s = 1;
-    if (s > kMaxSplitK) s = kMaxSplitK;
+    if (s > kMaxClusterSplit) s = kMaxClusterSplit;
     return (int)s;
 }
 
@@ -47,7 +73,22 @@ size_t bgemm_plane_bytes(int64_t M, int64_t K) {
 int64_t bgemm_act_ld(int64_t K) { return K < 1 ? 0 : (K + 255) / 256 * 256; }
 
 int bgemm_version(void) { return 100; }
+// Tuning aid (not declared in the public header): device buffer of 16 int64 per CTA that the GEMM fills
+// with phase stamps; pass NULL to switch it off again.
+void bgemm_debug_set_profile_buffer(void* dev_buffer) { g_prof = static_cast<long long*>(dev_buffer); }
 uint64_t bgemm_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
+
+int bgemm_device_status(int reset) {
+    int* w = device_status_word();
+    if (!w) return BGEMM_ERR_DRIVER;
+    int v = 0;
+    if (cudaMemcpy(&v, w, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) return BGEMM_ERR_DRIVER;
+    if (reset && v != 0) {
+        const int zero = 0;
+        cudaMemcpy(w, &zero, sizeof(int), cudaMemcpyHostToDevice);
+    }
+    return v;
+}
 
 const char* bgemm_status_string(int status) {
     switch (status) {
@@ -81,7 +122,7 @@ int bgemm_retile_rowmajor_msb(void* stream, const uint32_t* src_words, int64_t M
 int bgemm_pack_weights(void* stream, const void* src, int src_dtype, int64_t M, int64_t K, int64_t ld, int wbit_mode, void* plane,
                        int32_t* rowpop, void* alpha, int64_t batch, int64_t src_batch_stride) {
     if (!src || !plane) return BGEMM_ERR_NULL;
-    if (!valid_dtype(src_dtype) || wbit_mode < 0 || wbit_mode > 1) return BGEMM_ERR_ENUM;
+    if (!valid_dtype(src_dtype) || wbit_mode < BGEMM_WBIT_NEGATIVE || wbit_mode > BGEMM_WBIT_NEGATIVE_NZ) return BGEMM_ERR_ENUM;
     if (M < 1 || K < 1 || ld < K || batch < 1 || batch > 65535 || M > kMaxDim || K > kMaxDim) return BGEMM_ERR_SHAPE;
     if (batch > 1 && src_batch_stride < 0) return BGEMM_ERR_SHAPE;
     if (!aligned(plane, 16) || !aligned(src, dt_size(src_dtype))) return BGEMM_ERR_ALIGN;
@@ -107,7 +148,7 @@ int bgemm_gemm_auto_split_k(int64_t M, int64_t N, int64_t K, int64_t batch) {
 size_t bgemm_gemm_workspace_bytes(int64_t M, int64_t N, int64_t K, int split_k, int64_t batch) {
     if (M < 1 || N < 1 || K < 1 || batch < 1) return 0;
     const int s = resolve_split_k(M, N, K, batch, split_k);
-    if (s <= 1) return 0;
+    if (s <= kMaxClusterSplit) return 0;          // cluster / DSMEM reduction needs no global memory
     const int NT = gemm_tile_n(N);
     const long long tiles = ((M + 127) / 128) * ((N + NT - 1) / NT) * batch;
     return counter_bytes(tiles) + (size_t)tiles * (size_t)s * (size_t)NT * 128 * 4;
@@ -135,7 +176,8 @@ int bgemm_gemm(void* stream, const void* plane, int64_t M, int64_t K, const int8
     p.colsum = colsum;
     p.out = out;
     p.alpha = static_cast<const __half*>(alpha);
-    p.status = nullptr;
+    p.status = device_status_word();
+    p.prof = debug_profile_buffer();
     p.M = (int)M; p.N = (int)N; p.K = (int)K;
     p.kblocks = (int)((K + 255) / 256);
     p.mtiles = (int)mtiles;
@@ -144,7 +186,8 @@ int bgemm_gemm(void* stream, const void* plane, int64_t M, int64_t K, const int8
     p.out_kind = out_kind;
     p.out_layout = out_layout;
     p.plane_batch_bytes = (long long)bgemm_plane_bytes(M, K);
-    if (s > 1) {
+    p.cluster = (s > 1 && s <= kMaxClusterSplit) ? 1 : 0;
+    if (s > kMaxClusterSplit) {
         const size_t need = bgemm_gemm_workspace_bytes(M, N, K, s, batch);
         if (!workspace || workspace_bytes < need) return BGEMM_ERR_WORKSPACE;
         if (!aligned(workspace, 256)) return BGEMM_ERR_ALIGN;
@@ -159,7 +202,10 @@ int bgemm_gemm(void* stream, const void* plane, int64_t M, int64_t K, const int8
 // Workspace of the unpacked-operand entry point: [gemm workspace][plane][acts int8][colsum].
 static void linear_ws_layout(int64_t M, int64_t N, int64_t K, int s, size_t* off_plane, size_t* off_acts, size_t* off_colsum,
                              size_t* total) {
+    // The counter prefix is reserved even when this call needs no counters, so that operands are never
+    // parked where a later call on the same buffer expects zeroed counters.
     size_t o = align_up(bgemm_gemm_workspace_bytes(M, N, K, s, 1), 256);
+    if (o < kCounterBytes) o = kCounterBytes;
     *off_plane = o; o += align_up(bgemm_plane_bytes(M, K), 256);
     *off_acts = o;  o += align_up((size_t)N * (size_t)bgemm_act_ld(K), 256);
     *off_colsum = o; o += align_up((size_t)N * 4, 256);

@@ -6,19 +6,24 @@
 // the reference uses runs at ~0.4 POP/s on B200 (measured), an order of magnitude below kind::i8.
 //
 // One CTA computes a 128(M) x NT(N) tile over a K range [kb0, kb1) of 256-column blocks.
-//   warps 0-3  unpack: thread r owns weight row r of the tile; per K block it reads its 32 packed bytes
-//              from shared memory, expands them to 8 x (128 x 32) u8 operand slices with one or two
-//              logic ops per 4 elements, and writes them to tensor memory (tcgen05.st). Afterwards the
-//              same warps run the epilogue (tcgen05.ld, split-K reduction, scale, store).
-//   warp 4     allocates tensor memory; one lane issues 8 UMMAs (128 x NT x 32) per K block.
-//   warp 5     one lane streams the packed weight tiles (4 KB each, contiguous) with cp.async.bulk.
-//   warp 6     one lane loads the activation tiles [NT x 256 B] with two 128B-swizzled TMA boxes.
+//   warps 0-7  unpack, two sets of four warps taking alternate K blocks: thread r of a set owns weight row r
+//              of the tile; per K block it reads its 32 packed bytes from shared memory, expands them to
+//              8 x (128 x 32) u8 operand slices with one or two logic ops per 4 elements, and writes them to
+//              tensor memory (tcgen05.st). Afterwards all eight warps run the epilogue.
+//   warp 8     allocates tensor memory; one lane issues 8 UMMAs (128 x NT x 32) per K block.
+//   warp 9     one lane streams the packed weight tiles (4 KB each, contiguous) with cp.async.bulk.
+//   warp 10    one lane loads the activation tiles [NT x 256 B] with two 128B-swizzled TMA boxes.
 //
 // POW2 variant (NT <= 32, weight-streaming shapes): slice j keeps the weight bit at byte value 2^j
 // (a single AND per 4 elements) and accumulates into its own accumulator D_j; the epilogue adds
 // D_j >> j. The plain variant shifts the bit down to {0,1} and uses one accumulator.
 //
 // With D = sum_k bit_w(k) * x(k):  XOR / BWTA results are colsum_x[n] - 2 D, AND / ATTN results are D.
+//
+// Epilogue: the accumulator tile leaves tensor memory into shared memory as int32 [NT][128]; K partitions
+// are then summed -- by the CTAs of a thread-block cluster through distributed shared memory (up to 8
+// partitions), or through a global workspace by the last CTA to arrive (more than 8) -- and the result is
+// converted (fused per-row scale) and stored with 16-byte coalesced stores.
 #include <cuda_fp16.h>
 
 #include "internal.h"
@@ -26,8 +31,9 @@
 
 namespace bgemm {
 
-constexpr int kUnpackThreads = 128;
-constexpr int kGemmThreads = 224;
+constexpr int kUnpackThreads = 256;
+constexpr int kGemmThreads = 352;
+constexpr int kWarpMma = 8, kWarpW = 9, kWarpB = 10;
 
 __host__ __device__ constexpr int pow2_ceil(int v) {
     int p = 32;
@@ -38,45 +44,214 @@ __host__ __device__ constexpr int pow2_ceil(int v) {
 template <int NT, bool POW2>
 struct Cfg {
     static constexpr int D_COLS = POW2 ? 8 * NT : NT;
-    static constexpr int A_STAGES = POW2 ? (NT == 16 ? 2 : 4) : (NT == 64 ? 3 : (NT == 128 ? 2 : 4));
+    static constexpr int A_STAGES = POW2 ? (NT == 16 ? 2 : 4) : (NT <= 128 ? 2 : 4);
     static constexpr int A_COL0 = D_COLS;
     static constexpr int TMEM_COLS = pow2_ceil(D_COLS + 64 * A_STAGES);
     static constexpr int B_STAGE_BYTES = NT * 256;
-    static constexpr int B_STAGES = NT <= 32 ? 4 : 3;
-    static constexpr int W_STAGES = NT <= 32 ? 6 : (NT == 128 ? 3 : 4);
+    static constexpr int B_STAGES = NT <= 32 ? 6 : 3;
+    static constexpr int W_STAGES = NT <= 64 ? 8 : (NT == 128 ? 2 : 4);
     static constexpr int NBARS = 2 * W_STAGES + 2 * B_STAGES + 2 * A_STAGES + 1;
-    static constexpr int SMEM_USED = B_STAGES * B_STAGE_BYTES + W_STAGES * 4096 + 1024 /*barriers, flags*/ + 1024 /*align*/;
+    static constexpr int MISC_BYTES = 512 /*barriers*/ + 512 /*alpha*/ + 1024 /*colsum*/ + 512 /*flags*/;
+    static constexpr int STAGE_TILE_BYTES = NT * 128 * 4;   // epilogue staging, aliases the activation stages
+    static constexpr int SMEM_USED = B_STAGES * B_STAGE_BYTES + W_STAGES * 4096 + MISC_BYTES + 1024 /*align*/;
     // Co-resident CTAs must not ask for more tensor memory than the SM has (a later tcgen05.alloc would
     // stall until an earlier CTA exits): request enough shared memory to cap residency at 512 / TMEM_COLS.
     static constexpr int SMEM_FLOOR = TMEM_COLS == 512 ? 117 * 1024 : 77 * 1024;
     static constexpr int SMEM_BYTES = SMEM_USED > SMEM_FLOOR ? SMEM_USED : SMEM_FLOOR;
+    static constexpr int MIN_CTAS = TMEM_COLS <= 256 ? 2 : 1;
+    // The two unpack sets take alternate K blocks. With even stage counts a stage (and its barriers) is always
+    // served by the same set, so every waiter has seen the previous phase of the barrier it waits on; with an
+    // odd count a set's first wait on a barrier would name phase 1 and pass before phase 0 has completed.
+    static_assert(W_STAGES % 2 == 0 && A_STAGES % 2 == 0, "stage counts shared by the two unpack sets must be even");
     static_assert(TMEM_COLS <= 512, "tensor memory budget");
     static_assert(NT % 16 == 0 && NT >= 16 && NT <= 256, "UMMA N");
+    static_assert(NBARS * 8 <= 512, "barrier area");
+    static_assert(STAGE_TILE_BYTES <= B_STAGES * B_STAGE_BYTES, "staging tile must fit in the activation stages");
+    static_assert(SMEM_BYTES <= 227 * 1024, "shared memory budget");
 };
 
-__device__ __forceinline__ void store_result(const GemmParams& p, int batch, int m, int n, int acc) {
-    if (m >= p.M || n >= p.N) return;
-    const int val = p.epi ? (__ldg(p.colsum + (size_t)batch * p.N + n) - 2 * acc) : acc;
-    const size_t idx = (size_t)batch * p.M * p.N + (p.out_layout == BGEMM_LAYOUT_NM ? (size_t)n * p.M + m : (size_t)m * p.N + n);
+// Optional phase stamps (SM clock, relative to CTA start) for tuning; p.prof is null in normal use.
+#define BGEMM_STAMP(slot)                                                                                            \
+    do {                                                                                                             \
+        if (p.prof) p.prof[(size_t)((blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x) * 16 + (slot)] = \
+            (slot) >= 10 ? (long long)globaltimer_ns() : clock64() - t_cta0;                                         \
+    } while (0)
+
+// ---- epilogue: converting and storing 8 results --------------------------------------------------------------
+struct TileOut {
+    const GemmParams* p;
+    const float* s_alpha;    // [128] per-row scale of this tile (1 when unused)
+    const int* s_colsum;     // [NT] column sums of this tile (0 when unused)
+    int batch, m_base, n_base;
+};
+
+// 8 consecutive rows m0..m0+7 (tile-local) of column n (tile-local): the [N, M] layout.
+__device__ __forceinline__ void store8_rows(const TileOut& t, int n, int m0, const int (&acc)[8]) {
+    const GemmParams& p = *t.p;
+    const int gn = t.n_base + n, gm = t.m_base + m0;
+    if (gn >= p.N || gm >= p.M) return;
+    const int cs = t.s_colsum[n];
+    int val[8];
+#pragma unroll
+    for (int q = 0; q < 8; q++) val[q] = p.epi ? cs - 2 * acc[q] : acc[q];
+    const size_t idx = (size_t)t.batch * p.M * p.N + (size_t)gn * p.M + gm;
+    const bool full = gm + 8 <= p.M;
     if (p.out_kind == BGEMM_OUT_I32) {
-        reinterpret_cast<int*>(p.out)[idx] = val;
-    } else if (p.out_kind == BGEMM_OUT_F16) {
-        reinterpret_cast<__half*>(p.out)[idx] = __float2half_rn((float)val);
+        int* o = reinterpret_cast<int*>(p.out) + idx;
+        if (full && (reinterpret_cast<uintptr_t>(o) & 15) == 0) {
+            reinterpret_cast<int4*>(o)[0] = make_int4(val[0], val[1], val[2], val[3]);
+            reinterpret_cast<int4*>(o)[1] = make_int4(val[4], val[5], val[6], val[7]);
+        } else {
+#pragma unroll
+            for (int q = 0; q < 8; q++) if (gm + q < p.M) o[q] = val[q];
+        }
     } else {
-        const float a = __half2float(p.alpha[(size_t)batch * p.M + m]);
-        reinterpret_cast<__half*>(p.out)[idx] = __float2half_rn((float)val * a);
+        __align__(16) __half h[8];
+#pragma unroll
+        for (int q = 0; q < 8; q++)
+            h[q] = __float2half_rn(p.out_kind == BGEMM_OUT_F16 ? (float)val[q] : (float)val[q] * t.s_alpha[m0 + q]);
+        __half* o = reinterpret_cast<__half*>(p.out) + idx;
+        if (full && (reinterpret_cast<uintptr_t>(o) & 15) == 0) {
+            *reinterpret_cast<uint4*>(o) = *reinterpret_cast<const uint4*>(h);
+        } else {
+#pragma unroll
+            for (int q = 0; q < 8; q++) if (gm + q < p.M) o[q] = h[q];
+        }
+    }
+}
+
+// 8 consecutive columns n0..n0+7 (tile-local) of row m (tile-local): the [M, N] layout.
+__device__ __forceinline__ void store8_cols(const TileOut& t, int m, int n0, const int (&acc)[8]) {
+    const GemmParams& p = *t.p;
+    const int gm = t.m_base + m, gn = t.n_base + n0;
+    if (gm >= p.M || gn >= p.N) return;
+    int val[8];
+#pragma unroll
+    for (int q = 0; q < 8; q++) val[q] = p.epi ? t.s_colsum[n0 + q] - 2 * acc[q] : acc[q];
+    const size_t idx = (size_t)t.batch * p.M * p.N + (size_t)gm * p.N + gn;
+    const bool full = gn + 8 <= p.N;
+    if (p.out_kind == BGEMM_OUT_I32) {
+        int* o = reinterpret_cast<int*>(p.out) + idx;
+        if (full && (reinterpret_cast<uintptr_t>(o) & 15) == 0) {
+            reinterpret_cast<int4*>(o)[0] = make_int4(val[0], val[1], val[2], val[3]);
+            reinterpret_cast<int4*>(o)[1] = make_int4(val[4], val[5], val[6], val[7]);
+        } else {
+#pragma unroll
+            for (int q = 0; q < 8; q++) if (gn + q < p.N) o[q] = val[q];
+        }
+    } else {
+        const float a = t.s_alpha[m];
+        __align__(16) __half h[8];
+#pragma unroll
+        for (int q = 0; q < 8; q++) h[q] = __float2half_rn(p.out_kind == BGEMM_OUT_F16 ? (float)val[q] : (float)val[q] * a);
+        __half* o = reinterpret_cast<__half*>(p.out) + idx;
+        if (full && (reinterpret_cast<uintptr_t>(o) & 15) == 0) {
+            *reinterpret_cast<uint4*>(o) = *reinterpret_cast<const uint4*>(h);
+        } else {
+#pragma unroll
+            for (int q = 0; q < 8; q++) if (gn + q < p.N) o[q] = h[q];
+        }
+    }
+}
+
+// Where the partial tiles of the K partitions are: 0 this CTA's shared memory only (one partition),
+// 1 every cluster peer's shared memory, 2 slabs in global memory.
+enum { kSrcLocal = 0, kSrcCluster = 1, kSrcGlobal = 2 };
+
+// Sum over the partitions of 8 consecutive rows (element offset `off` = n * 128 + m0 of the [NT][128] tile).
+template <int SRC, int NT>
+__device__ __forceinline__ void gather8_rows(const int* sP, const int* gbase, int parts, int off, int (&acc)[8]) {
+    if (SRC == kSrcLocal) {
+        const int4 a = *reinterpret_cast<const int4*>(sP + off), b = *reinterpret_cast<const int4*>(sP + off + 4);
+        acc[0] = a.x; acc[1] = a.y; acc[2] = a.z; acc[3] = a.w; acc[4] = b.x; acc[5] = b.y; acc[6] = b.z; acc[7] = b.w;
+        return;
+    }
+#pragma unroll
+    for (int q = 0; q < 8; q++) acc[q] = 0;
+    if (SRC == kSrcCluster) {
+        const uint32_t mine = smem_u32(sP + off);
+#pragma unroll 4
+        for (int peer = 0; peer < parts; peer++) {
+            const uint32_t r = mapa_shared(mine, (uint32_t)peer);
+            const int4 a = ld_dsmem_v4(r), b = ld_dsmem_v4(r + 16);
+            acc[0] += a.x; acc[1] += a.y; acc[2] += a.z; acc[3] += a.w; acc[4] += b.x; acc[5] += b.y; acc[6] += b.z; acc[7] += b.w;
+        }
+    } else {
+#pragma unroll 4
+        for (int s = 0; s < parts; s++) {
+            const int4* g = reinterpret_cast<const int4*>(gbase + (size_t)s * (NT * 128) + off);
+            const int4 a = __ldcg(g), b = __ldcg(g + 1);
+            acc[0] += a.x; acc[1] += a.y; acc[2] += a.z; acc[3] += a.w; acc[4] += b.x; acc[5] += b.y; acc[6] += b.z; acc[7] += b.w;
+        }
+    }
+}
+
+// Sum over the partitions of 8 consecutive columns n0..n0+7 of row m.
+template <int SRC, int NT>
+__device__ __forceinline__ void gather8_cols(const int* sP, const int* gbase, int parts, int n0, int m, int (&acc)[8]) {
+#pragma unroll
+    for (int q = 0; q < 8; q++) acc[q] = 0;
+    if (SRC == kSrcLocal) {
+#pragma unroll
+        for (int q = 0; q < 8; q++) acc[q] = sP[(n0 + q) * 128 + m];
+    } else if (SRC == kSrcCluster) {
+        const uint32_t mine = smem_u32(sP + n0 * 128 + m);
+#pragma unroll 2
+        for (int peer = 0; peer < parts; peer++) {
+            const uint32_t r = mapa_shared(mine, (uint32_t)peer);
+#pragma unroll
+            for (int q = 0; q < 8; q++) acc[q] += ld_dsmem_s32(r + (uint32_t)(q * 128 * 4));
+        }
+    } else {
+#pragma unroll 2
+        for (int s = 0; s < parts; s++) {
+#pragma unroll
+            for (int q = 0; q < 8; q++) acc[q] += __ldcg(gbase + (size_t)s * (NT * 128) + (n0 + q) * 128 + m);
+        }
+    }
+}
+
+// Convert and store columns [nbeg, nend) of the tile with all 256 epilogue threads.
+template <int SRC, int NT>
+__device__ __forceinline__ void write_tile(const TileOut& t, const int* sP, const int* gbase, int parts, int nbeg, int nend, int et) {
+    const GemmParams& p = *t.p;
+    if (p.out_layout == BGEMM_LAYOUT_NM) {
+        const int units = (nend - nbeg) * 16;                   // (column, 8-row chunk)
+#pragma unroll 1
+        for (int u = et; u < units; u += kUnpackThreads) {
+            const int n = nbeg + (u >> 4), m0 = (u & 15) * 8;
+            if (t.n_base + n >= p.N || t.m_base + m0 >= p.M) continue;
+            int acc[8];
+            gather8_rows<SRC, NT>(sP, gbase, parts, n * 128 + m0, acc);
+            store8_rows(t, n, m0, acc);
+        }
+    } else {
+        const int units = ((nend - nbeg) >> 3) * 128;           // (8-column chunk, row)
+#pragma unroll 1
+        for (int u = et; u < units; u += kUnpackThreads) {
+            const int m = u & 127, n0 = nbeg + (u >> 7) * 8;
+            if (t.n_base + n0 >= p.N || t.m_base + m >= p.M) continue;
+            int acc[8];
+            gather8_cols<SRC, NT>(sP, gbase, parts, n0, m, acc);
+            store8_cols(t, m, n0, acc);
+        }
     }
 }
 
 template <int NT, bool POW2>
-__global__ void __launch_bounds__(kGemmThreads, 1) gemm_kernel(const __grid_constant__ CUtensorMap tmap_acts, const GemmParams p) {
+__global__ void __launch_bounds__(kGemmThreads, Cfg<NT, POW2>::MIN_CTAS) gemm_kernel(const __grid_constant__ CUtensorMap tmap_acts, const GemmParams p) {
     using C = Cfg<NT, POW2>;
+    const long long t_cta0 = clock64();
+    if (threadIdx.x == 0) BGEMM_STAMP(10);
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t* sB = smem;
     uint8_t* sW = sB + C::B_STAGES * C::B_STAGE_BYTES;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(sW + C::W_STAGES * 4096);
-    uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + C::NBARS);
+    uint8_t* misc = sW + C::W_STAGES * 4096;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(misc);
+    float* s_alpha = reinterpret_cast<float*>(misc + 512);
+    int* s_colsum = reinterpret_cast<int*>(misc + 1024);
+    uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(misc + 2048);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
     int* last_flag = reinterpret_cast<int*>(tmem_holder + 2);
 
@@ -90,32 +265,45 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_kernel(const __grid_cons
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int nt = blockIdx.x;
-    const int split = blockIdx.y % p.split_k;
+    const int split = blockIdx.y % p.split_k;     // == rank inside the cluster when p.cluster
     const int mt = blockIdx.y / p.split_k;
     const int batch = blockIdx.z;
     const int kb0 = (int)(((long long)p.kblocks * split) / p.split_k);
     const int kb1 = (int)(((long long)p.kblocks * (split + 1)) / p.split_k);
     const int nkb = kb1 - kb0;
 
-    if (tid == 0) {
-        for (int i = 0; i < C::W_STAGES; i++) { mbar_init(w_full + 8 * i, 1); mbar_init(w_empty + 8 * i, 4); }
-        for (int i = 0; i < C::B_STAGES; i++) { mbar_init(b_full + 8 * i, 1); mbar_init(b_empty + 8 * i, 1); }
-        for (int i = 0; i < C::A_STAGES; i++) { mbar_init(a_full + 8 * i, 4); mbar_init(a_empty + 8 * i, 1); }
-        mbar_init(d_full, 1);
-        *abort_flag = 0;
-        *last_flag = 0;
+    if (warp == 0) {
+        // barrier i of the area: arrival count 4 for the two kinds that collect one arrival per unpack warp
+        for (int i = lane; i < C::NBARS; i += 32) {
+            const bool four = (i >= C::W_STAGES && i < 2 * C::W_STAGES) ||
+                              (i >= 2 * C::W_STAGES + 2 * C::B_STAGES && i < 2 * C::W_STAGES + 2 * C::B_STAGES + C::A_STAGES);
+            mbar_init(w_full + 8 * i, four ? 4 : 1);
+        }
+        if (lane == 0) { *abort_flag = 0; *last_flag = 0; }
         mbar_fence_init();
+    } else if (warp == kWarpB) {
+        if (lane == 0) tma_prefetch_desc(&tmap_acts);
+    } else if (warp == kWarpMma) {
+        tmem_alloc(smem_u32(tmem_holder), C::TMEM_COLS);
+    } else if (warp >= 1 && warp <= 4) {
+        const int i = tid - 32;                                  // per-row scale of this tile
+        const int m = mt * 128 + i;
+        s_alpha[i] = (p.out_kind == BGEMM_OUT_F16_SCALED && m < p.M) ? __half2float(p.alpha[(size_t)batch * p.M + m]) : 1.f;
+    } else if (warp >= 5 && warp <= 7) {
+        for (int i = tid - 160; i < NT; i += 96) {               // column sums of this tile
+            const int n = nt * NT + i;
+            s_colsum[i] = (p.epi && n < p.N) ? __ldg(p.colsum + (size_t)batch * p.N + n) : 0;
+        }
     }
-    if (warp == 6 && lane == 0) tma_prefetch_desc(&tmap_acts);
-    if (warp == 4) tmem_alloc(smem_u32(tmem_holder), C::TMEM_COLS);
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = *tmem_holder;
     const uint32_t tmem_d = tmem;
     const uint32_t tmem_a = tmem + C::A_COL0;
+    if (tid == 0) BGEMM_STAMP(1);
 
-    if (warp == 5) {
+    if (warp == kWarpW) {
         // ---------------- weight producer ----------------
         if (lane == 0) {
             const uint8_t* src = p.plane + (size_t)batch * p.plane_batch_bytes + ((size_t)mt * p.kblocks + kb0) * 4096;
@@ -125,6 +313,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_kernel(const __grid_cons
                 if (i >= C::W_STAGES && !mbar_wait(w_empty + 8 * s, ((i / C::W_STAGES) - 1) & 1, abort_flag, p.status, 11)) break;
                 mbar_arrive_expect_tx(w_full + 8 * s, 4096);
                 bulk_g2s(smem_u32(sW + s * 4096), src + (size_t)i * 4096, 4096, w_full + 8 * s);
+                if (i == 0) BGEMM_STAMP(2);
                 issued = i + 1;
             }
             if (*abort_flag) {  // drain own copies before the CTA may exit
@@ -134,7 +323,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_kernel(const __grid_cons
                 }
             }
         }
-    } else if (warp == 6) {
+    } else if (warp == kWarpB) {
         // ---------------- activation producer ----------------
         if (lane == 0) {
             int issued = 0;
@@ -154,17 +343,18 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_kernel(const __grid_cons
                 }
             }
         }
-    } else if (warp == 4) {
+    } else if (warp == kWarpMma) {
         // ---------------- UMMA issuer ----------------
         if (lane == 0) {
             constexpr uint32_t idesc = umma_idesc_u8s8(NT);
             bool ok = true;
             for (int i = 0; i < nkb && ok; i++) {
                 const int as = i % C::A_STAGES, bs = i % C::B_STAGES;
-                ok = mbar_wait(a_full + 8 * as, (i / C::A_STAGES) & 1, abort_flag, p.status, 13) &&
-                     mbar_wait(b_full + 8 * bs, (i / C::B_STAGES) & 1, abort_flag, p.status, 14);
+                ok = mbar_wait(b_full + 8 * bs, (i / C::B_STAGES) & 1, abort_flag, p.status, 14) &&
+                     mbar_wait(a_full + 8 * as, (i / C::A_STAGES) & 1, abort_flag, p.status, 13);
                 if (!ok) break;
                 tc_fence_after();
+                if (i == 0) BGEMM_STAMP(5);
                 const uint32_t bbase = smem_u32(sB + bs * C::B_STAGE_BYTES);
 #pragma unroll
                 for (int j = 0; j < 8; j++) {
@@ -177,17 +367,20 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_kernel(const __grid_cons
                 umma_commit(b_empty + 8 * bs);
             }
             umma_commit(d_full);
+            BGEMM_STAMP(6);
         }
     } else {
-        // ---------------- unpack (warps 0-3), then epilogue ----------------
-        const int r = tid;  // weight row of the tile == tensor-memory lane
-        const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
+        // ---------------- unpack: set 0 = warps 0-3 takes even K blocks, set 1 = warps 4-7 odd ones ----------------
+        const int set = warp >> 2;
+        const int r = (warp & 3) * 32 + lane;                 // weight row of the tile == tensor-memory lane
+        const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
         bool ok = true;
-        for (int i = 0; i < nkb && ok; i++) {
+        for (int i = set; i < nkb && ok; i += 2) {
             const int ws = i % C::W_STAGES, as = i % C::A_STAGES;
             ok = mbar_wait(w_full + 8 * ws, (i / C::W_STAGES) & 1, abort_flag, p.status, 15);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
+            if (i == 0 && tid == 0) BGEMM_STAMP(3);
             const uint4 lo = *reinterpret_cast<const uint4*>(sW + ws * 4096 + r * 16);
             const uint4 hi = *reinterpret_cast<const uint4*>(sW + ws * 4096 + 2048 + r * 16);
             __syncwarp();
@@ -208,76 +401,108 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_kernel(const __grid_cons
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(a_full + 8 * as);
+            if (i == 0 && tid == 0) BGEMM_STAMP(4);
         }
-
-        // ---- epilogue ----
         ok = ok && mbar_wait(d_full, 0, abort_flag, p.status, 17);
         ok = __all_sync(0xffffffffu, ok);
         tc_fence_after();
-        const int m = mt * 128 + r;
-        const int tile_id = (batch * p.mtiles + mt) * p.ntiles + nt;
-        int* slab = p.ws_partial ? p.ws_partial + ((size_t)tile_id * p.split_k + split) * (NT * 128) : nullptr;
+        if (!ok) *abort_flag = 1;
+        if (tid == 0) BGEMM_STAMP(7);
+
+        // ---- accumulators -> shared memory: int32 [NT][128]; warps 0-3 take the lower half of the columns ----
+        int* sPw = reinterpret_cast<int*>(sB);
         if (ok) {
-            constexpr int CH = 8;
+            constexpr int HALF = NT / 2;
 #pragma unroll 1
-            for (int n0 = 0; n0 < NT; n0 += CH) {
-                int acc[CH];
+            for (int n0 = set * HALF; n0 < (set + 1) * HALF; n0 += 8) {
+                int acc[8];
                 if (POW2) {
+                    uint32_t t[8][8];
 #pragma unroll
-                    for (int q = 0; q < CH; q++) acc[q] = 0;
+                    for (int j = 0; j < 8; j++) tmem_ld8(tmem_d + lane_base + j * NT + n0, t[j]);
+                    tmem_wait_ld();
 #pragma unroll
-                    for (int j = 0; j < 8; j++) {
-                        uint32_t t[8];
-                        tmem_ld8(tmem_d + lane_base + j * NT + n0, t);
-                        tmem_wait_ld();
+                    for (int q = 0; q < 8; q++) {
+                        acc[q] = 0;
 #pragma unroll
-                        for (int q = 0; q < CH; q++) acc[q] += ((int)t[q]) >> j;
+                        for (int j = 0; j < 8; j++) acc[q] += ((int)t[j][q]) >> j;
                     }
                 } else {
                     uint32_t t[8];
                     tmem_ld8(tmem_d + lane_base + n0, t);
                     tmem_wait_ld();
 #pragma unroll
-                    for (int q = 0; q < CH; q++) acc[q] = (int)t[q];
+                    for (int q = 0; q < 8; q++) acc[q] = (int)t[q];
                 }
-                if (p.split_k == 1) {
 #pragma unroll
-                    for (int q = 0; q < CH; q++) store_result(p, batch, m, nt * NT + n0 + q, acc[q]);
-                } else {
-#pragma unroll
-                    for (int q = 0; q < CH; q++) slab[(n0 + q) * 128 + r] = acc[q];
-                }
-            }
-        }
-        if (p.split_k > 1) {
-            // The last CTA of this tile to arrive sums every partial slab and stores the result.
-            __threadfence();
-            named_bar_sync(1, kUnpackThreads);
-            if (tid == 0) {
-                const unsigned ticket = atomicAdd(p.ws_counters + tile_id, 1u);
-                const int last = (ticket == (unsigned)p.split_k - 1) ? 1 : 0;
-                if (last) p.ws_counters[tile_id] = 0;  // leave the counter ready for the next launch
-                *last_flag = last;
-            }
-            named_bar_sync(1, kUnpackThreads);
-            if (*last_flag && !*abort_flag) {
-                __threadfence();
-                const int* base = p.ws_partial + (size_t)tile_id * p.split_k * (NT * 128);
-#pragma unroll 1
-                for (int n = 0; n < NT; n++) {
-                    int acc = 0;
-                    for (int s = 0; s < p.split_k; s++) acc += __ldcg(base + (size_t)s * (NT * 128) + n * 128 + r);
-                    store_result(p, batch, m, nt * NT + n, acc);
-                }
+                for (int q = 0; q < 8; q++) sPw[(n0 + q) * 128 + r] = acc[q];
             }
         }
         tc_fence_before();
     }
+
+    // ======================================= reduce, convert, store ================================================
+    const bool epi_thread = warp < 8;
+    const int* sP = reinterpret_cast<const int*>(sB);
+    TileOut tout;
+    tout.p = &p; tout.s_alpha = s_alpha; tout.s_colsum = s_colsum;
+    tout.batch = batch; tout.m_base = mt * 128; tout.n_base = nt * NT;
+
+    if (p.split_k == 1) {
+        if (epi_thread) {
+            named_bar_sync(1, kUnpackThreads);
+            if (!*abort_flag) write_tile<kSrcLocal, NT>(tout, sP, nullptr, 1, 0, NT, tid);
+        }
+    } else if (p.cluster) {
+        // The K partitions of a tile form a thread-block cluster: after the barrier CTA c sums columns
+        // [c * per, (c + 1) * per) over all peers through distributed shared memory and stores them.
+        __syncwarp();
+        cluster_arrive_release();
+        cluster_wait_acquire();
+        if (epi_thread && !*abort_flag) {
+            const int per = ((NT + p.split_k - 1) / p.split_k + 7) & ~7;     // columns per CTA, multiple of 8
+            const int nbeg = min(NT, split * per), nend = min(NT, nbeg + per);
+            write_tile<kSrcCluster, NT>(tout, sP, nullptr, p.split_k, nbeg, nend, tid);
+        }
+        __syncwarp();
+        cluster_arrive_release();      // nobody may exit while a peer still reads its shared memory
+        cluster_wait_acquire();
+    } else if (epi_thread) {
+        // More partitions than a cluster holds: partial tiles go to a global workspace; the last CTA of a tile
+        // to arrive (atomic ticket, nobody spins) sums them.
+        const int tile_id = (batch * p.mtiles + mt) * p.ntiles + nt;
+        int* slab = p.ws_partial + ((size_t)tile_id * p.split_k + split) * (NT * 128);
+        named_bar_sync(1, kUnpackThreads);
+        if (!*abort_flag) {
+            for (int i = tid; i < NT * 32; i += kUnpackThreads) reinterpret_cast<int4*>(slab)[i] = reinterpret_cast<const int4*>(sP)[i];
+        }
+        __threadfence();
+        named_bar_sync(1, kUnpackThreads);
+        if (tid == 0) {
+            const unsigned ticket = atomicAdd(p.ws_counters + tile_id, 1u);
+            const int last = (ticket == (unsigned)p.split_k - 1) ? 1 : 0;
+            if (last) p.ws_counters[tile_id] = 0;  // leave the counter ready for the next launch
+            *last_flag = last;
+        }
+        named_bar_sync(1, kUnpackThreads);
+        if (*last_flag && !*abort_flag) {
+            __threadfence();
+            write_tile<kSrcGlobal, NT>(tout, sP, p.ws_partial + (size_t)tile_id * p.split_k * (NT * 128), p.split_k, 0, NT, tid);
+        }
+    }
+    if (tid == 0) BGEMM_STAMP(8);
+    tc_fence_before();
     __syncthreads();
-    if (warp == 4) {
+    if (warp == kWarpMma) {
+        if (*abort_flag && lane == 0) {   // a wait ran out: let the issued UMMAs finish before the columns are freed
+            const long long t0 = clock64();
+            while (!mbar_test(d_full, 0) && clock64() - t0 < kWaitBudgetClocks) {}
+        }
+        __syncwarp();
         tc_fence_after();
         tmem_dealloc(tmem, C::TMEM_COLS);
     }
+    if (tid == 0) { BGEMM_STAMP(9); BGEMM_STAMP(11); }
 }
 
 // ---- host side ----------------------------------------------------------------------------------------
@@ -311,9 +536,23 @@ static int launch_variant(cudaStream_t stream, const CUtensorMap& tmap, const Ge
         if (e != cudaSuccess) return (int)e;
         configured[dev] = true;
     }
-    gemm_kernel<NT, POW2><<<grid, kGemmThreads, C::SMEM_BYTES, stream>>>(tmap, p);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(kGemmThreads, 1, 1);
+    cfg.dynamicSmemBytes = C::SMEM_BYTES;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    if (p.cluster) {
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = 1;
+        attr[0].val.clusterDim.y = (unsigned)p.split_k;
+        attr[0].val.clusterDim.z = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+    }
+    const cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_kernel<NT, POW2>, tmap, p);
     count_launch();
-    return (int)cudaGetLastError();
+    return (int)(e != cudaSuccess ? e : cudaGetLastError());
 }
 
 int gemm_tile_n(long long N) {

@@ -17,16 +17,19 @@ struct GemmParams {
     int32_t* ws_partial;          // split-K slabs [tile][split][NT][128], null when split_k == 1
     unsigned int* ws_counters;    // split-K arrival counters [tile]
     int* status;                  // device status word (0 = fine), may be null
+    long long* prof;              // optional phase stamps, 16 slots per CTA (tuning aid), normally null
     int M, N, K;
     int kblocks;                  // ceil(K / 256)
     int mtiles, ntiles;
     int split_k;
+    int cluster;                  // 1: the split_k CTAs of a tile form a cluster and reduce through DSMEM
     int epi;                      // 0: result = D, 1: result = colsum[n] - 2 D
     int out_kind, out_layout;
     long long plane_batch_bytes;
 };
 
 void count_launch();
+long long* debug_profile_buffer();
 int* device_status_word();        // per-device status word, lazily created (cudaGetSymbolAddress)
 
 int gemm_tile_n(long long N);

@@ -42,12 +42,22 @@ template <> struct Elem<int8_t> {
 // four words of every row, so that a warp's 16-byte reads of consecutive rows are contiguous.
 __host__ __device__ __forceinline__ int tile_word_offset(int r, int c) { return (c >> 2) * 2048 + r * 16 + (c & 3) * 4; }
 
+// Bit a weight-slot element contributes under BGEMM_WBIT_* mode.
+template <typename T>
+__host__ __device__ __forceinline__ int weight_bit(const T& v, int mode) {
+    const int neg = Elem<T>::neg(v);
+    if (mode == BGEMM_WBIT_NEGATIVE) return neg;
+    if (mode == BGEMM_WBIT_NONNEGATIVE) return neg ^ 1;
+    const int nz = Elem<T>::zero(v) ^ 1;
+    return mode == BGEMM_WBIT_NONZERO ? nz : (neg & nz);
+}
+
 // ---- weights -> tiled plane (+ rowpop, alpha) ---------------------------------------------------------------
 // One warp per row of the padded matrix. Lane L reads elements k = 256 kb + 8 L + e (e = 0..7): slice
 // j = L / 4, words c = 2 (L % 4) + e / 4, byte b = e % 4 -> bit 8 b + j. Words are completed by OR-ing
 // across the eight lanes that share L % 4.
 template <typename T>
-__global__ void __launch_bounds__(256) pack_weights_kernel(const T* __restrict__ src, long long M, long long K, long long ld, int invert,
+__global__ void __launch_bounds__(256) pack_weights_kernel(const T* __restrict__ src, long long M, long long K, long long ld, int mode,
                                                            uint8_t* __restrict__ plane, int32_t* __restrict__ rowpop,
                                                            __half* __restrict__ alpha, long long src_batch_stride,
                                                            long long plane_batch_bytes) {
@@ -80,7 +90,7 @@ __global__ void __launch_bounds__(256) pack_weights_kernel(const T* __restrict__
 #pragma unroll
             for (int e = 0; e < 8; e++) {
                 if (k0 + e < K) {
-                    const uint32_t bit = (uint32_t)(Elem<T>::neg(v[e]) ^ invert);
+                    const uint32_t bit = (uint32_t)weight_bit<T>(v[e], mode);
                     if (e < 4) w0 |= bit << (8 * e + j); else w1 |= bit << (8 * (e - 4) + j);
                     if (alpha) mag += Elem<T>::mag(v[e]);
                 }
@@ -257,7 +267,7 @@ int launch_pack_weights(cudaStream_t stream, const void* src, int dtype, long lo
     dim3 grid((unsigned)((rows + 7) / 8), (unsigned)batch);
     const long long pbytes = (long long)bgemm_plane_bytes(M, K);
     BGEMM_DISPATCH_DTYPE(dtype, (pack_weights_kernel<T><<<grid, 256, 0, stream>>>(
-                                    static_cast<const T*>(src), M, K, ld, wbit_mode == BGEMM_WBIT_NONNEGATIVE ? 1 : 0,
+                                    static_cast<const T*>(src), M, K, ld, wbit_mode,
                                     static_cast<uint8_t*>(plane), rowpop, static_cast<__half*>(alpha), src_batch_stride, pbytes)));
     count_launch();
     return (int)cudaGetLastError();
@@ -313,6 +323,14 @@ static int host_neg_any(const void* p, int dtype) {
         default: return host_neg(static_cast<const int8_t*>(p));
     }
 }
+static int host_bit_any(const void* p, int dtype, int mode) {
+    switch (dtype) {
+        case BGEMM_DT_F16: return weight_bit(*static_cast<const __half*>(p), mode);
+        case BGEMM_DT_BF16: return weight_bit(*static_cast<const __nv_bfloat16*>(p), mode);
+        case BGEMM_DT_F32: return weight_bit(*static_cast<const float*>(p), mode);
+        default: return weight_bit(*static_cast<const int8_t*>(p), mode);
+    }
+}
 static size_t dtype_size(int dtype) { return dtype == BGEMM_DT_F32 ? 4 : (dtype == BGEMM_DT_I8 ? 1 : 2); }
 
 }  // namespace bgemm
@@ -323,7 +341,7 @@ extern "C" int bgemm_pack_weights_host(const void* src, int dtype, int64_t M, in
                                        int32_t* rowpop, void* alpha) {
     if (!src || !plane) return BGEMM_ERR_NULL;
     if (M < 1 || K < 1 || ld < K) return BGEMM_ERR_SHAPE;
-    if (dtype < 0 || dtype > 3 || wbit_mode < 0 || wbit_mode > 1) return BGEMM_ERR_ENUM;
+    if (dtype < 0 || dtype > 3 || wbit_mode < 0 || wbit_mode > 3) return BGEMM_ERR_ENUM;
     const int64_t kblocks = (K + 255) / 256;
     std::memset(plane, 0, bgemm_plane_bytes(M, K));
     const size_t es = dtype_size(dtype);
@@ -335,7 +353,7 @@ extern "C" int bgemm_pack_weights_host(const void* src, int dtype, int64_t M, in
         const int r = (int)(m % 128);
         for (int64_t k = 0; k < K; k++) {
             const void* e = s + (size_t)(m * ld + k) * es;
-            const int bit = host_neg_any(e, dtype) ^ (wbit_mode == BGEMM_WBIT_NONNEGATIVE ? 1 : 0);
+            const int bit = host_bit_any(e, dtype, wbit_mode);
             if (alpha) mag += host_mag(e, dtype);
             if (!bit) continue;
             pop++;

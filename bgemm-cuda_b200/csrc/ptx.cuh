@@ -10,6 +10,12 @@ namespace bgemm {
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
+__device__ __forceinline__ unsigned long long globaltimer_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
+
 // ---- mbarrier ---------------------------------------------------------------------------------------
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
@@ -34,20 +40,29 @@ __device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
 // Wait budget in SM clocks (~1 s at 2 GHz). Far above any legitimate wait of these kernels.
 constexpr long long kWaitBudgetClocks = 2000000000LL;
 
+// One blocking probe: the thread is suspended by the hardware (no issue slots burnt) until the phase
+// completes or a short, implementation-defined time passes.
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.b32 %0, 1, 0, p;\n}\n"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+
 // Bounded wait. `abort_flag` lives in shared memory; once any thread sets it every wait falls through.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status_word,
                                           int where) {
-    if (mbar_test(bar, parity)) return true;
+    if (mbar_try_wait(bar, parity)) return true;
     const long long t0 = clock64();
-    int spins = 0;
-    while (!mbar_test(bar, parity)) {
-        if (((++spins) & 63) == 0) {
-            if (*abort_flag) return false;
-            if (clock64() - t0 > kWaitBudgetClocks) {
-                *abort_flag = 1;
-                if (status_word) atomicCAS(status_word, 0, where);
-                return false;
-            }
+    while (!mbar_try_wait(bar, parity)) {
+        if (*abort_flag) return false;
+        if (clock64() - t0 > kWaitBudgetClocks) {
+            *abort_flag = 1;
+            if (status_word) atomicCAS(status_word, 0, where);
+            return false;
         }
     }
     return true;
@@ -125,6 +140,24 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
           "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
         : "r"(taddr)
         : "memory");
+}
+// ---- thread-block cluster: barrier and distributed shared memory ------------------------------------------------
+__device__ __forceinline__ void cluster_arrive_release() { asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory"); }
+__device__ __forceinline__ void cluster_wait_acquire() { asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory"); }
+__device__ __forceinline__ uint32_t mapa_shared(uint32_t addr, uint32_t cta_rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(cta_rank));
+    return r;
+}
+__device__ __forceinline__ int4 ld_dsmem_v4(uint32_t addr) {
+    int4 v;
+    asm volatile("ld.shared::cluster.v4.s32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr) : "memory");
+    return v;
+}
+__device__ __forceinline__ int ld_dsmem_s32(uint32_t addr) {
+    int v;
+    asm volatile("ld.shared::cluster.s32 %0, [%1];" : "=r"(v) : "r"(addr) : "memory");
+    return v;
 }
 __device__ __forceinline__ void named_bar_sync(int id, int nthreads) {
     asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");

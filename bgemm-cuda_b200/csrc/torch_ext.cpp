@@ -1,0 +1,233 @@
+// Python module `lowbit_kernel`: the reference's extension surface (lowbit_kernel/csrc/pybind.cpp:7-13)
+// as a thin torch wrapper over the C ABI of libbgemm_b200.so. Tensors in, tensors out; every
+// computation is one or more calls declared in include/bgemm_b200.h on torch's current stream.
+#include <c10/cuda/CUDAGuard.h>
+#include <c10/cuda/CUDAStream.h>
+#include <torch/extension.h>
+
+#include <mutex>
+#include <unordered_map>
+
+#include "../../include/bgemm_b200.h"
+
+namespace {
+
+void check(int status, const char* where) {
+    TORCH_CHECK(status == 0, where, ": status ", status, ": ", bgemm_status_string(status));
+}
+
+int dtype_code(const torch::Tensor& t) {
+    switch (t.scalar_type()) {
+        case at::kHalf: return BGEMM_DT_F16;
+        case at::kBFloat16: return BGEMM_DT_BF16;
+        case at::kFloat: return BGEMM_DT_F32;
+        case at::kChar: return BGEMM_DT_I8;
+        default: TORCH_CHECK(false, "unsupported dtype ", t.scalar_type(), ": use float16, bfloat16, float32 or int8");
+    }
+}
+
+void* stream_of(const torch::Tensor& t) { return c10::cuda::getCurrentCUDAStream(t.get_device()).stream(); }
+
+// Per-device scratch, zero-initialised when (re)allocated; the library keeps its counter prefix zero.
+torch::Tensor workspace(const torch::Device& dev, size_t bytes) {
+    static std::mutex mu;
+    static std::unordered_map<int, torch::Tensor> cache;
+    std::lock_guard<std::mutex> lock(mu);
+    auto it = cache.find(dev.index());
+    if (it == cache.end() || (size_t)it->second.numel() < bytes) {
+        const int64_t n = (int64_t)std::max<size_t>(bytes, (size_t)1 << 20);
+        cache[dev.index()] = torch::zeros({n}, torch::TensorOptions().dtype(torch::kUInt8).device(dev));
+        it = cache.find(dev.index());
+    }
+    return it->second;
+}
+
+int act_mode_of(int op) { return op == BGEMM_OP_AND ? BGEMM_ACT_NEG01 : (op == BGEMM_OP_BWTA ? BGEMM_ACT_TERNARY : BGEMM_ACT_SIGN); }
+
+// reference: bgemm_linear_forward_cuda(in_feats[N,K] half, weights[M,K] half, splitK=1, INSTR=1) -> [N,M] half
+// (lowbit_kernel/csrc/fp6_linear.cu:561-616). Differences: any M, N, K; runs on the current stream; splitK <= 1
+// lets the library pick the K partitioning (results do not depend on it); non-contiguous inputs are made
+// contiguous instead of being read as if they were.
+torch::Tensor bgemm_linear_forward_cuda(torch::Tensor in_feats, torch::Tensor weights, int64_t splitK, int64_t INSTR) {
+    TORCH_CHECK(in_feats.is_cuda() && weights.is_cuda(), "bgemm_linear_forward_cuda: CUDA tensors required (no CPU path)");
+    TORCH_CHECK(in_feats.dim() == 2 && weights.dim() == 2, "bgemm_linear_forward_cuda: 2-D tensors required");
+    TORCH_CHECK(in_feats.size(1) == weights.size(1), "bgemm_linear_forward_cuda: K mismatch");
+    TORCH_CHECK(INSTR >= 0 && INSTR <= 3, "bgemm_linear_forward_cuda: INSTR must be 0 (and), 1 (xor), 2 (attn) or 3 (bwta)");
+    c10::cuda::CUDAGuard guard(in_feats.device());
+    auto x = in_feats.to(at::kHalf).contiguous();
+    auto w = weights.to(at::kHalf).contiguous();
+    const int64_t N = x.size(0), K = x.size(1), M = w.size(0);
+    auto out = torch::empty({N, M}, x.options());
+    const int sk = splitK <= 1 ? 0 : (int)splitK;
+    const size_t need = bgemm_linear_workspace_bytes(M, N, K, sk);
+    auto ws = workspace(x.device(), need);
+    check(bgemm_linear_forward(stream_of(x), w.data_ptr(), x.data_ptr(), out.data_ptr(), M, N, K, (int)INSTR, BGEMM_OUT_F16,
+                               BGEMM_LAYOUT_NM, nullptr, sk, ws.data_ptr(), (size_t)ws.numel()),
+          "bgemm_linear_forward");
+    return out;
+}
+
+// The reference's GPU prepack entry (fp6_linear.cu:519-542) returned an uninitialised tensor; this one
+// packs. Returns the tiled 1-bit plane as a uint8 tensor. wbit_mode: 0 bit = sign bit, 1 bit = !sign bit
+// (ATTN mask slot), 2 bit = (w != 0), 3 bit = (w < 0) with -0.0 -> 0 (planes of a ternary matrix).
+torch::Tensor binary_weight_prepacking_cuda(torch::Tensor w, int64_t wbit_mode) {
+    TORCH_CHECK(w.is_cuda() && (w.dim() == 2 || w.dim() == 3), "binary_weight_prepacking_cuda: 2-D or 3-D CUDA tensor required");
+    c10::cuda::CUDAGuard guard(w.device());
+    if (w.stride(-1) != 1) w = w.contiguous();
+    const bool batched = w.dim() == 3;
+    const int64_t B = batched ? w.size(0) : 1, M = w.size(-2), K = w.size(-1);
+    auto plane = torch::empty({(int64_t)(B * bgemm_plane_bytes(M, K))}, torch::TensorOptions().dtype(torch::kUInt8).device(w.device()));
+    check(bgemm_pack_weights(stream_of(w), w.data_ptr(), dtype_code(w), M, K, w.stride(-2), (int)wbit_mode, plane.data_ptr(), nullptr,
+                             nullptr, B, batched ? w.stride(0) : 0),
+          "bgemm_pack_weights");
+    return plane;
+}
+
+// Same plus the per-row scale alpha[m] = mean |w[m,:]| (fp16) and the per-row bit count.
+std::vector<torch::Tensor> binary_weight_prepacking_scaled_cuda(torch::Tensor w) {
+    TORCH_CHECK(w.is_cuda() && w.dim() == 2, "binary_weight_prepacking_scaled_cuda: 2-D CUDA tensor required");
+    c10::cuda::CUDAGuard guard(w.device());
+    if (w.stride(-1) != 1) w = w.contiguous();
+    const int64_t M = w.size(0), K = w.size(1);
+    auto plane = torch::empty({(int64_t)bgemm_plane_bytes(M, K)}, torch::TensorOptions().dtype(torch::kUInt8).device(w.device()));
+    auto alpha = torch::empty({M}, torch::TensorOptions().dtype(at::kHalf).device(w.device()));
+    auto rowpop = torch::empty({M}, torch::TensorOptions().dtype(at::kInt).device(w.device()));
+    check(bgemm_pack_weights(stream_of(w), w.data_ptr(), dtype_code(w), M, K, w.stride(0), 0, plane.data_ptr(), rowpop.data_ptr<int>(),
+                             alpha.data_ptr(), 1, 0),
+          "bgemm_pack_weights");
+    return {plane, alpha, rowpop};
+}
+
+// `weight_prepacking_cpu` keeps the reference's export name (pybind.cpp:10); its FP6 meaning is out of
+// scope, so it is the binary prepack on the CPU: [OC, IC] CPU tensor -> tiled plane (uint8, CPU).
+torch::Tensor weight_prepacking_cpu(torch::Tensor w) {
+    TORCH_CHECK(!w.is_cuda() && w.dim() == 2, "weight_prepacking_cpu: 2-D CPU tensor required");
+    w = w.contiguous();
+    const int64_t M = w.size(0), K = w.size(1);
+    auto plane = torch::empty({(int64_t)bgemm_plane_bytes(M, K)}, torch::TensorOptions().dtype(torch::kUInt8));
+    check(bgemm_pack_weights_host(w.data_ptr(), dtype_code(w), M, K, K, 0, plane.data_ptr(), nullptr, nullptr), "bgemm_pack_weights_host");
+    return plane;
+}
+
+// The reference's row-major format (binary_matrix_prepacking_cpu, fp6_linear.cu:463-485): int32 [rows, K/32],
+// element k at bit 31 - k % 32. Works on CPU and CUDA tensors.
+torch::Tensor binary_matrix_prepacking(torch::Tensor w) {
+    TORCH_CHECK(w.dim() == 2 && w.size(1) % 32 == 0, "binary_matrix_prepacking: [rows, K] with K % 32 == 0 required");
+    w = w.contiguous();
+    const int64_t rows = w.size(0), K = w.size(1);
+    auto out = torch::empty({rows, K / 32}, torch::TensorOptions().dtype(at::kInt).device(w.device()));
+    if (w.is_cuda()) {
+        c10::cuda::CUDAGuard guard(w.device());
+        check(bgemm_pack_rowmajor_msb(stream_of(w), w.data_ptr(), dtype_code(w), rows, K, K, reinterpret_cast<uint32_t*>(out.data_ptr<int>())),
+              "bgemm_pack_rowmajor_msb");
+    } else {
+        check(bgemm_pack_rowmajor_msb_host(w.data_ptr(), dtype_code(w), rows, K, K, reinterpret_cast<uint32_t*>(out.data_ptr<int>())),
+              "bgemm_pack_rowmajor_msb_host");
+    }
+    return out;
+}
+
+// Activation prepare: [N, K] (or [B, N, K]; with transpose the matrices are [K, N]) -> (int8 rows, colsum).
+std::vector<torch::Tensor> prepare_acts(torch::Tensor x, int64_t act_mode, bool transpose) {
+    TORCH_CHECK(x.is_cuda() && (x.dim() == 2 || x.dim() == 3), "prepare_acts: 2-D or 3-D CUDA tensor required");
+    c10::cuda::CUDAGuard guard(x.device());
+    if (x.stride(-1) != 1) x = x.contiguous();
+    const bool batched = x.dim() == 3;
+    const int64_t B = batched ? x.size(0) : 1;
+    const int64_t N = transpose ? x.size(-1) : x.size(-2), K = transpose ? x.size(-2) : x.size(-1);
+    std::vector<int64_t> ashape = batched ? std::vector<int64_t>{B, N, bgemm_act_ld(K)} : std::vector<int64_t>{N, bgemm_act_ld(K)};
+    std::vector<int64_t> cshape = batched ? std::vector<int64_t>{B, N} : std::vector<int64_t>{N};
+    auto acts = torch::empty(ashape, torch::TensorOptions().dtype(at::kChar).device(x.device()));
+    auto colsum = torch::empty(cshape, torch::TensorOptions().dtype(at::kInt).device(x.device()));
+    check(bgemm_prepare_acts(stream_of(x), x.data_ptr(), dtype_code(x), N, K, x.stride(-2), (int)act_mode, transpose ? 1 : 0,
+                             acts.data_ptr<int8_t>(), colsum.data_ptr<int>(), B, batched ? x.stride(0) : 0),
+          "bgemm_prepare_acts");
+    return {acts, colsum};
+}
+
+// GEMM on prepared operands (see bgemm_gemm). out_kind: 0 int32, 1 fp16, 2 fp16 scaled by alpha[m].
+torch::Tensor gemm_prepared(torch::Tensor plane, int64_t M, int64_t K, torch::Tensor acts, torch::Tensor colsum, int64_t op,
+                            int64_t out_kind, int64_t out_layout, c10::optional<torch::Tensor> alpha, int64_t splitK) {
+    TORCH_CHECK(plane.is_cuda() && acts.is_cuda() && colsum.is_cuda(), "gemm_prepared: CUDA tensors required");
+    TORCH_CHECK(acts.is_contiguous() && colsum.is_contiguous() && plane.is_contiguous(), "gemm_prepared: contiguous tensors required");
+    TORCH_CHECK(acts.scalar_type() == at::kChar && colsum.scalar_type() == at::kInt, "gemm_prepared: acts int8 / colsum int32 required");
+    TORCH_CHECK(acts.size(-1) == bgemm_act_ld(K), "gemm_prepared: activation row pitch must be bgemm_act_ld(K)");
+    c10::cuda::CUDAGuard guard(acts.device());
+    const bool batched = acts.dim() == 3;
+    const int64_t B = batched ? acts.size(0) : 1, N = acts.size(-2);
+    TORCH_CHECK((size_t)plane.numel() >= (size_t)B * bgemm_plane_bytes(M, K), "gemm_prepared: plane too small for M, K");
+    std::vector<int64_t> shape = out_layout == BGEMM_LAYOUT_NM ? std::vector<int64_t>{N, M} : std::vector<int64_t>{M, N};
+    if (batched) shape.insert(shape.begin(), B);
+    auto out = torch::empty(shape, torch::TensorOptions().dtype(out_kind == BGEMM_OUT_I32 ? at::kInt : at::kHalf).device(acts.device()));
+    const void* alpha_ptr = nullptr;
+    torch::Tensor a;
+    if (alpha.has_value()) {
+        a = alpha->to(at::kHalf).contiguous();
+        TORCH_CHECK(a.is_cuda() && a.numel() == B * M, "gemm_prepared: alpha must hold M values per batch on the GPU");
+        alpha_ptr = a.data_ptr();
+    }
+    const size_t need = bgemm_gemm_workspace_bytes(M, N, K, (int)splitK, B);
+    torch::Tensor ws;
+    if (need) ws = workspace(acts.device(), need);
+    check(bgemm_gemm(stream_of(acts), plane.data_ptr(), M, K, acts.data_ptr<int8_t>(), colsum.data_ptr<int>(), N, (int)op, out.data_ptr(),
+                     (int)out_kind, (int)out_layout, alpha_ptr, (int)splitK, need ? ws.data_ptr() : nullptr, need ? (size_t)ws.numel() : 0, B),
+          "bgemm_gemm");
+    return out;
+}
+
+// x [N, K] unpacked x prepacked weights -> [N, M]. INSTR as in the reference; out_kind 1 = fp16, 0 = int32,
+// 2 = fp16 scaled by alpha (required then).
+torch::Tensor bgemm_linear_forward_packed(torch::Tensor x, torch::Tensor plane, int64_t M, int64_t K, c10::optional<torch::Tensor> alpha,
+                                          int64_t splitK, int64_t INSTR, int64_t out_kind) {
+    TORCH_CHECK(x.dim() == 2 && x.size(1) == K, "bgemm_linear_forward_packed: x must be [N, K]");
+    auto prep = prepare_acts(x, act_mode_of((int)INSTR), false);
+    return gemm_prepared(plane, M, K, prep[0], prep[1], INSTR, out_kind, BGEMM_LAYOUT_NM, alpha, splitK);
+}
+
+// Binary weight x ternary activation with the per-channel scale fused: fp16 [N, M] = sign(x) . sign(w)^T * alpha.
+torch::Tensor bwta_linear_forward_cuda(torch::Tensor x, torch::Tensor plane, int64_t M, int64_t K, torch::Tensor alpha, int64_t splitK) {
+    return bgemm_linear_forward_packed(x, plane, M, K, alpha, splitK, BGEMM_OP_BWTA, BGEMM_OUT_F16_SCALED);
+}
+
+// Batched {0,1} x {-1,+1} attention product: attn [B, Sq, Sk] ("1" = sign bit clear, as the reference
+// encodes it), value [B, Sk, d] -> [B, Sq, d]; int32 when exact is true, else fp16 like the reference op.
+torch::Tensor bgemm_attn_matmul_batched(torch::Tensor attn, torch::Tensor value, bool exact) {
+    TORCH_CHECK(attn.is_cuda() && value.is_cuda() && attn.dim() == 3 && value.dim() == 3, "bgemm_attn_matmul_batched: 3-D CUDA tensors required");
+    TORCH_CHECK(attn.size(0) == value.size(0) && attn.size(2) == value.size(1), "bgemm_attn_matmul_batched: shape mismatch");
+    const int64_t Sq = attn.size(1), Sk = attn.size(2);
+    auto plane = binary_weight_prepacking_cuda(attn, BGEMM_WBIT_NONNEGATIVE);
+    auto prep = prepare_acts(value, BGEMM_ACT_SIGN, true);
+    return gemm_prepared(plane, Sq, Sk, prep[0], prep[1], BGEMM_OP_ATTN, exact ? BGEMM_OUT_I32 : BGEMM_OUT_F16, BGEMM_LAYOUT_MN, c10::nullopt, 0);
+}
+
+torch::Tensor fp6_not_provided(py::args, py::kwargs) {
+    throw py::type_error("the FP6 entry points of the reference (linear_forward_cuda, weight_dequant_cpu) are not part of this library");
+}
+
+}  // namespace
+
+PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
+    m.def("bgemm_linear_forward_cuda", &bgemm_linear_forward_cuda, "Computes BGEMM.", py::arg("in_feats"), py::arg("weights"),
+          py::arg("splitK") = 1, py::arg("INSTR") = 1);
+    m.def("weight_prepacking_cpu", &weight_prepacking_cpu, "Binary weight prepacking on the CPU (tiled 1-bit plane).");
+    m.def("binary_weight_prepacking_cuda", &binary_weight_prepacking_cuda, "Binary weight prepacking on the GPU.", py::arg("w"),
+          py::arg("wbit_mode") = 0);
+    m.def("binary_weight_prepacking_scaled_cuda", &binary_weight_prepacking_scaled_cuda, "Prepack + per-row mean-abs scale + bit count.");
+    m.def("binary_matrix_prepacking", &binary_matrix_prepacking, "Row-major MSB-first prepack (the reference's packed format).");
+    m.def("prepare_acts", &prepare_acts, "Activations -> int8 rows + column sums.", py::arg("x"), py::arg("act_mode"),
+          py::arg("transpose") = false);
+    m.def("gemm_prepared", &gemm_prepared, "GEMM on prepared operands.", py::arg("plane"), py::arg("M"), py::arg("K"), py::arg("acts"),
+          py::arg("colsum"), py::arg("op"), py::arg("out_kind") = 0, py::arg("out_layout") = 0, py::arg("alpha") = py::none(),
+          py::arg("splitK") = 0);
+    m.def("bgemm_linear_forward_packed", &bgemm_linear_forward_packed, "x x prepacked weights.", py::arg("x"), py::arg("plane"), py::arg("M"),
+          py::arg("K"), py::arg("alpha") = py::none(), py::arg("splitK") = 0, py::arg("INSTR") = 1, py::arg("out_kind") = 1);
+    m.def("bwta_linear_forward_cuda", &bwta_linear_forward_cuda, "Binary weight x ternary activation, scaled.", py::arg("x"), py::arg("plane"),
+          py::arg("M"), py::arg("K"), py::arg("alpha"), py::arg("splitK") = 0);
+    m.def("bgemm_attn_matmul_batched", &bgemm_attn_matmul_batched, "Batched {0,1} x {-1,+1} matmul.", py::arg("attn"), py::arg("value"),
+          py::arg("exact") = false);
+    m.def("linear_forward_cuda", &fp6_not_provided, "FP6 GEMM of the reference: not provided.");
+    m.def("weight_dequant_cpu", &fp6_not_provided, "FP6 dequant of the reference: not provided.");
+    m.def("plane_bytes", [](int64_t M, int64_t K) { return (int64_t)bgemm_plane_bytes(M, K); });
+    m.def("act_ld", [](int64_t K) { return bgemm_act_ld(K); });
+    m.def("launch_count", []() { return (uint64_t)bgemm_launch_count(); });
+}

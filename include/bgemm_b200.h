@@ -59,6 +59,8 @@ extern "C" {
 /* ---- how a weight-slot row is turned into a bit (bgemm_pack_weights mode) ----------------------- */
 #define BGEMM_WBIT_NEGATIVE     0   /* bit = sign bit            (ops AND, XOR, BWTA)                   */
 #define BGEMM_WBIT_NONNEGATIVE  1   /* bit = !sign bit           (op ATTN: 1 where the mask is "1")     */
+#define BGEMM_WBIT_NONZERO      2   /* bit = (w != 0)            (mask plane of a ternary matrix)       */
+#define BGEMM_WBIT_NEGATIVE_NZ  3   /* bit = (w < 0), -0.0 -> 0  (sign plane of a ternary matrix)       */
 
 /* ---- how an activation-slot element is turned into an int8 (bgemm_prepare_acts mode) ------------ */
 #define BGEMM_ACT_SIGN      0   /* -1 if sign bit else +1          (ops XOR, ATTN)                     */
@@ -132,10 +134,12 @@ int bgemm_prepare_acts(void* stream, const void* src, int src_dtype, int64_t N, 
  *   acts      int8 [N, bgemm_act_ld(K)] and colsum int32 [N] (bgemm_prepare_acts with the mode of `op`)
  *   out       BGEMM_LAYOUT_NM: [N, M]; BGEMM_LAYOUT_MN: [M, N]; element type per out_kind
  *   alpha     fp16 [M], required for BGEMM_OUT_F16_SCALED, else may be NULL
- *   split_k   >= 1 forces that many K partitions, 0 lets the library choose
- *   workspace needed when the chosen split_k > 1: bgemm_gemm_workspace_bytes() bytes, 256-byte aligned.
+ *   split_k   >= 1 forces that many K partitions, 0 lets the library choose (at most 8). Up to 8 partitions
+ *             are reduced on chip (thread-block cluster + distributed shared memory) and need no workspace.
+ *   workspace needed only when split_k > 8: bgemm_gemm_workspace_bytes() bytes, 256-byte aligned.
  *             Zero it once after allocating it; the library restores the part that must be zero
- *             (arrival counters at its start) before each call returns.
+ *             (arrival counters in its first 64 KiB) before each call returns, so one buffer can serve
+ *             calls of any shapes one after another on a stream.
  *   batch     number of independent problems (A x V heads); problem i uses plane + i*plane_bytes,
  *             acts + i*N*act_ld, colsum + i*N, out + i*M*N elements, alpha + i*M.
  * Replaces bin_pack_linear_kernel + PACK_BGEMM_Kernel + SplitK_Reduction (see file header).           */
@@ -163,6 +167,13 @@ const char* bgemm_status_string(int status);
 int bgemm_version(void);
 /* Number of kernels this library has launched in this process (for launch accounting in benchmarks). */
 uint64_t bgemm_launch_count(void);
+
+/* Every wait inside the kernels is time-bounded (about one second). A wait that runs out makes its kernel
+ * drain and exit normally and records a small positive code in a per-device status word; the results of
+ * that launch are then undefined. This call synchronises with the device, returns the word (0 = no wait
+ * ever ran out) and clears it when `reset` is non-zero. The reference has no counterpart: its kernels
+ * have no inter-thread waits beyond __syncthreads (kernel_matmul.cuh:458-459,507-508).                   */
+int bgemm_device_status(int reset);
 
 #ifdef __cplusplus
 }

@@ -244,11 +244,10 @@ def np_tiled_plane(bits: np.ndarray) -> np.ndarray:
 
 def np_pack_weights(w, wbit_mode: int):
     """(plane uint8, rowpop int32[M]) from unpacked weights."""
-    if isinstance(w, torch.Tensor):
-        s = torch.signbit(w.detach().cpu()).numpy()
-    else:
-        s = np.signbit(np.asarray(w))
-    bits = s if wbit_mode == 0 else ~s
+    wt = w.detach().cpu() if isinstance(w, torch.Tensor) else torch.as_tensor(np.asarray(w))
+    s = torch.signbit(wt).numpy()
+    nz = (wt != 0).numpy()
+    bits = {0: s, 1: ~s, 2: nz, 3: s & nz}[wbit_mode]
     return np_tiled_plane(bits), bits.sum(axis=1).astype(np.int32)
 
 

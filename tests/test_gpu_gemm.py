@@ -132,7 +132,7 @@ def test_gemm_all_tile_widths(B, op, N):
 
 @pytest.mark.parametrize("M,K", [(128, 256), (130, 384), (10, 4096), (257, 1000), (640, 129), (1, 1), (300, 8192)])
 @pytest.mark.parametrize("N", [3, 24, 64, 130])
-@pytest.mark.parametrize("split_k", [1, 0, 3])
+@pytest.mark.parametrize("split_k", [1, 0, 3, 8, 12])
 def test_gemm_ragged_shapes_and_split_k(B, M, K, N, split_k):
     g = O._gen(M + K + N)
     for op in (O.OP_XOR, O.OP_BWTA):
@@ -166,7 +166,7 @@ def test_gemm_known_answers(B):
 
 
 @pytest.mark.parametrize("layout", [0, 1])
-@pytest.mark.parametrize("split_k", [1, 4])
+@pytest.mark.parametrize("split_k", [1, 4, 5, 8])
 def test_output_kinds(B, layout, split_k):
     cfg = O.config2(M=384, K=2048, N=40)
     w, x, alpha = cfg["w"], cfg["x"], cfg["alpha"]
@@ -213,6 +213,16 @@ def test_linear_forward_dropin(B, op, M, N, K):
             assert np.array_equal(bits, got32.numpy())
 
 
+def test_shared_workspace_survives_calls_of_different_shapes(B):
+    """One scratch buffer serves calls whose layouts differ; the arrival counters must stay usable."""
+    g = O._gen(91)
+    for (M, N, K, sk) in [(256, 32, 8192, 16), (1024, 200, 4096, 12), (128, 16, 8192, 32), (256, 32, 8192, 16), (640, 64, 2560, 9)]:
+        w, x = _rand_w(M, K, g, "randn"), _acts_for(O.OP_BWTA, N, K, g)
+        assert torch.equal(_run(B, w, x, O.OP_BWTA, split_k=sk), O.ref_acc(w, x, O.OP_BWTA)), (M, N, K, sk)
+        got = B.linear_forward(w.cuda(), x.cuda(), O.OP_BWTA, out_kind=B.OUT_I32, split_k=sk).cpu()
+        assert torch.equal(got, O.ref_acc(w, x, O.OP_BWTA)), (M, N, K, sk)
+
+
 def test_batched_attention_heads(B):
     cfg = O.config3(heads=6, S=256, d=64)
     a, v = cfg["attn"], cfg["v"]
@@ -232,7 +242,7 @@ def test_argument_errors(B):
     assert B.lib.bgemm_pack_weights(None, x.data_ptr(), 0, 0, 256, 256, 0, x.data_ptr(), None, None, 1, 0) == -2
     assert B.lib.bgemm_gemm(None, x.data_ptr(), 4, 256, x.data_ptr(), x.data_ptr(), 4, 1, x.data_ptr(), 2, 0, None, 1, None, 0, 1) == -1
     # split-K without a workspace is refused before anything is launched
-    assert B.lib.bgemm_gemm(None, x.data_ptr(), 4, 1024, x.data_ptr(), x.data_ptr(), 4, 1, x.data_ptr(), 0, 0, None, 2, None, 0, 1) == -5
+    assert B.lib.bgemm_gemm(None, x.data_ptr(), 4, 8192, x.data_ptr(), x.data_ptr(), 4, 1, x.data_ptr(), 0, 0, None, 16, None, 0, 1) == -5
     assert b"workspace" in B.lib.bgemm_status_string(-5)
     with pytest.raises(ValueError):
         B.pack_weights(torch.zeros(4, 256, dtype=torch.float16))
