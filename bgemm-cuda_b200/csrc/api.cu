@@ -1,6 +1,7 @@
 // extern "C" surface of libbgemm_b200.so: argument validation, workspace carving, launch order.
 // Declared and documented in include/bgemm_b200.h.
 #include <atomic>
+#include <cstdlib>
 
 #include "internal.h"
 
@@ -8,6 +9,14 @@ namespace bgemm {
 
 static std::atomic<uint64_t> g_launches{0};
 void count_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
+
+bool programmatic_launch_enabled() {
+    static const bool on = [] {
+        const char* e = std::getenv("BGEMM_PDL");
+        return !(e && e[0] == '0');
+    }();
+    return on;
+}
 
 static long long* g_prof = nullptr;
 long long* debug_profile_buffer() { return g_prof; }
@@ -50,8 +59,8 @@ static int resolve_split_k(long long M, long long N, long long K, long long batc
         if (split_k > kMaxClusterSplit && tiles > kMaxCounterTiles) split_k = kMaxClusterSplit;
         return (int)(split_k > kblocks ? kblocks : split_k);
     }
-    // auto: aim at ~2 CTAs per SM worth of tiles, keep at least 2 K blocks per partition
-    const long long target = 148LL * (NT <= 128 ? 2 : 1);
+    // auto: fill the SMs once (one deep-pipeline CTA per SM measured best), keep at least 2 K blocks per partition
+    const long long target = 148LL;
     long long s = target / (tiles > 0 ? tiles : 1);
     if (s < 1) s = 1;
     if (s > kblocks / 2) s = kblocks / 2;

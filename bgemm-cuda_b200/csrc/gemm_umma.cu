@@ -41,18 +41,30 @@ __host__ __device__ constexpr int pow2_ceil(int v) {
     return p;
 }
 
-template <int NT, bool POW2>
+// DEEP: the CTA takes all 512 tensor-memory columns (one CTA per SM, six K blocks of operand in flight) -- best
+// when the launch has at most one CTA per SM. Otherwise 256 columns, two CTAs per SM covering each other's bubbles.
+template <int NT, bool POW2, bool DEEP>
 struct Cfg {
     static constexpr int D_COLS = POW2 ? 8 * NT : NT;
-    static constexpr int A_STAGES = POW2 ? (NT == 16 ? 2 : 4) : (NT <= 128 ? 2 : 4);
+    static constexpr int TMEM_BUDGET = (DEEP || D_COLS >= 256) ? 512 : 256;
+    // An A stage holds G-th of a K block: 8 / G operand slices of 8 columns each. The unpack -> UMMA -> release
+    // round trip of a stage costs ~1500 clocks of signalling latency, so the ring must hold several K blocks of
+    // operand for the tensor pipe to stay busy: it takes everything D leaves of the 512 columns.
+    static constexpr int G = 1;
+    static constexpr int A_STAGE_COLS = 64 / G;
+    static constexpr int A_FIT = ((TMEM_BUDGET - D_COLS) / A_STAGE_COLS) / (2 * G) * (2 * G);
+    static constexpr int A_STAGES = A_FIT > 6 * G ? 6 * G : A_FIT;
     static constexpr int A_COL0 = D_COLS;
-    static constexpr int TMEM_COLS = pow2_ceil(D_COLS + 64 * A_STAGES);
+    static constexpr int TMEM_COLS = pow2_ceil(D_COLS + A_STAGE_COLS * A_STAGES);
     static constexpr int B_STAGE_BYTES = NT * 256;
-    static constexpr int B_STAGES = NT <= 32 ? 6 : 3;
-    static constexpr int W_STAGES = NT <= 64 ? 8 : (NT == 128 ? 2 : 4);
+    static constexpr bool ONE_PER_SM = TMEM_BUDGET == 512;
+    static constexpr int B_STAGES = NT <= 32 ? 8 : (NT == 64 ? (ONE_PER_SM ? 6 : 4) : (NT == 128 ? (ONE_PER_SM ? 4 : 3) : 3));
+    static constexpr int W_STAGES = NT == 256 ? 4 : ((NT == 128 && !ONE_PER_SM) ? 2 : 8);
     static constexpr int NBARS = 2 * W_STAGES + 2 * B_STAGES + 2 * A_STAGES + 1;
     static constexpr int MISC_BYTES = 512 /*barriers*/ + 512 /*alpha*/ + 1024 /*colsum*/ + 512 /*flags*/;
-    static constexpr int STAGE_TILE_BYTES = NT * 128 * 4;   // epilogue staging, aliases the activation stages
+    // Epilogue staging aliases the activation and weight stages: one [NT][128] int32 tile, or -- K partitions in a
+    // cluster -- up to (NT + 7 * 8) columns of partial sums received from the peers.
+    static constexpr int STAGE_TILE_BYTES = (NT + 56) * 128 * 4;
     static constexpr int SMEM_USED = B_STAGES * B_STAGE_BYTES + W_STAGES * 4096 + MISC_BYTES + 1024 /*align*/;
     // Co-resident CTAs must not ask for more tensor memory than the SM has (a later tcgen05.alloc would
     // stall until an earlier CTA exits): request enough shared memory to cap residency at 512 / TMEM_COLS.
@@ -62,19 +74,31 @@ struct Cfg {
     // The two unpack sets take alternate K blocks. With even stage counts a stage (and its barriers) is always
     // served by the same set, so every waiter has seen the previous phase of the barrier it waits on; with an
     // odd count a set's first wait on a barrier would name phase 1 and pass before phase 0 has completed.
-    static_assert(W_STAGES % 2 == 0 && A_STAGES % 2 == 0, "stage counts shared by the two unpack sets must be even");
+    static_assert(W_STAGES % 2 == 0 && A_STAGES % (2 * G) == 0, "stage counts shared by the two unpack sets must keep stage -> set fixed");
     static_assert(TMEM_COLS <= 512, "tensor memory budget");
     static_assert(NT % 16 == 0 && NT >= 16 && NT <= 256, "UMMA N");
     static_assert(NBARS * 8 <= 512, "barrier area");
-    static_assert(STAGE_TILE_BYTES <= B_STAGES * B_STAGE_BYTES, "staging tile must fit in the activation stages");
+    static_assert(STAGE_TILE_BYTES <= B_STAGES * B_STAGE_BYTES + W_STAGES * 4096, "staging must fit in the operand stages");
     static_assert(SMEM_BYTES <= 227 * 1024, "shared memory budget");
 };
 
 // Optional phase stamps (SM clock, relative to CTA start) for tuning; p.prof is null in normal use.
 #define BGEMM_STAMP(slot)                                                                                            \
     do {                                                                                                             \
-        if (p.prof) p.prof[(size_t)((blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x) * 16 + (slot)] = \
-            (slot) >= 10 ? (long long)globaltimer_ns() : clock64() - t_cta0;                                         \
+        if (p.prof) p.prof[(size_t)((blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x) * 32 + (slot)] = \
+            ((slot) == 10 || (slot) == 11) ? (long long)globaltimer_ns() : clock64() - t_cta0;                                         \
+    } while (0)
+
+// Accumulate the clocks a role spends blocked in one kind of wait (tuning aid, only when p.prof is set).
+#define BGEMM_TIMED(acc_var, expr)                      \
+    do {                                                \
+        const long long tw0__ = p.prof ? clock64() : 0; \
+        expr;                                           \
+        if (p.prof) acc_var += clock64() - tw0__;       \
+    } while (0)
+#define BGEMM_PUT(slot, value)                                                                                                \
+    do {                                                                                                                      \
+        if (p.prof) p.prof[(size_t)((blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x) * 32 + (slot)] = (value); \
     } while (0)
 
 // ---- epilogue: converting and storing 8 results --------------------------------------------------------------
@@ -154,94 +178,67 @@ __device__ __forceinline__ void store8_cols(const TileOut& t, int m, int n0, con
     }
 }
 
-// Where the partial tiles of the K partitions are: 0 this CTA's shared memory only (one partition),
-// 1 every cluster peer's shared memory, 2 slabs in global memory.
-enum { kSrcLocal = 0, kSrcCluster = 1, kSrcGlobal = 2 };
-
-// Sum over the partitions of 8 consecutive rows (element offset `off` = n * 128 + m0 of the [NT][128] tile).
-template <int SRC, int NT>
-__device__ __forceinline__ void gather8_rows(const int* sP, const int* gbase, int parts, int off, int (&acc)[8]) {
-    if (SRC == kSrcLocal) {
-        const int4 a = *reinterpret_cast<const int4*>(sP + off), b = *reinterpret_cast<const int4*>(sP + off + 4);
-        acc[0] = a.x; acc[1] = a.y; acc[2] = a.z; acc[3] = a.w; acc[4] = b.x; acc[5] = b.y; acc[6] = b.z; acc[7] = b.w;
-        return;
-    }
+// Sum `parts` partial tiles (each `stride` ints apart, starting at `base`) over 8 consecutive rows at element
+// offset `off` of a [columns][128] int32 tile. GLOBAL: the tiles are slabs in global memory (L2 reads).
+template <bool GLOBAL>
+__device__ __forceinline__ void gather8_rows(const int* base, int parts, int stride, int off, int (&acc)[8]) {
 #pragma unroll
     for (int q = 0; q < 8; q++) acc[q] = 0;
-    if (SRC == kSrcCluster) {
-        const uint32_t mine = smem_u32(sP + off);
 #pragma unroll 4
-        for (int peer = 0; peer < parts; peer++) {
-            const uint32_t r = mapa_shared(mine, (uint32_t)peer);
-            const int4 a = ld_dsmem_v4(r), b = ld_dsmem_v4(r + 16);
-            acc[0] += a.x; acc[1] += a.y; acc[2] += a.z; acc[3] += a.w; acc[4] += b.x; acc[5] += b.y; acc[6] += b.z; acc[7] += b.w;
-        }
-    } else {
-#pragma unroll 4
-        for (int s = 0; s < parts; s++) {
-            const int4* g = reinterpret_cast<const int4*>(gbase + (size_t)s * (NT * 128) + off);
-            const int4 a = __ldcg(g), b = __ldcg(g + 1);
-            acc[0] += a.x; acc[1] += a.y; acc[2] += a.z; acc[3] += a.w; acc[4] += b.x; acc[5] += b.y; acc[6] += b.z; acc[7] += b.w;
-        }
+    for (int s = 0; s < parts; s++) {
+        const int4* g = reinterpret_cast<const int4*>(base + (size_t)s * stride + off);
+        const int4 a = GLOBAL ? __ldcg(g) : g[0];
+        const int4 b = GLOBAL ? __ldcg(g + 1) : g[1];
+        acc[0] += a.x; acc[1] += a.y; acc[2] += a.z; acc[3] += a.w; acc[4] += b.x; acc[5] += b.y; acc[6] += b.z; acc[7] += b.w;
     }
 }
 
-// Sum over the partitions of 8 consecutive columns n0..n0+7 of row m.
-template <int SRC, int NT>
-__device__ __forceinline__ void gather8_cols(const int* sP, const int* gbase, int parts, int n0, int m, int (&acc)[8]) {
+// The same over 8 consecutive columns c0..c0+7 of row m.
+template <bool GLOBAL>
+__device__ __forceinline__ void gather8_cols(const int* base, int parts, int stride, int c0, int m, int (&acc)[8]) {
 #pragma unroll
     for (int q = 0; q < 8; q++) acc[q] = 0;
-    if (SRC == kSrcLocal) {
-#pragma unroll
-        for (int q = 0; q < 8; q++) acc[q] = sP[(n0 + q) * 128 + m];
-    } else if (SRC == kSrcCluster) {
-        const uint32_t mine = smem_u32(sP + n0 * 128 + m);
 #pragma unroll 2
-        for (int peer = 0; peer < parts; peer++) {
-            const uint32_t r = mapa_shared(mine, (uint32_t)peer);
+    for (int s = 0; s < parts; s++) {
+        const int* g = base + (size_t)s * stride + c0 * 128 + m;
 #pragma unroll
-            for (int q = 0; q < 8; q++) acc[q] += ld_dsmem_s32(r + (uint32_t)(q * 128 * 4));
-        }
-    } else {
-#pragma unroll 2
-        for (int s = 0; s < parts; s++) {
-#pragma unroll
-            for (int q = 0; q < 8; q++) acc[q] += __ldcg(gbase + (size_t)s * (NT * 128) + (n0 + q) * 128 + m);
-        }
+        for (int q = 0; q < 8; q++) acc[q] += GLOBAL ? __ldcg(g + q * 128) : g[q * 128];
     }
 }
 
-// Convert and store columns [nbeg, nend) of the tile with all 256 epilogue threads.
-template <int SRC, int NT>
-__device__ __forceinline__ void write_tile(const TileOut& t, const int* sP, const int* gbase, int parts, int nbeg, int nend, int et) {
+// Convert and store `ncols` columns with all 256 epilogue threads. Column c of the partial tiles at `base` is
+// tile column n_first + c.
+template <bool GLOBAL>
+__device__ __forceinline__ void write_tile(const TileOut& t, const int* base, int parts, int stride, int n_first, int ncols, int et) {
     const GemmParams& p = *t.p;
     if (p.out_layout == BGEMM_LAYOUT_NM) {
-        const int units = (nend - nbeg) * 16;                   // (column, 8-row chunk)
+        const int units = ncols * 16;                           // (column, 8-row chunk)
 #pragma unroll 1
         for (int u = et; u < units; u += kUnpackThreads) {
-            const int n = nbeg + (u >> 4), m0 = (u & 15) * 8;
-            if (t.n_base + n >= p.N || t.m_base + m0 >= p.M) continue;
+            const int c = u >> 4, m0 = (u & 15) * 8;
+            if (t.n_base + n_first + c >= p.N || t.m_base + m0 >= p.M) continue;
             int acc[8];
-            gather8_rows<SRC, NT>(sP, gbase, parts, n * 128 + m0, acc);
-            store8_rows(t, n, m0, acc);
+            gather8_rows<GLOBAL>(base, parts, stride, c * 128 + m0, acc);
+            store8_rows(t, n_first + c, m0, acc);
         }
     } else {
-        const int units = ((nend - nbeg) >> 3) * 128;           // (8-column chunk, row)
+        const int units = (ncols >> 3) * 128;                   // (8-column chunk, row)
 #pragma unroll 1
         for (int u = et; u < units; u += kUnpackThreads) {
-            const int m = u & 127, n0 = nbeg + (u >> 7) * 8;
-            if (t.n_base + n0 >= p.N || t.m_base + m >= p.M) continue;
+            const int m = u & 127, c0 = (u >> 7) * 8;
+            if (t.n_base + n_first + c0 >= p.N || t.m_base + m >= p.M) continue;
             int acc[8];
-            gather8_cols<SRC, NT>(sP, gbase, parts, n0, m, acc);
-            store8_cols(t, m, n0, acc);
+            gather8_cols<GLOBAL>(base, parts, stride, c0, m, acc);
+            store8_cols(t, m, n_first + c0, acc);
         }
     }
 }
 
-template <int NT, bool POW2>
-__global__ void __launch_bounds__(kGemmThreads, Cfg<NT, POW2>::MIN_CTAS) gemm_kernel(const __grid_constant__ CUtensorMap tmap_acts, const GemmParams p) {
-    using C = Cfg<NT, POW2>;
+template <int NT, bool POW2, bool DEEP>
+__global__ void __launch_bounds__(kGemmThreads, Cfg<NT, POW2, DEEP>::MIN_CTAS) gemm_kernel(const __grid_constant__ CUtensorMap tmap_acts, const GemmParams p) {
+    using C = Cfg<NT, POW2, DEEP>;
     const long long t_cta0 = clock64();
+    grid_launch_dependents();
     if (threadIdx.x == 0) BGEMM_STAMP(10);
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -285,19 +282,13 @@ __global__ void __launch_bounds__(kGemmThreads, Cfg<NT, POW2>::MIN_CTAS) gemm_ke
         if (lane == 0) tma_prefetch_desc(&tmap_acts);
     } else if (warp == kWarpMma) {
         tmem_alloc(smem_u32(tmem_holder), C::TMEM_COLS);
-    } else if (warp >= 1 && warp <= 4) {
-        const int i = tid - 32;                                  // per-row scale of this tile
-        const int m = mt * 128 + i;
-        s_alpha[i] = (p.out_kind == BGEMM_OUT_F16_SCALED && m < p.M) ? __half2float(p.alpha[(size_t)batch * p.M + m]) : 1.f;
-    } else if (warp >= 5 && warp <= 7) {
-        for (int i = tid - 160; i < NT; i += 96) {               // column sums of this tile
-            const int n = nt * NT + i;
-            s_colsum[i] = (p.epi && n < p.N) ? __ldg(p.colsum + (size_t)batch * p.N + n) : 0;
-        }
     }
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
+    // Everything above touches no global memory, so under programmatic dependent launch it overlaps the tail of
+    // the previous kernel in the stream; from here on that kernel's results are needed.
+    grid_dependency_wait();
     const uint32_t tmem = *tmem_holder;
     const uint32_t tmem_d = tmem;
     const uint32_t tmem_a = tmem + C::A_COL0;
@@ -308,14 +299,18 @@ __global__ void __launch_bounds__(kGemmThreads, Cfg<NT, POW2>::MIN_CTAS) gemm_ke
         if (lane == 0) {
             const uint8_t* src = p.plane + (size_t)batch * p.plane_batch_bytes + ((size_t)mt * p.kblocks + kb0) * 4096;
             int issued = 0;
+            long long tw = 0;
             for (int i = 0; i < nkb; i++) {
                 const int s = i % C::W_STAGES;
-                if (i >= C::W_STAGES && !mbar_wait(w_empty + 8 * s, ((i / C::W_STAGES) - 1) & 1, abort_flag, p.status, 11)) break;
+                bool okw = true;
+                if (i >= C::W_STAGES) BGEMM_TIMED(tw, okw = mbar_wait(w_empty + 8 * s, ((i / C::W_STAGES) - 1) & 1, abort_flag, p.status, 11));
+                if (!okw) break;
                 mbar_arrive_expect_tx(w_full + 8 * s, 4096);
                 bulk_g2s(smem_u32(sW + s * 4096), src + (size_t)i * 4096, 4096, w_full + 8 * s);
                 if (i == 0) BGEMM_STAMP(2);
                 issued = i + 1;
             }
+            BGEMM_PUT(20, tw);
             if (*abort_flag) {  // drain own copies before the CTA may exit
                 for (int i = issued - 1; i >= 0 && i >= issued - C::W_STAGES; i--) {
                     const long long t0 = clock64();
@@ -327,15 +322,19 @@ __global__ void __launch_bounds__(kGemmThreads, Cfg<NT, POW2>::MIN_CTAS) gemm_ke
         // ---------------- activation producer ----------------
         if (lane == 0) {
             int issued = 0;
+            long long tw = 0;
             for (int i = 0; i < nkb; i++) {
                 const int s = i % C::B_STAGES;
-                if (i >= C::B_STAGES && !mbar_wait(b_empty + 8 * s, ((i / C::B_STAGES) - 1) & 1, abort_flag, p.status, 12)) break;
+                bool okb = true;
+                if (i >= C::B_STAGES) BGEMM_TIMED(tw, okb = mbar_wait(b_empty + 8 * s, ((i / C::B_STAGES) - 1) & 1, abort_flag, p.status, 12));
+                if (!okb) break;
                 mbar_arrive_expect_tx(b_full + 8 * s, C::B_STAGE_BYTES);
                 const uint32_t dst = smem_u32(sB + s * C::B_STAGE_BYTES);
                 tma_load_3d(dst, &tmap_acts, (kb0 + i) * 256, nt * NT, batch, b_full + 8 * s);
                 tma_load_3d(dst + NT * 128, &tmap_acts, (kb0 + i) * 256 + 128, nt * NT, batch, b_full + 8 * s);
                 issued = i + 1;
             }
+            BGEMM_PUT(21, tw);
             if (*abort_flag) {
                 for (int i = issued - 1; i >= 0 && i >= issued - C::B_STAGES; i--) {
                     const long long t0 = clock64();
@@ -348,36 +347,56 @@ __global__ void __launch_bounds__(kGemmThreads, Cfg<NT, POW2>::MIN_CTAS) gemm_ke
         if (lane == 0) {
             constexpr uint32_t idesc = umma_idesc_u8s8(NT);
             bool ok = true;
+            long long twa = 0, twb = 0;
+            const long long tloop0 = clock64();
             for (int i = 0; i < nkb && ok; i++) {
-                const int as = i % C::A_STAGES, bs = i % C::B_STAGES;
-                ok = mbar_wait(b_full + 8 * bs, (i / C::B_STAGES) & 1, abort_flag, p.status, 14) &&
-                     mbar_wait(a_full + 8 * as, (i / C::A_STAGES) & 1, abort_flag, p.status, 13);
-                if (!ok) break;
-                tc_fence_after();
-                if (i == 0) BGEMM_STAMP(5);
+                const int bs = i % C::B_STAGES;
+                BGEMM_TIMED(twb, ok = mbar_wait(b_full + 8 * bs, (i / C::B_STAGES) & 1, abort_flag, p.status, 14));
                 const uint32_t bbase = smem_u32(sB + bs * C::B_STAGE_BYTES);
 #pragma unroll
-                for (int j = 0; j < 8; j++) {
-                    const uint64_t bdesc = umma_desc_sw128(bbase + (j >> 2) * (NT * 128) + (j & 3) * 32);
-                    const uint32_t d = tmem_d + (POW2 ? j * NT : 0);
-                    const uint32_t acc = POW2 ? (i > 0 ? 1u : 0u) : ((i | j) ? 1u : 0u);
-                    umma_i8_ts(d, tmem_a + as * 64 + j * 8, bdesc, idesc, acc);
+                for (int g = 0; g < C::G && ok; g++) {
+                    const int h = C::G * i + g, as = h % C::A_STAGES;
+                    BGEMM_TIMED(twa, ok = mbar_wait(a_full + 8 * as, (h / C::A_STAGES) & 1, abort_flag, p.status, 13));
+                    if (!ok) break;
+                    tc_fence_after();
+                    if (h == 0) BGEMM_STAMP(5);
+#pragma unroll
+                    for (int jj = 0; jj < 8 / C::G; jj++) {
+                        const int j = (8 / C::G) * g + jj;
+                        const uint64_t bdesc = umma_desc_sw128(bbase + (j >> 2) * (NT * 128) + (j & 3) * 32);
+                        const uint32_t d = tmem_d + (POW2 ? j * NT : 0);
+                        const uint32_t acc = POW2 ? (i > 0 ? 1u : 0u) : ((i | j) ? 1u : 0u);
+                        umma_i8_ts(d, tmem_a + as * C::A_STAGE_COLS + jj * 8, bdesc, idesc, acc);
+                    }
+                    umma_commit(a_empty + 8 * as);
                 }
-                umma_commit(a_empty + 8 * as);
                 umma_commit(b_empty + 8 * bs);
             }
             umma_commit(d_full);
             BGEMM_STAMP(6);
+            BGEMM_PUT(16, twa); BGEMM_PUT(17, twb); BGEMM_PUT(24, clock64() - tloop0);
         }
     } else {
         // ---------------- unpack: set 0 = warps 0-3 takes even K blocks, set 1 = warps 4-7 odd ones ----------------
         const int set = warp >> 2;
         const int r = (warp & 3) * 32 + lane;                 // weight row of the tile == tensor-memory lane
         const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
+        // per-row scales and column sums of this tile (needed by the epilogue only; their latency hides behind
+        // the first weight load)
+        if (tid < 128) {
+            const int m = mt * 128 + tid;
+            s_alpha[tid] = (p.out_kind == BGEMM_OUT_F16_SCALED && m < p.M) ? __half2float(p.alpha[(size_t)batch * p.M + m]) : 1.f;
+        }
+        for (int i = tid; i < NT; i += kUnpackThreads) {
+            const int n = nt * NT + i;
+            s_colsum[i] = (p.epi && n < p.N) ? __ldg(p.colsum + (size_t)batch * p.N + n) : 0;
+        }
         bool ok = true;
+        long long tww = 0, twe = 0, tst = 0;
+        const long long tloop0 = clock64();
         for (int i = set; i < nkb && ok; i += 2) {
-            const int ws = i % C::W_STAGES, as = i % C::A_STAGES;
-            ok = mbar_wait(w_full + 8 * ws, (i / C::W_STAGES) & 1, abort_flag, p.status, 15);
+            const int ws = i % C::W_STAGES;
+            BGEMM_TIMED(tww, ok = mbar_wait(w_full + 8 * ws, (i / C::W_STAGES) & 1, abort_flag, p.status, 15));
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
             if (i == 0 && tid == 0) BGEMM_STAMP(3);
@@ -385,91 +404,113 @@ __global__ void __launch_bounds__(kGemmThreads, Cfg<NT, POW2>::MIN_CTAS) gemm_ke
             const uint4 hi = *reinterpret_cast<const uint4*>(sW + ws * 4096 + 2048 + r * 16);
             __syncwarp();
             if (lane == 0) mbar_arrive(w_empty + 8 * ws);
-            if (i >= C::A_STAGES) ok = mbar_wait(a_empty + 8 * as, ((i / C::A_STAGES) - 1) & 1, abort_flag, p.status, 16);
-            ok = __all_sync(0xffffffffu, ok);
-            if (!ok) break;
-            tc_fence_after();
             const uint32_t w[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
 #pragma unroll
-            for (int j = 0; j < 8; j++) {
-                uint32_t v[8];
+            for (int g = 0; g < C::G; g++) {
+                const int h = C::G * i + g, as = h % C::A_STAGES;
+                if (h >= C::A_STAGES) BGEMM_TIMED(twe, ok = mbar_wait(a_empty + 8 * as, ((h / C::A_STAGES) - 1) & 1, abort_flag, p.status, 16));
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) break;
+                tc_fence_after();
 #pragma unroll
-                for (int c = 0; c < 8; c++) v[c] = POW2 ? (w[c] & (0x01010101u << j)) : ((w[c] >> j) & 0x01010101u);
-                tmem_st8(tmem_a + lane_base + as * 64 + j * 8, v);
+                for (int jj = 0; jj < 8 / C::G; jj++) {
+                    const int j = (8 / C::G) * g + jj;
+                    uint32_t v[8];
+#pragma unroll
+                    for (int c = 0; c < 8; c++) v[c] = POW2 ? (w[c] & (0x01010101u << j)) : ((w[c] >> j) & 0x01010101u);
+                    tmem_st8(tmem_a + lane_base + as * C::A_STAGE_COLS + jj * 8, v);
+                }
+                BGEMM_TIMED(tst, tmem_wait_st());
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(a_full + 8 * as);
+                if (h == 0 && tid == 0) BGEMM_STAMP(4);
             }
-            tmem_wait_st();
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(a_full + 8 * as);
-            if (i == 0 && tid == 0) BGEMM_STAMP(4);
         }
+        if (tid == 0) { BGEMM_PUT(18, tww); BGEMM_PUT(19, twe); BGEMM_PUT(25, clock64() - tloop0); BGEMM_PUT(26, tst); }
+        if (tid == 128) { BGEMM_PUT(22, tww); BGEMM_PUT(23, twe); }
         ok = ok && mbar_wait(d_full, 0, abort_flag, p.status, 17);
         ok = __all_sync(0xffffffffu, ok);
         tc_fence_after();
         if (!ok) *abort_flag = 1;
         if (tid == 0) BGEMM_STAMP(7);
-
-        // ---- accumulators -> shared memory: int32 [NT][128]; warps 0-3 take the lower half of the columns ----
-        int* sPw = reinterpret_cast<int*>(sB);
-        if (ok) {
-            constexpr int HALF = NT / 2;
-#pragma unroll 1
-            for (int n0 = set * HALF; n0 < (set + 1) * HALF; n0 += 8) {
-                int acc[8];
-                if (POW2) {
-                    uint32_t t[8][8];
-#pragma unroll
-                    for (int j = 0; j < 8; j++) tmem_ld8(tmem_d + lane_base + j * NT + n0, t[j]);
-                    tmem_wait_ld();
-#pragma unroll
-                    for (int q = 0; q < 8; q++) {
-                        acc[q] = 0;
-#pragma unroll
-                        for (int j = 0; j < 8; j++) acc[q] += ((int)t[j][q]) >> j;
-                    }
-                } else {
-                    uint32_t t[8];
-                    tmem_ld8(tmem_d + lane_base + n0, t);
-                    tmem_wait_ld();
-#pragma unroll
-                    for (int q = 0; q < 8; q++) acc[q] = (int)t[q];
-                }
-#pragma unroll
-                for (int q = 0; q < 8; q++) sPw[(n0 + q) * 128 + r] = acc[q];
-            }
-        }
-        tc_fence_before();
     }
 
-    // ======================================= reduce, convert, store ================================================
+    // ======================================= epilogue ==========================================================
+    // Accumulators leave tensor memory as int32 [columns][128] tiles in shared memory (aliasing the operand stages,
+    // which are idle by now). With K partitions in a cluster, column c of partition `split` is PUSHED into the
+    // shared memory of the CTA that will store it (st.shared::cluster, slot `split`), so that after one cluster
+    // barrier every CTA sums its own slots locally. With more partitions than a cluster holds, tiles go through a
+    // global workspace and the last CTA to arrive sums them.
     const bool epi_thread = warp < 8;
-    const int* sP = reinterpret_cast<const int*>(sB);
+    int* sP = reinterpret_cast<int*>(sB);
+    const int per = p.cluster ? (((NT + p.split_k - 1) / p.split_k + 7) & ~7) : NT;      // columns stored by one CTA
     TileOut tout;
     tout.p = &p; tout.s_alpha = s_alpha; tout.s_colsum = s_colsum;
     tout.batch = batch; tout.m_base = mt * 128; tout.n_base = nt * NT;
 
-    if (p.split_k == 1) {
-        if (epi_thread) {
-            named_bar_sync(1, kUnpackThreads);
-            if (!*abort_flag) write_tile<kSrcLocal, NT>(tout, sP, nullptr, 1, 0, NT, tid);
-        }
-    } else if (p.cluster) {
-        // The K partitions of a tile form a thread-block cluster: after the barrier CTA c sums columns
-        // [c * per, (c + 1) * per) over all peers through distributed shared memory and stores them.
+    if (p.cluster) {   // every CTA of the cluster is past its mainloop: peers' operand stages may be overwritten
         __syncwarp();
         cluster_arrive_release();
         cluster_wait_acquire();
-        if (epi_thread && !*abort_flag) {
-            const int per = ((NT + p.split_k - 1) / p.split_k + 7) & ~7;     // columns per CTA, multiple of 8
-            const int nbeg = min(NT, split * per), nend = min(NT, nbeg + per);
-            write_tile<kSrcCluster, NT>(tout, sP, nullptr, p.split_k, nbeg, nend, tid);
+        if (tid == 0) BGEMM_STAMP(13);
+    }
+    if (epi_thread && !*abort_flag) {
+        const int set = warp >> 2;
+        const int r = (warp & 3) * 32 + lane;
+        const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
+        constexpr int HALF = NT / 2;                             // warps 0-3 take the lower half of the columns
+        tc_fence_after();
+#pragma unroll 1
+        for (int n0 = set * HALF; n0 < (set + 1) * HALF; n0 += 8) {
+            int acc[8];
+            if (POW2) {
+                uint32_t t[8][8];
+#pragma unroll
+                for (int j = 0; j < 8; j++) tmem_ld8(tmem_d + lane_base + j * NT + n0, t[j]);
+                tmem_wait_ld();
+#pragma unroll
+                for (int q = 0; q < 8; q++) {
+                    acc[q] = 0;
+#pragma unroll
+                    for (int j = 0; j < 8; j++) acc[q] += ((int)t[j][q]) >> j;
+                }
+            } else {
+                uint32_t t[8];
+                tmem_ld8(tmem_d + lane_base + n0, t);
+                tmem_wait_ld();
+#pragma unroll
+                for (int q = 0; q < 8; q++) acc[q] = (int)t[q];
+            }
+            if (p.cluster) {
+                const int dst = n0 / per;                        // the 8 columns of a chunk share their destination
+                const uint32_t remote = mapa_shared(smem_u32(sP + ((split * per + (n0 - dst * per)) * 128 + r)), (uint32_t)dst);
+#pragma unroll
+                for (int q = 0; q < 8; q++) st_dsmem_s32(remote + (uint32_t)(q * 128 * 4), acc[q]);
+            } else {
+#pragma unroll
+                for (int q = 0; q < 8; q++) sP[(n0 + q) * 128 + r] = acc[q];
+            }
         }
+        tc_fence_before();
+    }
+    if (tid == 0) BGEMM_STAMP(12);
+
+    if (p.split_k == 1) {
+        if (epi_thread) {
+            named_bar_sync(1, kUnpackThreads);
+            if (!*abort_flag) write_tile<false>(tout, sP, 1, 0, 0, NT, tid);
+        }
+    } else if (p.cluster) {
         __syncwarp();
-        cluster_arrive_release();      // nobody may exit while a peer still reads its shared memory
-        cluster_wait_acquire();
+        cluster_arrive_release();      // the pushes of all peers are visible after this barrier; afterwards
+        cluster_wait_acquire();        // nobody touches another CTA's shared memory again
+        if (tid == 0) BGEMM_STAMP(14);
+        if (epi_thread && !*abort_flag) {
+            const int nbeg = min(NT, split * per), ncols = min(NT, nbeg + per) - nbeg;
+            write_tile<false>(tout, sP, p.split_k, per * 128, nbeg, ncols, tid);
+        }
     } else if (epi_thread) {
-        // More partitions than a cluster holds: partial tiles go to a global workspace; the last CTA of a tile
-        // to arrive (atomic ticket, nobody spins) sums them.
         const int tile_id = (batch * p.mtiles + mt) * p.ntiles + nt;
         int* slab = p.ws_partial + ((size_t)tile_id * p.split_k + split) * (NT * 128);
         named_bar_sync(1, kUnpackThreads);
@@ -487,7 +528,7 @@ __global__ void __launch_bounds__(kGemmThreads, Cfg<NT, POW2>::MIN_CTAS) gemm_ke
         named_bar_sync(1, kUnpackThreads);
         if (*last_flag && !*abort_flag) {
             __threadfence();
-            write_tile<kSrcGlobal, NT>(tout, sP, p.ws_partial + (size_t)tile_id * p.split_k * (NT * 128), p.split_k, 0, NT, tid);
+            write_tile<true>(tout, p.ws_partial + (size_t)tile_id * p.split_k * (NT * 128), p.split_k, NT * 128, 0, NT, tid);
         }
     }
     if (tid == 0) BGEMM_STAMP(8);
@@ -511,6 +552,17 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
                                   const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
+static int sm_count() {
+    static int cache[64] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+    if (!cache[dev]) {
+        int n = 0;
+        cache[dev] = (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && n > 0) ? n : 148;
+    }
+    return cache[dev];
+}
+
 static EncodeTiledFn get_encode_fn() {
     static EncodeTiledFn fn = nullptr;
     static bool tried = false;
@@ -525,14 +577,14 @@ static EncodeTiledFn get_encode_fn() {
     return fn;
 }
 
-template <int NT, bool POW2>
+template <int NT, bool POW2, bool DEEP>
 static int launch_variant(cudaStream_t stream, const CUtensorMap& tmap, const GemmParams& p, dim3 grid) {
-    using C = Cfg<NT, POW2>;
+    using C = Cfg<NT, POW2, DEEP>;
     static bool configured[64] = {};
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev < 64 && !configured[dev]) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_kernel<NT, POW2>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
+        cudaError_t e = cudaFuncSetAttribute(gemm_kernel<NT, POW2, DEEP>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
         if (e != cudaSuccess) return (int)e;
         configured[dev] = true;
     }
@@ -541,16 +593,25 @@ static int launch_variant(cudaStream_t stream, const CUtensorMap& tmap, const Ge
     cfg.blockDim = dim3(kGemmThreads, 1, 1);
     cfg.dynamicSmemBytes = C::SMEM_BYTES;
     cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
+    unsigned na = 0;
     if (p.cluster) {
-        attr[0].id = cudaLaunchAttributeClusterDimension;
-        attr[0].val.clusterDim.x = 1;
-        attr[0].val.clusterDim.y = (unsigned)p.split_k;
-        attr[0].val.clusterDim.z = 1;
-        cfg.attrs = attr;
-        cfg.numAttrs = 1;
+        attr[na].id = cudaLaunchAttributeClusterDimension;
+        attr[na].val.clusterDim.x = 1;
+        attr[na].val.clusterDim.y = (unsigned)p.split_k;
+        attr[na].val.clusterDim.z = 1;
+        na++;
     }
-    const cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_kernel<NT, POW2>, tmap, p);
+    if (programmatic_launch_enabled()) {
+        // The kernel's prologue (barrier set-up, tensor-memory allocation) may start while the previous kernel of
+        // the stream drains; it executes griddepcontrol.wait before its first global-memory access.
+        attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[na].val.programmaticStreamSerializationAllowed = 1;
+        na++;
+    }
+    cfg.attrs = na ? attr : nullptr;
+    cfg.numAttrs = na;
+    const cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_kernel<NT, POW2, DEEP>, tmap, p);
     count_launch();
     return (int)(e != cudaSuccess ? e : cudaGetLastError());
 }
@@ -581,12 +642,14 @@ int launch_gemm(cudaStream_t stream, GemmParams p, const int8_t* acts, long long
     if (r != CUDA_SUCCESS) return BGEMM_ERR_DRIVER;
 
     dim3 grid((unsigned)p.ntiles, (unsigned)(p.mtiles * p.split_k), (unsigned)batch);
+    // At most one CTA per SM in the whole launch: give each CTA the full tensor memory and a deeper pipeline.
+    const bool deep = (long long)grid.x * grid.y * grid.z <= sm_count();
     switch (NT) {
-        case 16: return launch_variant<16, true>(stream, tmap, p, grid);
-        case 32: return launch_variant<32, true>(stream, tmap, p, grid);
-        case 64: return launch_variant<64, false>(stream, tmap, p, grid);
-        case 128: return launch_variant<128, false>(stream, tmap, p, grid);
-        default: return launch_variant<256, false>(stream, tmap, p, grid);
+        case 16: return deep ? launch_variant<16, true, true>(stream, tmap, p, grid) : launch_variant<16, true, false>(stream, tmap, p, grid);
+        case 32: return launch_variant<32, true, true>(stream, tmap, p, grid);
+        case 64: return deep ? launch_variant<64, false, true>(stream, tmap, p, grid) : launch_variant<64, false, false>(stream, tmap, p, grid);
+        case 128: return deep ? launch_variant<128, false, true>(stream, tmap, p, grid) : launch_variant<128, false, false>(stream, tmap, p, grid);
+        default: return launch_variant<256, false, true>(stream, tmap, p, grid);
     }
 }
 

@@ -29,6 +29,7 @@ struct GemmParams {
 };
 
 void count_launch();
+bool programmatic_launch_enabled();   // BGEMM_PDL=0 in the environment switches it off
 long long* debug_profile_buffer();
 int* device_status_word();        // per-device status word, lazily created (cudaGetSymbolAddress)
 
@@ -41,6 +42,25 @@ int launch_prepare_acts(cudaStream_t stream, const void* src, int dtype, long lo
                         int transpose, int8_t* dst, int32_t* colsum, long long batch, long long src_batch_stride);
 int launch_pack_rowmajor_msb(cudaStream_t stream, const void* src, int dtype, long long rows, long long K, long long ld, uint32_t* dst);
 int launch_retile(cudaStream_t stream, const uint32_t* src_words, long long M, long long K, int invert, void* plane);
+
+// Launch with the programmatic-stream-serialization attribute (when enabled): the kernel may start while the
+// previous kernel of the stream drains and must execute griddepcontrol.wait before touching global memory.
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, cudaStream_t stream, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = 0;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    if (programmatic_launch_enabled()) {
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+    }
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
 
 inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 

@@ -12,6 +12,7 @@
 #include <cstring>
 
 #include "internal.h"
+#include "ptx.cuh"
 
 namespace bgemm {
 
@@ -61,6 +62,8 @@ __global__ void __launch_bounds__(256) pack_weights_kernel(const T* __restrict__
                                                            uint8_t* __restrict__ plane, int32_t* __restrict__ rowpop,
                                                            __half* __restrict__ alpha, long long src_batch_stride,
                                                            long long plane_batch_bytes) {
+    grid_launch_dependents();
+    grid_dependency_wait();
     const int lane = threadIdx.x & 31;
     const long long row = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     const long long batch = blockIdx.y;
@@ -133,6 +136,8 @@ template <typename T>
 __global__ void __launch_bounds__(256) prepare_acts_kernel(const T* __restrict__ src, long long N, long long K, long long ld, int mode,
                                                            int8_t* __restrict__ dst, int32_t* __restrict__ colsum,
                                                            long long src_batch_stride) {
+    grid_launch_dependents();
+    grid_dependency_wait();
     const int lane = threadIdx.x & 31;
     const long long row = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     const long long batch = blockIdx.y;
@@ -175,6 +180,8 @@ __global__ void __launch_bounds__(256) prepare_acts_t_kernel(const T* __restrict
                                                              long long src_batch_stride) {
     __shared__ int8_t tile[32][33];
     __shared__ int part[8][32];
+    grid_launch_dependents();
+    grid_dependency_wait();
     const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
     const long long n0 = (long long)blockIdx.x * 32;
     const long long batch = blockIdx.y;
@@ -266,26 +273,27 @@ int launch_pack_weights(cudaStream_t stream, const void* src, int dtype, long lo
     const long long rows = (M + 127) / 128 * 128;
     dim3 grid((unsigned)((rows + 7) / 8), (unsigned)batch);
     const long long pbytes = (long long)bgemm_plane_bytes(M, K);
-    BGEMM_DISPATCH_DTYPE(dtype, (pack_weights_kernel<T><<<grid, 256, 0, stream>>>(
-                                    static_cast<const T*>(src), M, K, ld, wbit_mode,
-                                    static_cast<uint8_t*>(plane), rowpop, static_cast<__half*>(alpha), src_batch_stride, pbytes)));
+    cudaError_t e = cudaSuccess;
+    BGEMM_DISPATCH_DTYPE(dtype, (e = launch_pdl(pack_weights_kernel<T>, grid, dim3(256), stream, static_cast<const T*>(src), M, K, ld, wbit_mode,
+                                                static_cast<uint8_t*>(plane), rowpop, static_cast<__half*>(alpha), src_batch_stride, pbytes)));
     count_launch();
-    return (int)cudaGetLastError();
+    return (int)(e != cudaSuccess ? e : cudaGetLastError());
 }
 
 int launch_prepare_acts(cudaStream_t stream, const void* src, int dtype, long long N, long long K, long long ld, int act_mode,
                         int transpose, int8_t* dst, int32_t* colsum, long long batch, long long src_batch_stride) {
+    cudaError_t e = cudaSuccess;
     if (transpose) {
         dim3 grid((unsigned)((N + 31) / 32), (unsigned)batch);
-        BGEMM_DISPATCH_DTYPE(dtype, (prepare_acts_t_kernel<T><<<grid, 256, 0, stream>>>(static_cast<const T*>(src), N, K, ld, act_mode,
-                                                                                       dst, colsum, src_batch_stride)));
+        BGEMM_DISPATCH_DTYPE(dtype, (e = launch_pdl(prepare_acts_t_kernel<T>, grid, dim3(256), stream, static_cast<const T*>(src), N, K, ld, act_mode,
+                                                    dst, colsum, src_batch_stride)));
     } else {
         dim3 grid((unsigned)((N + 7) / 8), (unsigned)batch);
-        BGEMM_DISPATCH_DTYPE(dtype, (prepare_acts_kernel<T><<<grid, 256, 0, stream>>>(static_cast<const T*>(src), N, K, ld, act_mode, dst,
-                                                                                     colsum, src_batch_stride)));
+        BGEMM_DISPATCH_DTYPE(dtype, (e = launch_pdl(prepare_acts_kernel<T>, grid, dim3(256), stream, static_cast<const T*>(src), N, K, ld, act_mode, dst,
+                                                    colsum, src_batch_stride)));
     }
     count_launch();
-    return (int)cudaGetLastError();
+    return (int)(e != cudaSuccess ? e : cudaGetLastError());
 }
 
 int launch_pack_rowmajor_msb(cudaStream_t stream, const void* src, int dtype, long long rows, long long K, long long ld, uint32_t* dst) {

@@ -34,13 +34,24 @@ def test_binary_linear_layers_match_reference_bnn_twin(L, tag, cls):
     bias = GOLD[f"{tag}_bias"] if f"{tag}_bias" in GOLD.files else None
     layer = _set_weight(getattr(L, cls)(w.shape[1], w.shape[0], bias is not None), w, bias)
     y = layer(torch.from_numpy(x).cuda())
-    want = torch.from_numpy(GOLD[f"{tag}_y"])
-    assert np.allclose(layer.sw.detach().cpu().numpy(), GOLD[f"{tag}_sw"], rtol=1e-6)
-    # same integers, same fp32 scales; products are associated differently ((acc*sw)*sa vs bias folded in)
-    assert torch.allclose(y.float().cpu(), want, rtol=1e-5, atol=1e-7)
-    # and the in-module dense twin agrees on the GPU as well
+    gold = torch.from_numpy(GOLD[f"{tag}_y"])
+    sw, sa = layer.sw.detach().cpu(), float(layer.sa.detach().cpu())
+    assert np.allclose(sw.numpy(), GOLD[f"{tag}_sw"], rtol=1e-6) and abs(sa - float(GOLD[f"{tag}_sa"])) <= 1e-6 * sa
+    # integers recovered from the reference twin's output: y = (acc + bias) * sw * sa there (F.linear adds the bias first)
+    b = torch.zeros(w.shape[0]) if bias is None else torch.from_numpy(bias)
+    acc_gold = (gold / (sw * sa) - b).round()
+    xc = torch.from_numpy(x) - torch.from_numpy(x).mean()
+    wc = torch.from_numpy(w) - torch.from_numpy(w).mean()
+    acc = O.ref_acc(wc, xc, O.OP_XOR).float()
+    assert torch.equal(acc, acc_gold)
+    # the GPU layers follow the reference's BGEMM layers, which scale the fp16 kernel output and add the bias last
+    want = acc.half() * sw * sa + b
+    assert torch.allclose(y.float().cpu(), want, rtol=1e-6, atol=1e-7)
+    if bias is None:
+        assert torch.allclose(y.float().cpu(), gold, rtol=1e-6, atol=1e-7)
+    # the in-module dense twin reproduces the golden output on the GPU as well
     twin = _set_weight(L.BNNLinear(w.shape[1], w.shape[0], bias is not None), w, bias)
-    assert torch.allclose(twin(torch.from_numpy(x).cuda()).cpu(), want, rtol=1e-5, atol=1e-7)
+    assert torch.allclose(twin(torch.from_numpy(x).cuda()).cpu(), gold, rtol=1e-5, atol=1e-7)
 
 
 def test_bwta_layer_matches_reference_random(L):
