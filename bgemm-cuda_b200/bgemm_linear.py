@@ -61,7 +61,11 @@ def _ste_grads(x_sign: torch.Tensor, w_sign: torch.Tensor, grad_output: torch.Te
 # autograd functions (reference: bgemm_linear.py:9-219)
 # --------------------------------------------------------------------------------------------------
 class bgemm_matmul(torch.autograd.Function):
-    """{-1,+1} x {-1,+1} (or {0,1} with instruction='and') product matA @ matB, both binarised by sign."""
+    """{-1,+1} x {-1,+1} (or {0,1} with instruction='and') product matA @ matB, both binarised by sign.
+
+    Backward is the straight-through gradient of A @ B. (The reference's formulas, bgemm_linear.py:28-42, multiply
+    grad_output by matB without transposing it, which only has consistent shapes when matB is square.)
+    """
 
     @staticmethod
     def forward(ctx, matA, matB, instruction="xor"):
@@ -76,11 +80,11 @@ class bgemm_matmul(torch.autograd.Function):
         if b.dim() != 2:
             raise AssertionError("matB dim must be 2, now is %d" % b.dim())
         if a.dim() == 3:
-            b_grad = torch.bmm(a.transpose(1, 2), grad_output).transpose(1, 2)
-            a_grad = torch.bmm(grad_output, b.repeat(a.shape[0], 1, 1))
+            b_grad = torch.bmm(a.transpose(1, 2), grad_output).sum(dim=0)
+            a_grad = torch.matmul(grad_output, b.T)
         else:
-            b_grad = torch.mm(a.T, grad_output).T
-            a_grad = torch.mm(grad_output, b)
+            b_grad = torch.mm(a.T, grad_output)
+            a_grad = torch.mm(grad_output, b.T)
         return a_grad, b_grad, None
 
 
