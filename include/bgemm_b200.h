@@ -168,6 +168,34 @@ int bgemm_version(void);
 /* Number of kernels this library has launched in this process (for launch accounting in benchmarks). */
 uint64_t bgemm_launch_count(void);
 
+/* bgemm_linear_forward for callers that cannot provide a workspace. This entry point has no counterpart in the
+ * reference, whose wrapper allocates its scratch with torch::empty on every call (fp6_linear.cu:580-586).
+ *
+ * Who needs it: code that runs where device memory cannot be obtained at call time -- a serving loop that
+ * reserves all GPU memory for its own pools at start-up and forbids allocation on the request path (an
+ * allocation may take a driver-wide lock, synchronise the device or simply fail once the pools own the
+ * memory), or a plug-in written in C whose host application owns the allocator and exposes no hook to it.
+ * Such callers still pass their operands and the output buffer; only the library's internal scratch (packed
+ * weight plane, int8 activations, column sums) is missing, and here it comes from a fixed array of
+ * BGEMM_NOALLOC_SCRATCH_BYTES in device global memory that belongs to the library image. Every GPU that loads
+ * the library holds that array until the process exits.
+ *
+ * Same arguments and results as bgemm_linear_forward, minus split_k (chosen by the library, at most 8, so the
+ * reduction stays on chip) and the workspace. Limits and rules:
+ *   - the problem must satisfy bgemm_linear_workspace_bytes(M, N, K, 0) <= BGEMM_NOALLOC_SCRATCH_BYTES (for
+ *     example M = K = 4096 with N up to ~1400, or 28672 x 1024 x 16); larger ones return BGEMM_ERR_TOO_LARGE
+ *     and launch nothing;
+ *   - the first call on a device looks up the array's device address (cudaGetSymbolAddress with that device
+ *     current) and sets kernel attributes; make that first call outside any stream capture;
+ *   - the call itself performs no cudaMalloc / cudaFree and calls no allocating library routine;
+ *   - all calls on a device share the one array, which keeps the previous call's contents: nothing in it has
+ *     to start at zero for this variant, but two calls whose kernels can overlap on the GPU (different
+ *     streams, or different host threads without ordering) race on it -- serialise them on one stream.        */
+#define BGEMM_NOALLOC_SCRATCH_BYTES (8u << 20)
+int bgemm_linear_forward_noalloc(void* stream, const void* weight_f16, const void* acts_f16, void* out,
+                                 int64_t M, int64_t N, int64_t K, int op, int out_kind, int out_layout,
+                                 const void* alpha);
+
 /* Every wait inside the kernels is time-bounded (about one second). A wait that runs out makes its kernel
  * drain and exit normally and records a small positive code in a per-device status word; the results of
  * that launch are then undefined. This call synchronises with the device, returns the word (0 = no wait
