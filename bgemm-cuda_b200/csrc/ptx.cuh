@@ -68,7 +68,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     return true;
 }
 
-// ---- bulk (TMA) copies, no multicast anywhere ---------------------------------------------------------
+// ---- bulk (TMA) copies: every CTA fetches its own tiles -----------------------------------------------
 __device__ __forceinline__ void bulk_g2s(uint32_t dst_smem, const void* src, uint32_t bytes, uint32_t bar) {
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst_smem),
                  "l"(src), "r"(bytes), "r"(bar)
