@@ -10,7 +10,10 @@
 //              of the tile; per K block it reads its 32 packed bytes from shared memory, expands them to
 //              8 x (128 x 32) u8 operand slices with one or two logic ops per 4 elements, and writes them to
 //              tensor memory (tcgen05.st). Afterwards all eight warps run the epilogue.
-//   warp 8     allocates tensor memory; one lane issues 8 UMMAs (128 x NT x 32) per K block.
+//   warp 8     allocates tensor memory; one lane issues the 8 UMMAs (128 x NT x 32) of every even K block.
+//   warp 11    one lane issues the UMMAs of the odd K blocks. Issuing a UMMA blocks the thread until the tensor pipe
+//              accepts it and an mbarrier poll costs it ~200 clocks, so one issuer leaves the pipe idle between K
+//              blocks; two issuers, each polling while the other feeds the pipe, keep it busy (measured 1.4x).
 //   warp 9     one lane streams the packed weight tiles (4 KB each, contiguous) with cp.async.bulk.
 //   warp 10    one lane loads the activation tiles [NT x 256 B] with two 128B-swizzled TMA boxes.
 //
@@ -32,8 +35,8 @@
 namespace bgemm {
 
 constexpr int kUnpackThreads = 256;
-constexpr int kGemmThreads = 352;
-constexpr int kWarpMma = 8, kWarpW = 9, kWarpB = 10;
+constexpr int kGemmThreads = 384;
+constexpr int kWarpMma = 8, kWarpW = 9, kWarpB = 10, kWarpMma2 = 11;
 
 __host__ __device__ constexpr int pow2_ceil(int v) {
     int p = 32;
@@ -58,9 +61,11 @@ struct Cfg {
     static constexpr int TMEM_COLS = pow2_ceil(D_COLS + A_STAGE_COLS * A_STAGES);
     static constexpr int B_STAGE_BYTES = NT * 256;
     static constexpr bool ONE_PER_SM = TMEM_BUDGET == 512;
-    static constexpr int B_STAGES = NT <= 32 ? 8 : (NT == 64 ? (ONE_PER_SM ? 6 : 4) : (NT == 128 ? (ONE_PER_SM ? 4 : 3) : 3));
-    static constexpr int W_STAGES = NT == 256 ? 4 : ((NT == 128 && !ONE_PER_SM) ? 2 : 8);
-    static constexpr int NBARS = 2 * W_STAGES + 2 * B_STAGES + 2 * A_STAGES + 1;
+    static constexpr int B_STAGES = NT <= 32 ? 8 : (NT == 64 ? (ONE_PER_SM ? 6 : 4) : (NT == 128 ? (ONE_PER_SM ? 4 : 2) : 3));
+    static constexpr int W_STAGES = NT == 256 ? 4 : 8;
+    // Tiles of 256 columns are bound by UMMA execution even with one issuer; narrower ones use two.
+    static constexpr int NMMA = NT == 256 ? 1 : 2;
+    static constexpr int NBARS = 2 * W_STAGES + 2 * B_STAGES + 2 * A_STAGES + 2;
     static constexpr int MISC_BYTES = 512 /*barriers*/ + 512 /*alpha*/ + 1024 /*colsum*/ + 512 /*flags*/;
     // Epilogue staging aliases the activation and weight stages: one [NT][128] int32 tile, or -- K partitions in a
     // cluster -- up to (NT + 7 * 8) columns of partial sums received from the peers.
@@ -75,6 +80,7 @@ struct Cfg {
     // served by the same set, so every waiter has seen the previous phase of the barrier it waits on; with an
     // odd count a set's first wait on a barrier would name phase 1 and pass before phase 0 has completed.
     static_assert(W_STAGES % 2 == 0 && A_STAGES % (2 * G) == 0, "stage counts shared by the two unpack sets must keep stage -> set fixed");
+    static_assert(NMMA == 1 || B_STAGES % 2 == 0, "activation stages shared by the two UMMA issuers must keep stage -> issuer fixed");
     static_assert(TMEM_COLS <= 512, "tensor memory budget");
     static_assert(NT % 16 == 0 && NT >= 16 && NT <= 256, "UMMA N");
     static_assert(NBARS * 8 <= 512, "barrier area");
@@ -259,6 +265,7 @@ __global__ void __launch_bounds__(kGemmThreads, Cfg<NT, POW2, DEEP>::MIN_CTAS) g
     const uint32_t a_full = b_empty + 8 * C::B_STAGES;
     const uint32_t a_empty = a_full + 8 * C::A_STAGES;
     const uint32_t d_full = a_empty + 8 * C::A_STAGES;
+    const uint32_t first_done = d_full + 8;       // K block 0 (which zeroes the accumulators) has been executed
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int nt = blockIdx.x;
@@ -274,7 +281,7 @@ __global__ void __launch_bounds__(kGemmThreads, Cfg<NT, POW2, DEEP>::MIN_CTAS) g
         for (int i = lane; i < C::NBARS; i += 32) {
             const bool four = (i >= C::W_STAGES && i < 2 * C::W_STAGES) ||
                               (i >= 2 * C::W_STAGES + 2 * C::B_STAGES && i < 2 * C::W_STAGES + 2 * C::B_STAGES + C::A_STAGES);
-            mbar_init(w_full + 8 * i, four ? 4 : 1);
+            mbar_init(w_full + 8 * i, four ? 4 : (i == C::NBARS - 2 ? C::NMMA : 1));       // d_full collects one commit per issuer
         }
         if (lane == 0) { *abort_flag = 0; *last_flag = 0; }
         mbar_fence_init();
@@ -342,14 +349,18 @@ __global__ void __launch_bounds__(kGemmThreads, Cfg<NT, POW2, DEEP>::MIN_CTAS) g
                 }
             }
         }
-    } else if (warp == kWarpMma) {
-        // ---------------- UMMA issuer ----------------
-        if (lane == 0) {
+    } else if (warp == kWarpMma || warp == kWarpMma2) {
+        // ---------------- UMMA issuers: issuer `me` takes K blocks me, me + NMMA, ... ----------------
+        const int me = warp == kWarpMma ? 0 : 1;
+        if (lane == 0 && me < C::NMMA) {
             constexpr uint32_t idesc = umma_idesc_u8s8(NT);
             bool ok = true;
             long long twa = 0, twb = 0;
             const long long tloop0 = clock64();
-            for (int i = 0; i < nkb && ok; i++) {
+            // Integer accumulation commutes, so the two issuers need no mutual order -- except that the UMMAs of K
+            // block 0 overwrite the accumulators (accumulate = 0) and must run before anything is added.
+            if (me == 1 && nkb > 1) ok = mbar_wait(first_done, 0, abort_flag, p.status, 18);
+            for (int i = me; i < nkb && ok; i += C::NMMA) {
                 const int bs = i % C::B_STAGES;
                 BGEMM_TIMED(twb, ok = mbar_wait(b_full + 8 * bs, (i / C::B_STAGES) & 1, abort_flag, p.status, 14));
                 const uint32_t bbase = smem_u32(sB + bs * C::B_STAGE_BYTES);
@@ -371,10 +382,10 @@ __global__ void __launch_bounds__(kGemmThreads, Cfg<NT, POW2, DEEP>::MIN_CTAS) g
                     umma_commit(a_empty + 8 * as);
                 }
                 umma_commit(b_empty + 8 * bs);
+                if (i == 0) umma_commit(first_done);
             }
             umma_commit(d_full);
-            BGEMM_STAMP(6);
-            BGEMM_PUT(16, twa); BGEMM_PUT(17, twb); BGEMM_PUT(24, clock64() - tloop0);
+            if (me == 0) { BGEMM_STAMP(6); BGEMM_PUT(16, twa); BGEMM_PUT(17, twb); BGEMM_PUT(24, clock64() - tloop0); }
         }
     } else {
         // ---------------- unpack: set 0 = warps 0-3 takes even K blocks, set 1 = warps 4-7 odd ones ----------------
