@@ -29,6 +29,8 @@
 // converted (fused per-row scale) and stored with 16-byte coalesced stores.
 #include <cuda_fp16.h>
 
+#include <cstdlib>
+
 #include "internal.h"
 #include "ptx.cuh"
 
@@ -627,7 +629,18 @@ static int launch_variant(cudaStream_t stream, const CUtensorMap& tmap, const Ge
     return (int)(e != cudaSuccess ? e : cudaGetLastError());
 }
 
+// Tuning overrides (read once): BGEMM_FORCE_NT = 16|32|64|128|256 forces the tile width, BGEMM_FORCE_DEEP = 0|1 the
+// occupancy variant. Unset in normal use.
+static int env_int(const char* name) {
+    const char* e = std::getenv(name);
+    return e ? std::atoi(e) : -1;
+}
+static int forced_nt() { static const int v = env_int("BGEMM_FORCE_NT"); return v; }
+static int forced_deep() { static const int v = env_int("BGEMM_FORCE_DEEP"); return v; }
+
 int gemm_tile_n(long long N) {
+    const int f = forced_nt();
+    if (f == 16 || f == 32 || f == 64 || f == 128 || f == 256) return f;
     if (N <= 16) return 16;
     if (N <= 32) return 32;
     if (N <= 64) return 64;
@@ -654,7 +667,7 @@ int launch_gemm(cudaStream_t stream, GemmParams p, const int8_t* acts, long long
 
     dim3 grid((unsigned)p.ntiles, (unsigned)(p.mtiles * p.split_k), (unsigned)batch);
     // At most one CTA per SM in the whole launch: give each CTA the full tensor memory and a deeper pipeline.
-    const bool deep = (long long)grid.x * grid.y * grid.z <= sm_count();
+    const bool deep = forced_deep() >= 0 ? forced_deep() != 0 : (long long)grid.x * grid.y * grid.z <= sm_count();
     switch (NT) {
         case 16: return deep ? launch_variant<16, true, true>(stream, tmap, p, grid) : launch_variant<16, true, false>(stream, tmap, p, grid);
         case 32: return launch_variant<32, true, true>(stream, tmap, p, grid);

@@ -79,34 +79,46 @@ __global__ void __launch_bounds__(256) pack_weights_kernel(const T* __restrict__
     uint8_t* tile_row = plane + (row / 128) * kblocks * 4096;
     const int r = (int)(row % 128);
     const bool vec_ok = (sizeof(T) == 2) && ((reinterpret_cast<uintptr_t>(rp) & 15) == 0);
-    for (long long kb = 0; kb < kblocks; kb++) {
-        uint32_t w0 = 0, w1 = 0;
-        const long long k0 = kb * 256 + lane * 8;
-        if (live && k0 < K) {
-            T v[8];
-            if (vec_ok && k0 + 8 <= K) {
-                *reinterpret_cast<uint4*>(v) = *reinterpret_cast<const uint4*>(rp + k0);
-            } else {
+    constexpr int U = 4;        // K blocks in flight per warp: four independent 16-byte streaming loads per lane
+    for (long long kb0 = 0; kb0 < kblocks; kb0 += U) {
+        T v[U][8];
 #pragma unroll
-                for (int e = 0; e < 8; e++) v[e] = (k0 + e < K) ? rp[k0 + e] : T();
-            }
+        for (int u = 0; u < U; u++) {
+            const long long k0 = (kb0 + u) * 256 + lane * 8;
+            if (live && k0 < K) {
+                if (vec_ok && k0 + 8 <= K) {
+                    *reinterpret_cast<uint4*>(v[u]) = __ldcs(reinterpret_cast<const uint4*>(rp + k0));
+                } else {
 #pragma unroll
-            for (int e = 0; e < 8; e++) {
-                if (k0 + e < K) {
-                    const uint32_t bit = (uint32_t)weight_bit<T>(v[e], mode);
-                    if (e < 4) w0 |= bit << (8 * e + j); else w1 |= bit << (8 * (e - 4) + j);
-                    if (alpha) mag += Elem<T>::mag(v[e]);
+                    for (int e = 0; e < 8; e++) v[u][e] = (k0 + e < K) ? rp[k0 + e] : T();
                 }
             }
         }
 #pragma unroll
-        for (int off = 4; off < 32; off <<= 1) {
-            w0 |= __shfl_xor_sync(0xffffffffu, w0, off);
-            w1 |= __shfl_xor_sync(0xffffffffu, w1, off);
-        }
-        if (lane < 4) {
-            pop += __popc(w0) + __popc(w1);
-            *reinterpret_cast<uint2*>(tile_row + kb * 4096 + tile_word_offset(r, 2 * lane)) = make_uint2(w0, w1);
+        for (int u = 0; u < U; u++) {
+            const long long kb = kb0 + u;
+            if (kb >= kblocks) break;
+            const long long k0 = kb * 256 + lane * 8;
+            uint32_t w0 = 0, w1 = 0;
+            if (live && k0 < K) {
+#pragma unroll
+                for (int e = 0; e < 8; e++) {
+                    if (k0 + e < K) {
+                        const uint32_t bit = (uint32_t)weight_bit<T>(v[u][e], mode);
+                        if (e < 4) w0 |= bit << (8 * e + j); else w1 |= bit << (8 * (e - 4) + j);
+                        if (alpha) mag += Elem<T>::mag(v[u][e]);
+                    }
+                }
+            }
+#pragma unroll
+            for (int off = 4; off < 32; off <<= 1) {
+                w0 |= __shfl_xor_sync(0xffffffffu, w0, off);
+                w1 |= __shfl_xor_sync(0xffffffffu, w1, off);
+            }
+            if (lane < 4) {
+                pop += __popc(w0) + __popc(w1);
+                *reinterpret_cast<uint2*>(tile_row + kb * 4096 + tile_word_offset(r, 2 * lane)) = make_uint2(w0, w1);
+            }
         }
     }
     if (live && (rowpop || alpha)) {
@@ -147,26 +159,33 @@ __global__ void __launch_bounds__(256) prepare_acts_kernel(const T* __restrict__
     int8_t* dp = dst + (batch * N + row) * kld;
     const bool vec_ok = (sizeof(T) == 2) && ((reinterpret_cast<uintptr_t>(rp) & 15) == 0);
     int sum = 0;
-    for (long long k0 = lane * 8; k0 < kld; k0 += 256) {
-        int8_t o[8];
-        if (k0 < K) {
-            T v[8];
-            if (vec_ok && k0 + 8 <= K) {
-                *reinterpret_cast<uint4*>(v) = *reinterpret_cast<const uint4*>(rp + k0);
-            } else {
+    constexpr int U = 4;        // four independent 16-byte streaming loads per lane in flight
+    for (long long kbase = lane * 8; kbase < kld; kbase += 256 * U) {
+        T v[U][8];
 #pragma unroll
-                for (int e = 0; e < 8; e++) v[e] = (k0 + e < K) ? rp[k0 + e] : T();
+        for (int u = 0; u < U; u++) {
+            const long long k0 = kbase + 256 * u;
+            if (k0 < K) {
+                if (vec_ok && k0 + 8 <= K) {
+                    *reinterpret_cast<uint4*>(v[u]) = __ldcs(reinterpret_cast<const uint4*>(rp + k0));
+                } else {
+#pragma unroll
+                    for (int e = 0; e < 8; e++) v[u][e] = (k0 + e < K) ? rp[k0 + e] : T();
+                }
             }
+        }
+#pragma unroll
+        for (int u = 0; u < U; u++) {
+            const long long k0 = kbase + 256 * u;
+            if (k0 >= kld) break;
+            int8_t o[8];
 #pragma unroll
             for (int e = 0; e < 8; e++) {
-                o[e] = (k0 + e < K) ? act_value<T>(v[e], mode) : (int8_t)0;
+                o[e] = (k0 + e < K) ? act_value<T>(v[u][e], mode) : (int8_t)0;
                 sum += o[e];
             }
-        } else {
-#pragma unroll
-            for (int e = 0; e < 8; e++) o[e] = 0;
+            *reinterpret_cast<uint2*>(dp + k0) = *reinterpret_cast<const uint2*>(o);
         }
-        *reinterpret_cast<uint2*>(dp + k0) = *reinterpret_cast<const uint2*>(o);
     }
 #pragma unroll
     for (int off = 16; off > 0; off >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, off);
