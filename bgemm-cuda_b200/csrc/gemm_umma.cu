@@ -63,8 +63,8 @@ struct Cfg {
     static constexpr int TMEM_COLS = pow2_ceil(D_COLS + A_STAGE_COLS * A_STAGES);
     static constexpr int B_STAGE_BYTES = NT * 256;
     static constexpr bool ONE_PER_SM = TMEM_BUDGET == 512;
-    static constexpr int B_STAGES = NT <= 32 ? 8 : (NT == 64 ? (ONE_PER_SM ? 6 : 4) : (NT == 128 ? (ONE_PER_SM ? 4 : 2) : 3));
-    static constexpr int W_STAGES = NT == 256 ? 4 : 8;
+    static constexpr int B_STAGES = NT <= 32 ? 8 : (NT == 64 ? (ONE_PER_SM ? 6 : 4) : (NT == 128 ? (ONE_PER_SM ? 5 : 3) : 3));
+    static constexpr int W_STAGES = NT == 256 ? 4 : ((NT == 128 && !ONE_PER_SM) ? 2 : 8);
     // Tiles of 256 columns are bound by UMMA execution even with one issuer; narrower ones use two.
     static constexpr int NMMA = NT == 256 ? 1 : 2;
     static constexpr int NBARS = 2 * W_STAGES + 2 * B_STAGES + 2 * A_STAGES + 2;
@@ -82,7 +82,6 @@ struct Cfg {
     // served by the same set, so every waiter has seen the previous phase of the barrier it waits on; with an
     // odd count a set's first wait on a barrier would name phase 1 and pass before phase 0 has completed.
     static_assert(W_STAGES % 2 == 0 && A_STAGES % (2 * G) == 0, "stage counts shared by the two unpack sets must keep stage -> set fixed");
-    static_assert(NMMA == 1 || B_STAGES % 2 == 0, "activation stages shared by the two UMMA issuers must keep stage -> issuer fixed");
     static_assert(TMEM_COLS <= 512, "tensor memory budget");
     static_assert(NT % 16 == 0 && NT >= 16 && NT <= 256, "UMMA N");
     static_assert(NBARS * 8 <= 512, "barrier area");
@@ -283,7 +282,9 @@ __global__ void __launch_bounds__(kGemmThreads, Cfg<NT, POW2, DEEP>::MIN_CTAS) g
         for (int i = lane; i < C::NBARS; i += 32) {
             const bool four = (i >= C::W_STAGES && i < 2 * C::W_STAGES) ||
                               (i >= 2 * C::W_STAGES + 2 * C::B_STAGES && i < 2 * C::W_STAGES + 2 * C::B_STAGES + C::A_STAGES);
-            mbar_init(w_full + 8 * i, four ? 4 : (i == C::NBARS - 2 ? C::NMMA : 1));       // d_full collects one commit per issuer
+            const bool per_issuer = i == C::NBARS - 2 ||                                              // d_full
+                                    (i >= 2 * C::W_STAGES + C::B_STAGES && i < 2 * C::W_STAGES + 2 * C::B_STAGES);   // b_empty
+            mbar_init(w_full + 8 * i, four ? 4 : (per_issuer ? C::NMMA : 1));
         }
         if (lane == 0) { *abort_flag = 0; *last_flag = 0; }
         mbar_fence_init();
@@ -362,9 +363,15 @@ __global__ void __launch_bounds__(kGemmThreads, Cfg<NT, POW2, DEEP>::MIN_CTAS) g
             // Integer accumulation commutes, so the two issuers need no mutual order -- except that the UMMAs of K
             // block 0 overwrite the accumulators (accumulate = 0) and must run before anything is added.
             if (me == 1 && nkb > 1) ok = mbar_wait(first_done, 0, abort_flag, p.status, 18);
-            for (int i = me; i < nkb && ok; i += C::NMMA) {
+            for (int i = 0; i < nkb && ok; i++) {
                 const int bs = i % C::B_STAGES;
+                // Both issuers observe EVERY phase of every activation barrier and both release it (the owner of the K
+                // block through tcgen05.commit after its UMMAs, the other with a plain arrive): the producer cannot
+                // refill a stage -- and its barrier cannot advance -- before both have seen the phase, so a parity
+                // wait can never be a phase behind. That keeps the stage count free of parity constraints.
                 BGEMM_TIMED(twb, ok = mbar_wait(b_full + 8 * bs, (i / C::B_STAGES) & 1, abort_flag, p.status, 14));
+                if (!ok) break;
+                if ((i % C::NMMA) != me) { mbar_arrive(b_empty + 8 * bs); continue; }
                 const uint32_t bbase = smem_u32(sB + bs * C::B_STAGE_BYTES);
 #pragma unroll
                 for (int g = 0; g < C::G && ok; g++) {

@@ -37,8 +37,8 @@ __device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
     return ok != 0;
 }
 
-// Wait budget in SM clocks (~1 s at 2 GHz). Far above any legitimate wait of these kernels.
-constexpr long long kWaitBudgetClocks = 2000000000LL;
+// Wait budget in SM clocks (~0.2 s at 2 GHz). Far above any legitimate wait of these kernels.
+constexpr long long kWaitBudgetClocks = 400000000LL;
 
 // One blocking probe: the thread is suspended by the hardware (no issue slots burnt) until the phase
 // completes or a short, implementation-defined time passes.
