@@ -47,9 +47,9 @@ WORKLOADS = {
     "c5n4096": (28672, 8192, 4096, "bwta", "LLM projection 28672x8192, ternary X, N=4096"),
 }
 L2_BYTES = 126 * 1024 * 1024
-# dram__bytes_read.sum + dram__bytes_write.sum of ONE batched gemm_kernel launch of the workload, from the ncu
-# capture summarised under profiles/ (null until a capture of that workload exists).
-NCU_DRAM_BYTES_PER_LAUNCH = {}
+# dram__bytes_read.sum + dram__bytes_write.sum per layer of a batched gemm_kernel launch, from the ncu capture summarised
+# under profiles/ (80 layers captured; traffic grows in proportion to the layer count). Workloads without a capture: null.
+NCU_DRAM_BYTES_PER_LAYER = {"c2": 269.76e6 / 80}     # profiles/gemm_kernel_bwta_4096x4096x128_batched80.md
 METRIC = "bwta_effective_tops"
 UNIT = "TOPS (2*M*N*K/s)"
 
@@ -360,13 +360,13 @@ def main():
     t_tensor, t_hbm = ops_layer / (int8_peak * 1e12), bytes_layer / (peaks["hbm_gbs"] * 1e9)
     if t_tensor >= t_hbm:
         roofline = {"bound": "tensor", "achieved": gemm_tops, "peak": int8_peak, "unit": "TFLOP/s", "frac": gemm_tops / int8_peak,
-                    "traffic": NCU_DRAM_BYTES_PER_LAUNCH.get(args.workload),
+                    "traffic": (NCU_DRAM_BYTES_PER_LAYER[args.workload] * layers if args.workload in NCU_DRAM_BYTES_PER_LAYER else None),
                     "peak_source": f"2 x sustained bf16 GEMM peak ({peaks['source']}; the int8 pipe runs at twice the bf16 rate); burst "
                                    f"2 x {peaks['bf16_tflops']}; tcgen05 kind::i8 issue-rate microbenchmark on this pool: 3873",
                     "ops": "integer multiply-adds x 2"}
     else:
         roofline = {"bound": "hbm", "achieved": gemm_gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": gemm_gbs / peaks["hbm_gbs"],
-                    "traffic": NCU_DRAM_BYTES_PER_LAUNCH.get(args.workload), "peak_source": peaks["source"]}
+                    "traffic": (NCU_DRAM_BYTES_PER_LAYER[args.workload] * layers if args.workload in NCU_DRAM_BYTES_PER_LAYER else None), "peak_source": peaks["source"]}
     roofline.update({"kernel": "gemm_kernel (tcgen05 kind::i8, A operand unpacked into tensor memory)", "launch_us": launch_us,
                      "layers_per_launch": layers, "bytes_alg_per_launch": bytes_layer * layers, "ops_per_launch": ops_layer * layers,
                      "kernel_gbs": gemm_gbs, "kernel_tops": gemm_tops})
