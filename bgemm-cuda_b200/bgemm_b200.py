@@ -53,6 +53,8 @@ lib.bgemm_gemm_auto_split_k.argtypes = [_i64, _i64, _i64, _i64]
 lib.bgemm_linear_forward.argtypes = [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _int, _int, _int, _vp, _int, _vp, _sz]
 lib.bgemm_linear_workspace_bytes.restype = _sz
 lib.bgemm_linear_workspace_bytes.argtypes = [_i64, _i64, _i64, _int]
+lib.bgemm_device_status.restype = _int
+lib.bgemm_device_status.argtypes = [_int]
 
 
 class BgemmError(RuntimeError):

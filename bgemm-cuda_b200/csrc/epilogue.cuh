@@ -1,0 +1,144 @@
+// Epilogue helpers shared by the GEMM kernels: an accumulator tile staged in shared (or global) memory as
+// int32 [columns][128] is summed over K partitions, mapped to the op's result (D or colsum - 2 D), scaled per row
+// where asked, and stored with 16-byte coalesced stores in either output layout.
+#pragma once
+#include <cuda_fp16.h>
+
+#include "internal.h"
+
+namespace bgemm {
+
+// ---- epilogue: converting and storing 8 results --------------------------------------------------------------
+struct TileOut {
+    const GemmParams* p;
+    const float* s_alpha;    // [128] per-row scale of this tile (1 when unused)
+    const int* s_colsum;     // [NT] column sums of this tile (0 when unused)
+    int batch, m_base, n_base;
+};
+
+// 8 consecutive rows m0..m0+7 (tile-local) of column n (tile-local): the [N, M] layout.
+__device__ __forceinline__ void store8_rows(const TileOut& t, int n, int m0, const int (&acc)[8]) {
+    const GemmParams& p = *t.p;
+    const int gn = t.n_base + n, gm = t.m_base + m0;
+    if (gn >= p.N || gm >= p.M) return;
+    const int cs = t.s_colsum[n];
+    int val[8];
+#pragma unroll
+    for (int q = 0; q < 8; q++) val[q] = p.epi ? cs - 2 * acc[q] : acc[q];
+    const size_t idx = (size_t)t.batch * p.M * p.N + (size_t)gn * p.M + gm;
+    const bool full = gm + 8 <= p.M;
+    if (p.out_kind == BGEMM_OUT_I32) {
+        int* o = reinterpret_cast<int*>(p.out) + idx;
+        if (full && (reinterpret_cast<uintptr_t>(o) & 15) == 0) {
+            reinterpret_cast<int4*>(o)[0] = make_int4(val[0], val[1], val[2], val[3]);
+            reinterpret_cast<int4*>(o)[1] = make_int4(val[4], val[5], val[6], val[7]);
+        } else {
+#pragma unroll
+            for (int q = 0; q < 8; q++) if (gm + q < p.M) o[q] = val[q];
+        }
+    } else {
+        __align__(16) __half h[8];
+#pragma unroll
+        for (int q = 0; q < 8; q++)
+            h[q] = __float2half_rn(p.out_kind == BGEMM_OUT_F16 ? (float)val[q] : (float)val[q] * t.s_alpha[m0 + q]);
+        __half* o = reinterpret_cast<__half*>(p.out) + idx;
+        if (full && (reinterpret_cast<uintptr_t>(o) & 15) == 0) {
+            *reinterpret_cast<uint4*>(o) = *reinterpret_cast<const uint4*>(h);
+        } else {
+#pragma unroll
+            for (int q = 0; q < 8; q++) if (gm + q < p.M) o[q] = h[q];
+        }
+    }
+}
+
+// 8 consecutive columns n0..n0+7 (tile-local) of row m (tile-local): the [M, N] layout.
+__device__ __forceinline__ void store8_cols(const TileOut& t, int m, int n0, const int (&acc)[8]) {
+    const GemmParams& p = *t.p;
+    const int gm = t.m_base + m, gn = t.n_base + n0;
+    if (gm >= p.M || gn >= p.N) return;
+    int val[8];
+#pragma unroll
+    for (int q = 0; q < 8; q++) val[q] = p.epi ? t.s_colsum[n0 + q] - 2 * acc[q] : acc[q];
+    const size_t idx = (size_t)t.batch * p.M * p.N + (size_t)gm * p.N + gn;
+    const bool full = gn + 8 <= p.N;
+    if (p.out_kind == BGEMM_OUT_I32) {
+        int* o = reinterpret_cast<int*>(p.out) + idx;
+        if (full && (reinterpret_cast<uintptr_t>(o) & 15) == 0) {
+            reinterpret_cast<int4*>(o)[0] = make_int4(val[0], val[1], val[2], val[3]);
+            reinterpret_cast<int4*>(o)[1] = make_int4(val[4], val[5], val[6], val[7]);
+        } else {
+#pragma unroll
+            for (int q = 0; q < 8; q++) if (gn + q < p.N) o[q] = val[q];
+        }
+    } else {
+        const float a = t.s_alpha[m];
+        __align__(16) __half h[8];
+#pragma unroll
+        for (int q = 0; q < 8; q++) h[q] = __float2half_rn(p.out_kind == BGEMM_OUT_F16 ? (float)val[q] : (float)val[q] * a);
+        __half* o = reinterpret_cast<__half*>(p.out) + idx;
+        if (full && (reinterpret_cast<uintptr_t>(o) & 15) == 0) {
+            *reinterpret_cast<uint4*>(o) = *reinterpret_cast<const uint4*>(h);
+        } else {
+#pragma unroll
+            for (int q = 0; q < 8; q++) if (gn + q < p.N) o[q] = h[q];
+        }
+    }
+}
+
+// Sum `parts` partial tiles (each `stride` ints apart, starting at `base`) over 8 consecutive rows at element
+// offset `off` of a [columns][128] int32 tile. GLOBAL: the tiles are slabs in global memory (L2 reads).
+template <bool GLOBAL>
+__device__ __forceinline__ void gather8_rows(const int* base, int parts, int stride, int off, int (&acc)[8]) {
+#pragma unroll
+    for (int q = 0; q < 8; q++) acc[q] = 0;
+#pragma unroll 4
+    for (int s = 0; s < parts; s++) {
+        const int4* g = reinterpret_cast<const int4*>(base + (size_t)s * stride + off);
+        const int4 a = GLOBAL ? __ldcg(g) : g[0];
+        const int4 b = GLOBAL ? __ldcg(g + 1) : g[1];
+        acc[0] += a.x; acc[1] += a.y; acc[2] += a.z; acc[3] += a.w; acc[4] += b.x; acc[5] += b.y; acc[6] += b.z; acc[7] += b.w;
+    }
+}
+
+// The same over 8 consecutive columns c0..c0+7 of row m.
+template <bool GLOBAL>
+__device__ __forceinline__ void gather8_cols(const int* base, int parts, int stride, int c0, int m, int (&acc)[8]) {
+#pragma unroll
+    for (int q = 0; q < 8; q++) acc[q] = 0;
+#pragma unroll 2
+    for (int s = 0; s < parts; s++) {
+        const int* g = base + (size_t)s * stride + c0 * 128 + m;
+#pragma unroll
+        for (int q = 0; q < 8; q++) acc[q] += GLOBAL ? __ldcg(g + q * 128) : g[q * 128];
+    }
+}
+
+// Convert and store `ncols` columns with `nthreads` epilogue threads (`et` = this thread's index among them).
+// Column c of the partial tiles at `base` is tile column n_first + c.
+template <bool GLOBAL>
+__device__ __forceinline__ void write_tile(const TileOut& t, const int* base, int parts, int stride, int n_first, int ncols, int et, int nthreads) {
+    const GemmParams& p = *t.p;
+    if (p.out_layout == BGEMM_LAYOUT_NM) {
+        const int units = ncols * 16;                           // (column, 8-row chunk)
+#pragma unroll 1
+        for (int u = et; u < units; u += nthreads) {
+            const int c = u >> 4, m0 = (u & 15) * 8;
+            if (t.n_base + n_first + c >= p.N || t.m_base + m0 >= p.M) continue;
+            int acc[8];
+            gather8_rows<GLOBAL>(base, parts, stride, c * 128 + m0, acc);
+            store8_rows(t, n_first + c, m0, acc);
+        }
+    } else {
+        const int units = (ncols >> 3) * 128;                   // (8-column chunk, row)
+#pragma unroll 1
+        for (int u = et; u < units; u += nthreads) {
+            const int m = u & 127, c0 = (u >> 7) * 8;
+            if (t.n_base + n_first + c0 >= p.N || t.m_base + m >= p.M) continue;
+            int acc[8];
+            gather8_cols<GLOBAL>(base, parts, stride, c0, m, acc);
+            store8_cols(t, m, n_first + c0, acc);
+        }
+    }
+}
+
+}  // namespace bgemm

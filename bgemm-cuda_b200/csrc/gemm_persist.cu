@@ -1,0 +1,382 @@
+// Persistent variant of the binary-weight GEMM for launches with many output tiles (pools of layers or heads,
+// wide activation matrices): one CTA per SM walks over tiles t = blockIdx.x, blockIdx.x + gridDim.x, ... and
+// keeps the operand pipeline running across tile boundaries, while the finished accumulator of the previous
+// tile is converted and stored by separate warps. The per-tile set-up, pipeline fill and epilogue that the
+// one-tile-per-CTA kernel pays for every 128 x NT tile are paid once per CTA here.
+//
+// Same math and operand formats as gemm_kernel (gemm_umma.cu); replaces the same reference code
+// (PACK_BGEMM_Kernel, lowbit_kernel/csrc/include/kernel_matmul.cuh:370-547).
+//
+// Tensor memory (all 512 columns): two accumulators of NT columns (tile t is accumulated into buffer t & 1 while the
+// epilogue drains the other one) and a ring of u8 weight operand stages of 64 columns.
+//   warps 0-7    unpack, two sets taking alternate K blocks of the CTA's whole K-block stream
+//   warps 8-11   epilogue: accumulator -> shared memory staging tile -> scaled / converted 16-byte stores
+//   warp 12      tensor-memory allocation; one lane issues the UMMAs of the even K blocks of the stream
+//   warp 15      one lane issues the UMMAs of the odd K blocks
+//   warp 13      one lane streams the packed weight tiles (cp.async.bulk)
+//   warp 14      one lane loads the activation tiles (TMA, 128B swizzle)
+// All rings are indexed by the running K-block number g of the CTA, so nothing drains between tiles.
+#include <cuda.h>
+#include <cuda_fp16.h>
+
+#include "epilogue.cuh"
+#include "internal.h"
+#include "prof.cuh"
+#include "ptx.cuh"
+
+namespace bgemm {
+
+// Event trace of CTA 0 (tuning aid, behind the per-CTA slots of the profile buffer): event `ev`, occurrence `idx`.
+#define BGEMM_TRACE(ev, idx)                                                                                        \
+    do {                                                                                                            \
+        if (p.prof && blockIdx.x == 0 && (idx) < 1024) p.prof[(size_t)gridDim.x * 32 + (ev) * 1024 + (idx)] = clock64() - t_cta0; \
+    } while (0)
+
+constexpr int kPThreads = 512;
+constexpr int kPEpiThreads = 128;
+constexpr int kPWarpEpi = 8, kPWarpMma0 = 12, kPWarpW = 13, kPWarpB = 14, kPWarpMma1 = 15;
+constexpr long long kCopyDrainClocks = 4000000;   // ~2 ms: far beyond any TMA copy of a 32 KB tile
+
+template <int NT>
+struct PCfg {
+    // One ring of S operand stages: stage s holds the activation tile of a K block in shared memory (NT x 256 B) and
+    // the unpacked weight operand of the same K block in tensor memory (64 columns). Filling it takes one arrival
+    // of the activation producer (with the TMA byte count) and one of each unpack warp of the set; one
+    // tcgen05.commit of the issuer frees both halves. The issuing threads are a scarce resource -- a UMMA costs its
+    // issuer ~85 clocks, a commit ~80, a barrier wait ~100 even when it does not block -- so each K block costs its
+    // issuer one wait, eight UMMAs and one commit and nothing else.
+    static constexpr int A_STAGE_COLS = 64;
+    static constexpr int S_FIT = ((512 - 2 * NT) / A_STAGE_COLS) / 2 * 2;
+    static constexpr int STAGES = S_FIT > 6 ? 6 : S_FIT;
+    static constexpr int A_COL0 = 2 * NT;
+    static constexpr int B_STAGE_BYTES = NT * 256;
+    static constexpr int W_STAGES = 6;
+    static constexpr int STAGE_TILE_BYTES = NT * 128 * 4;
+    // w_full/w_empty, full/empty, d_full[2], d_empty[2], first_done[2], drained
+    static constexpr int NBARS = 2 * W_STAGES + 2 * STAGES + 7;
+    static constexpr int MISC_BYTES = 512 /*barriers*/ + 512 /*alpha*/ + 1024 /*colsum*/ + 512 /*flags*/;
+    static constexpr int SMEM_BYTES = STAGES * B_STAGE_BYTES + W_STAGES * 4096 + STAGE_TILE_BYTES + MISC_BYTES + 1024 /*align*/;
+    // K block g of the CTA's stream uses stage g % STAGES, is unpacked by set g % 2 and issued by issuer g % 2:
+    // with even stage counts a stage and its barriers always meet the same set and the same issuer, so every
+    // parity wait has seen the previous phase of its barrier.
+    static_assert(W_STAGES % 2 == 0 && STAGES % 2 == 0 && STAGES >= 2, "stage -> unpack set / issuer must stay fixed");
+    static_assert(NBARS * 8 <= 512, "barrier area");
+    static_assert(SMEM_BYTES <= 227 * 1024, "shared memory budget");
+    // More than half of an SM's shared memory: at most one CTA per SM, so the 512-column allocation never waits
+    // for a co-resident CTA of this kernel.
+    static_assert(SMEM_BYTES > 114 * 1024, "one CTA per SM");
+};
+
+template <int NT>
+__global__ void __launch_bounds__(kPThreads, 1) gemm_persist_kernel(const __grid_constant__ CUtensorMap tmap_acts, const GemmParams p, const long long total_tiles) {
+    using C = PCfg<NT>;
+    const long long t_cta0 = clock64();
+    grid_launch_dependents();
+    if (threadIdx.x == 0) BGEMM_STAMP(10);
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint8_t* sB = smem;
+    uint8_t* sW = sB + C::STAGES * C::B_STAGE_BYTES;
+    int* sP = reinterpret_cast<int*>(sW + C::W_STAGES * 4096);
+    uint8_t* misc = reinterpret_cast<uint8_t*>(sP) + C::STAGE_TILE_BYTES;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(misc);
+    float* s_alpha = reinterpret_cast<float*>(misc + 512);
+    int* s_colsum = reinterpret_cast<int*>(misc + 1024);
+    uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(misc + 2048);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
+
+    const uint32_t w_full = smem_u32(bars);
+    const uint32_t w_empty = w_full + 8 * C::W_STAGES;
+    const uint32_t full = w_empty + 8 * C::W_STAGES;     // [S] operand stage filled (activation bytes + four unpack warps)
+    const uint32_t empty = full + 8 * C::STAGES;         // [S] operand stage consumed (one commit)
+    const uint32_t d_full = empty + 8 * C::STAGES;       // [2] accumulator buffer complete (one commit per issuer)
+    const uint32_t d_empty = d_full + 16;                // [2] accumulator buffer read out (one arrive per epilogue warp)
+    const uint32_t first_done = d_empty + 16;            // [2] per buffer: the K block that zeroes it has been executed
+    const uint32_t drained = first_done + 16;            // every UMMA of the CTA has been executed (one commit per issuer)
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int nkb = p.kblocks;
+    // tiles of this CTA: blockIdx.x, blockIdx.x + gridDim.x, ... (tile index = (batch * mtiles + mt) * ntiles + nt)
+    const long long my_tiles = (total_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x;
+
+    if (warp == 0) {
+        for (int i = lane; i < C::NBARS; i += 32) {
+            const int f0 = 2 * C::W_STAGES, d0 = f0 + 2 * C::STAGES;
+            int count = 1;
+            if (i >= C::W_STAGES && i < 2 * C::W_STAGES) count = 4;           // w_empty: unpack warps of a set
+            else if (i >= f0 && i < f0 + C::STAGES) count = 5;                // full: activation producer + unpack warps of a set
+            else if (i == d0 || i == d0 + 1) count = 2;                       // d_full: both issuers
+            else if (i == d0 + 2 || i == d0 + 3) count = 4;                   // d_empty: epilogue warps
+            else if (i == d0 + 6) count = 2;                                  // drained: both issuers
+            mbar_init(w_full + 8 * i, count);
+        }
+        if (lane == 0) *abort_flag = 0;
+        mbar_fence_init();
+    } else if (warp == kPWarpB) {
+        if (lane == 0) tma_prefetch_desc(&tmap_acts);
+    } else if (warp == kPWarpMma0) {
+        tmem_alloc(smem_u32(tmem_holder), 512);
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    grid_dependency_wait();      // nothing above touches global memory (programmatic dependent launch)
+    const uint32_t tmem = *tmem_holder;
+    const uint32_t tmem_d = tmem;
+    const uint32_t tmem_a = tmem + C::A_COL0;
+    if (tid == 0) BGEMM_STAMP(1);
+
+    if (warp == kPWarpW) {
+        // ---------------- weight producer ----------------
+        if (lane == 0) {
+            long long g = 0, tw = 0;
+            bool ok = true;
+            for (long long t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+                const long long bm = t / p.ntiles;                      // batch * mtiles + mt
+                const int mt = (int)(bm % p.mtiles), batch = (int)(bm / p.mtiles);
+                const uint8_t* src = p.plane + (size_t)batch * p.plane_batch_bytes + (size_t)mt * nkb * 4096;
+                for (int i = 0; i < nkb; i++, g++) {
+                    const int s = (int)(g % C::W_STAGES);
+                    if (g >= C::W_STAGES) BGEMM_TIMED(tw, ok = mbar_wait(w_empty + 8 * s, (uint32_t)((g / C::W_STAGES) - 1) & 1, abort_flag, p.status, 21));
+                    if (!ok) break;
+                    mbar_arrive_expect_tx(w_full + 8 * s, 4096);
+                    bulk_g2s(smem_u32(sW + s * 4096), src + (size_t)i * 4096, 4096, w_full + 8 * s);
+                }
+            }
+            BGEMM_PUT(20, tw);
+            if (*abort_flag) {  // drain own copies before the CTA may exit
+                for (long long i = g - 1; i >= 0 && i >= g - C::W_STAGES; i--) {
+                    const long long t0 = clock64();
+                    while (!mbar_test(w_full + 8 * (int)(i % C::W_STAGES), (uint32_t)(i / C::W_STAGES) & 1) && clock64() - t0 < kWaitBudgetClocks) {}
+                }
+            }
+        }
+    } else if (warp == kPWarpB) {
+        // ---------------- activation producer ----------------
+        if (lane == 0) {
+            long long g = 0, tw = 0;
+            bool ok = true;
+            for (long long t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+                const int nt = (int)(t % p.ntiles);
+                const int batch = (int)(t / p.ntiles / p.mtiles);
+                for (int i = 0; i < nkb; i++, g++) {
+                    const int s = (int)(g % C::STAGES);
+                    if (g >= C::STAGES) BGEMM_TIMED(tw, ok = mbar_wait(empty + 8 * s, (uint32_t)((g / C::STAGES) - 1) & 1, abort_flag, p.status, 22));
+                    if (!ok) break;
+                    BGEMM_TRACE(4, g);
+                    mbar_arrive_expect_tx(full + 8 * s, C::B_STAGE_BYTES);
+                    const uint32_t dst = smem_u32(sB + s * C::B_STAGE_BYTES);
+                    tma_load_3d(dst, &tmap_acts, i * 256, nt * NT, batch, full + 8 * s);
+                    tma_load_3d(dst + NT * 128, &tmap_acts, i * 256 + 128, nt * NT, batch, full + 8 * s);
+                }
+            }
+            BGEMM_PUT(21, tw);
+            if (*abort_flag) {
+                // The copies in flight must land before the CTA may exit. Their barriers also need the unpack warps,
+                // which have stopped: wait for the longest plausible copy time instead of the barrier.
+                const long long t0 = clock64();
+                while (g > 0 && clock64() - t0 < kCopyDrainClocks) {}
+            }
+        }
+    } else if (warp == kPWarpMma0 || warp == kPWarpMma1) {
+        // ---------------- UMMA issuers: issuer `me` takes the K blocks with g % 2 == me ----------------
+        const int me = warp == kPWarpMma0 ? 0 : 1;
+        if (lane == 0) {
+            constexpr uint32_t idesc = umma_idesc_u8s8(NT);
+            bool ok = true;
+            long long twf = 0, twd = 0, g = 0;
+            const long long tloop0 = clock64();
+            for (long long lt = 0; lt < my_tiles && ok; lt++) {
+                const int buf = (int)(lt & 1);
+                const uint32_t k = (uint32_t)(lt >> 1);             // use number of this accumulator buffer
+                const uint32_t d = tmem_d + buf * NT;
+                // The first K block of a tile overwrites the accumulator (accumulate = 0). Its issuer (the "opener",
+                // whoever owns that K block) waits until the epilogue has read the buffer out (tile lt - 2); the other
+                // issuer waits until that K block has been executed before it adds anything. Integer accumulation
+                // commutes, so no other order is needed.
+                // Parity waits must not name a phase the barrier has not reached. d_empty[buf]: phase k - 2 was
+                // awaited by the opener of tile lt - 2 and the other issuer waited for that tile to be opened.
+                // first_done[buf]: the waiter either waited for phase k - 1 itself (tile lt - 2) or committed it and
+                // has since reused one of its operand stages (tiles have at least STAGES K blocks, checked by the
+                // launcher), whose release was committed after first_done. Neither barrier can be two phases
+                // ahead: that needs the epilogue of tile lt, which needs this issuer's d_full commit below.
+                const bool opener = (int)(g & 1) == me;
+                if (opener) {
+                    if (k >= 1) BGEMM_TIMED(twd, ok = mbar_wait(d_empty + 8 * buf, (k - 1) & 1, abort_flag, p.status, 25));
+                } else {
+                    BGEMM_TIMED(twd, ok = mbar_wait(first_done + 8 * buf, k & 1, abort_flag, p.status, 26));
+                }
+                if (!ok) break;
+                tc_fence_after();
+                for (int i = 0; i < nkb; i++, g++) {
+                    if ((int)(g & 1) != me) continue;
+                    const int s = (int)(g % C::STAGES);
+                    BGEMM_TIMED(twf, ok = mbar_wait(full + 8 * s, (uint32_t)(g / C::STAGES) & 1, abort_flag, p.status, 23));
+                    if (!ok) break;
+                    BGEMM_TRACE(0, g);
+                    tc_fence_after();
+                    const uint32_t bbase = smem_u32(sB + s * C::B_STAGE_BYTES);
+#pragma unroll
+                    for (int j = 0; j < 8; j++) {
+                        const uint64_t bdesc = umma_desc_sw128(bbase + (j >> 2) * (NT * 128) + (j & 3) * 32);
+                        umma_i8_ts(d, tmem_a + s * C::A_STAGE_COLS + j * 8, bdesc, idesc, (i | j) ? 1u : 0u);
+                    }
+                    if (i == 0) umma_commit(first_done + 8 * buf);
+                    umma_commit(empty + 8 * s);
+                    BGEMM_TRACE(1, g);
+                }
+                if (!ok) break;
+                umma_commit(d_full + 8 * buf);
+            }
+            umma_commit(drained);
+            if (me == 0) { BGEMM_PUT(16, twf); BGEMM_PUT(24, clock64() - tloop0); BGEMM_PUT(27, twd); }
+        }
+    } else if (warp < 8) {
+        // ---------------- unpack: set 0 = warps 0-3 takes even K blocks of the stream, set 1 = warps 4-7 odd ones ----
+        const int set = warp >> 2;
+        const int r = (warp & 3) * 32 + lane;                 // weight row of the tile == tensor-memory lane
+        const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
+        const long long total_kb = my_tiles * nkb;
+        bool ok = true;
+        long long tww = 0, twe = 0;
+        const long long tloop0 = clock64();
+        for (long long g = set; g < total_kb && ok; g += 2) {
+            const int ws = (int)(g % C::W_STAGES);
+            BGEMM_TIMED(tww, ok = mbar_wait(w_full + 8 * ws, (uint32_t)(g / C::W_STAGES) & 1, abort_flag, p.status, 27));
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            if ((tid & 127) == 0) BGEMM_TRACE(5, g);
+            const uint4 lo = *reinterpret_cast<const uint4*>(sW + ws * 4096 + r * 16);
+            const uint4 hi = *reinterpret_cast<const uint4*>(sW + ws * 4096 + 2048 + r * 16);
+            fence_proxy_async_smem();     // generic-proxy reads before the producer's next bulk copy into this stage
+            __syncwarp();
+            if (lane == 0) mbar_arrive(w_empty + 8 * ws);
+            const uint32_t w[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
+            const int as = (int)(g % C::STAGES);
+            if (g >= C::STAGES) BGEMM_TIMED(twe, ok = mbar_wait(empty + 8 * as, (uint32_t)((g / C::STAGES) - 1) & 1, abort_flag, p.status, 28));
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            if ((tid & 127) == 0) BGEMM_TRACE(2, g);
+            tc_fence_after();
+#pragma unroll
+            for (int j = 0; j < 8; j++) {
+                uint32_t v[8];
+#pragma unroll
+                for (int c = 0; c < 8; c++) v[c] = (w[c] >> j) & 0x01010101u;
+                tmem_st8(tmem_a + lane_base + as * C::A_STAGE_COLS + j * 8, v);
+            }
+            tmem_wait_st();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(full + 8 * as);
+            if ((tid & 127) == 0) BGEMM_TRACE(3, g);
+        }
+        if (tid == 0) { BGEMM_PUT(18, tww); BGEMM_PUT(19, twe); BGEMM_PUT(25, clock64() - tloop0); }
+        if (tid == 128) { BGEMM_PUT(22, tww); BGEMM_PUT(23, twe); }
+    } else if (warp >= kPWarpEpi && warp < kPWarpEpi + 4) {
+        // ---------------- epilogue: overlaps the mainloop of the next tile ----------------
+        const int et = tid - kPWarpEpi * 32;                  // 0..127 == accumulator row == tensor-memory lane
+        const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
+        TileOut tout;
+        tout.p = &p; tout.s_alpha = s_alpha; tout.s_colsum = s_colsum;
+        long long twd = 0, tbusy = 0;
+        long long lt = 0;
+        for (long long t = blockIdx.x; t < total_tiles; t += gridDim.x, lt++) {
+            const int nt = (int)(t % p.ntiles);
+            const long long bm = t / p.ntiles;
+            const int mt = (int)(bm % p.mtiles), batch = (int)(bm / p.mtiles);
+            const int buf = (int)(lt & 1);
+            tout.batch = batch; tout.m_base = mt * 128; tout.n_base = nt * NT;
+            {
+                const int m = mt * 128 + et;
+                s_alpha[et] = (p.out_kind == BGEMM_OUT_F16_SCALED && m < p.M) ? __half2float(p.alpha[(size_t)batch * p.M + m]) : 1.f;
+            }
+            for (int i = et; i < NT; i += kPEpiThreads) {
+                const int n = nt * NT + i;
+                s_colsum[i] = (p.epi && n < p.N) ? __ldg(p.colsum + (size_t)batch * p.N + n) : 0;
+            }
+            bool ok;
+            BGEMM_TIMED(twd, ok = mbar_wait(d_full + 8 * buf, (uint32_t)(lt >> 1) & 1, abort_flag, p.status, 29));
+            ok = __all_sync(0xffffffffu, ok);
+            const long long tb0 = p.prof ? clock64() : 0;
+            if (ok) {
+                tc_fence_after();
+#pragma unroll 1
+                for (int n0 = 0; n0 < NT; n0 += 32) {
+                    uint32_t v0[16], v1[16];
+                    tmem_ld16(tmem_d + buf * NT + lane_base + n0, v0);
+                    tmem_ld16(tmem_d + buf * NT + lane_base + n0 + 16, v1);
+                    tmem_wait_ld();
+#pragma unroll
+                    for (int q = 0; q < 16; q++) sP[(n0 + q) * 128 + et] = (int)v0[q];
+#pragma unroll
+                    for (int q = 0; q < 16; q++) sP[(n0 + 16 + q) * 128 + et] = (int)v1[q];
+                }
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(d_empty + 8 * buf);   // the accumulator may be overwritten from here on
+            }
+            // One answer for all four warps: either everybody stores this tile or everybody leaves.
+            if (named_bar_or(2, kPEpiThreads, !ok)) break;
+            write_tile<false>(tout, sP, 1, 0, 0, NT, et, kPEpiThreads);
+            named_bar_sync(3, kPEpiThreads);                      // staging tile and scales are free for the next tile
+            if (p.prof) tbusy += clock64() - tb0;
+        }
+        if (et == 0) { BGEMM_PUT(28, twd); BGEMM_PUT(29, tbusy); }
+    }
+    if (tid == 0) BGEMM_STAMP(8);
+    tc_fence_before();
+    __syncthreads();
+    if (warp == kPWarpMma0) {
+        if (lane == 0) {   // every UMMA has been executed before the columns are freed (immediate unless a wait ran out)
+            const long long t0 = clock64();
+            while (!mbar_test(drained, 0) && clock64() - t0 < kWaitBudgetClocks) {}
+        }
+        __syncwarp();
+        tc_fence_after();
+        tmem_dealloc(tmem, 512);
+    }
+    if (tid == 0) { BGEMM_STAMP(9); BGEMM_STAMP(11); }
+}
+
+template <int NT>
+static int launch_persist_variant(cudaStream_t stream, const CUtensorMap& tmap, const GemmParams& p, long long total_tiles, int ctas) {
+    using C = PCfg<NT>;
+    if (p.kblocks < C::STAGES) return BGEMM_ERR_UNSUPPORTED;   // see the issuers' note on first_done
+    static bool configured[64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 64 && !configured[dev]) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_persist_kernel<NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
+        if (e != cudaSuccess) return (int)e;
+        configured[dev] = true;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)ctas, 1, 1);
+    cfg.blockDim = dim3(kPThreads, 1, 1);
+    cfg.dynamicSmemBytes = C::SMEM_BYTES;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    if (programmatic_launch_enabled()) {
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+    }
+    const cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_persist_kernel<NT>, tmap, p, total_tiles);
+    count_launch();
+    return (int)(e != cudaSuccess ? e : cudaGetLastError());
+}
+
+bool persistent_supported(int NT) { return NT == 64 || NT == 128; }
+
+int launch_gemm_persistent(cudaStream_t stream, const void* tensor_map, const GemmParams& p, int NT, long long total_tiles, int ctas) {
+    const CUtensorMap& tmap = *static_cast<const CUtensorMap*>(tensor_map);
+    switch (NT) {
+        case 64: return launch_persist_variant<64>(stream, tmap, p, total_tiles, ctas);
+        case 128: return launch_persist_variant<128>(stream, tmap, p, total_tiles, ctas);
+        default: return BGEMM_ERR_UNSUPPORTED;
+    }
+}
+
+}  // namespace bgemm

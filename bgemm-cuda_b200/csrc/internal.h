@@ -36,6 +36,10 @@ int* device_status_word();        // per-device status word, lazily created (cud
 int gemm_tile_n(long long N);
 int launch_gemm(cudaStream_t stream, GemmParams p, const int8_t* acts, long long act_ld, long long batch);
 
+// Persistent variant (gemm_persist.cu); `tensor_map` points to the CUtensorMap of the activations.
+bool persistent_supported(int NT);
+int launch_gemm_persistent(cudaStream_t stream, const void* tensor_map, const GemmParams& p, int NT, long long total_tiles, int ctas);
+
 int launch_pack_weights(cudaStream_t stream, const void* src, int dtype, long long M, long long K, long long ld, int wbit_mode,
                         void* plane, int32_t* rowpop, void* alpha, long long batch, long long src_batch_stride);
 int launch_prepare_acts(cudaStream_t stream, const void* src, int dtype, long long N, long long K, long long ld, int act_mode,

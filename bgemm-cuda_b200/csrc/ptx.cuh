@@ -80,6 +80,11 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst_smem, const CUtensorMap
         "l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(bar)
         : "memory");
 }
+// Orders this thread's generic-proxy accesses to shared memory (ld/st.shared) with async-proxy accesses (TMA, bulk
+// copies) that follow in synchronisation order: needed before a TMA store reads what threads wrote, and before a
+// buffer that threads have READ is handed back to a producer whose next bulk copy overwrites it -- an mbarrier
+// arrive alone does not order the two proxies.
+__device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 __device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* map) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
 }
@@ -167,6 +172,17 @@ __device__ __forceinline__ int ld_dsmem_s32(uint32_t addr) {
 }
 __device__ __forceinline__ void named_bar_sync(int id, int nthreads) {
     asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
+}
+// Barrier over `nthreads` threads that also ORs a predicate: every participant gets the same answer, so a
+// group can leave a loop together when any member has given up.
+__device__ __forceinline__ bool named_bar_or(int id, int nthreads, bool pred) {
+    uint32_t r;
+    asm volatile(
+        "{\n.reg .pred p, q;\nsetp.ne.b32 q, %3, 0;\nbar.red.or.pred p, %1, %2, q;\nselp.u32 %0, 1, 0, p;\n}\n"
+        : "=r"(r)
+        : "r"(id), "r"(nthreads), "r"((uint32_t)pred)
+        : "memory");
+    return r != 0;
 }
 
 }  // namespace bgemm

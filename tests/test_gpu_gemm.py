@@ -235,6 +235,73 @@ def test_batched_attention_heads(B):
     assert torch.equal(got, O.ref_attn_heads(a, v))
 
 
+def test_late_waves_mn_int32_every_run(B):
+    """More tiles than the GPU holds at once, [M, N] int32 output (the slowest epilogue), repeated: tiles of the
+    later waves run next to CTAs that are storing, which once let a weight stage be refilled before a stalled warp
+    had read it (32 rows of a tile wrong in ~45 % of the runs). Every run must equal the oracle bit for bit."""
+    M, K, N = 4096, 2048, 2048
+    g = O._gen(4242)
+    w = O.rand_pm1((M, K), g)
+    x = O.rand_ternary((N, K), g)
+    ref = O.ref_acc(w, x, O.OP_BWTA).t().contiguous()
+    plane, _, _ = B.pack_weights(w.cuda(), B.WBIT_OF_OP[O.OP_BWTA])
+    acts, colsum = B.prepare_acts(x.cuda(), B.ACT_MODE_OF_OP[O.OP_BWTA])
+    for rep in range(12):
+        got = B.gemm(plane, M, K, acts, colsum, O.OP_BWTA, O.OUT_I32, 1, None, 1).cpu()
+        assert torch.equal(got, ref), f"run {rep}: {int((got != ref).sum())} elements differ"
+    assert B.lib.bgemm_device_status(1) == 0
+
+
+@pytest.mark.parametrize("M,K,N,batch,layout", [(512, 2048, 128, 80, 0), (384, 2304, 104, 80, 1), (1000, 2048, 100, 40, 0),
+                                                (256, 4096, 64, 200, 0), (128, 2304, 64, 333, 1), (100, 2048, 40, 150, 0)])
+def test_pools_on_the_persistent_kernel(B, M, K, N, batch, layout):
+    """Pools of narrow problems in one launch (more tiles than SMs, one tile across N, >= 8 K blocks) take the
+    persistent kernel: odd K-block counts, ragged M and N, both layouts, all three output kinds."""
+    g = O._gen(M + K + N + batch)
+    w = O.rand_pm1((batch, M, K), g)
+    x = O.rand_ternary((batch, N, K), g)
+    alpha = (torch.rand(batch, M, generator=g) + 0.5).to(torch.float16)
+    acc = O.ref_acc(w, x, O.OP_BWTA)                                   # [batch, N, M]
+    plane, _, _ = B.pack_weights(w.cuda(), B.WBIT_OF_OP[O.OP_BWTA])
+    acts, colsum = B.prepare_acts(x.cuda(), B.ACT_MODE_OF_OP[O.OP_BWTA])
+    for kind in (O.OUT_I32, O.OUT_F16, O.OUT_F16_SCALED):
+        want = O.ref_out(acc, kind, alpha.unsqueeze(1))
+        if layout == 1:
+            want = want.transpose(1, 2)
+        got = B.gemm(plane, M, K, acts, colsum, O.OP_BWTA, kind, layout, alpha.cuda(), 1).cpu()
+        assert got.shape == want.shape
+        if kind != O.OUT_I32:
+            assert torch.allclose(got.float(), want.float(), rtol=1e-3, atol=0)
+        assert torch.equal(got, want), (kind, int((got != want).sum()))
+    assert B.lib.bgemm_device_status(1) == 0
+
+
+def test_persistent_kernel_under_graph_replay(B):
+    """The persistent kernel's barrier rings across many tiles, replayed back to back from a CUDA graph."""
+    M, K, N, batch = 1024, 2304, 128, 60
+    g = O._gen(77)
+    w = O.rand_pm1((batch, M, K), g)
+    x = O.rand_ternary((batch, N, K), g)
+    ref = O.ref_acc(w, x, O.OP_BWTA)
+    plane, _, _ = B.pack_weights(w.cuda(), B.WBIT_OF_OP[O.OP_BWTA])
+    acts, colsum = B.prepare_acts(x.cuda(), B.ACT_MODE_OF_OP[O.OP_BWTA])
+    out = torch.empty((batch, N, M), dtype=torch.int32, device="cuda")
+    B.gemm(plane, M, K, acts, colsum, O.OP_BWTA, O.OUT_I32, 0, None, 1, out=out)
+    torch.cuda.synchronize()
+    s = torch.cuda.Stream()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(s):
+        with torch.cuda.graph(graph, stream=s):
+            for _ in range(10):
+                B.gemm(plane, M, K, acts, colsum, O.OP_BWTA, O.OUT_I32, 0, None, 1, out=out)
+    for _ in range(3):
+        out.fill_(-1)
+        graph.replay()
+        torch.cuda.synchronize()
+        assert torch.equal(out.cpu(), ref)
+    assert B.lib.bgemm_device_status(1) == 0
+
+
 def test_argument_errors(B):
     x = torch.zeros(4, 256, dtype=torch.float16, device="cuda")
     assert B.lib.bgemm_pack_weights(None, None, 0, 4, 256, 256, 0, x.data_ptr(), None, None, 1, 0) == -1
