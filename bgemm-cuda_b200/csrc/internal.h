@@ -33,6 +33,7 @@ bool programmatic_launch_enabled();   // BGEMM_PDL=0 in the environment switches
 long long* debug_profile_buffer();
 int* device_status_word();        // per-device status word, lazily created (cudaGetSymbolAddress)
 
+int sm_count();                   // SMs of the current device (cached)
 int gemm_tile_n(long long N);
 int launch_gemm(cudaStream_t stream, GemmParams p, const int8_t* acts, long long act_ld, long long batch);
 

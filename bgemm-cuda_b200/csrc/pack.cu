@@ -53,6 +53,15 @@ __host__ __device__ __forceinline__ int weight_bit(const T& v, int mode) {
     return mode == BGEMM_WBIT_NONZERO ? nz : (neg & nz);
 }
 
+// Weight-slot bits of two 16-bit floats (fp16 or bf16) held in one 32-bit word: bit 0 = low element, bit 16 = high.
+__device__ __forceinline__ uint32_t weight_bits_x2(uint32_t w, int mode) {
+    const uint32_t s = (w >> 15) & 0x00010001u;
+    if (mode == BGEMM_WBIT_NEGATIVE) return s;
+    if (mode == BGEMM_WBIT_NONNEGATIVE) return s ^ 0x00010001u;
+    const uint32_t nz = (((w & 0x7fff7fffu) + 0x7fff7fffu) >> 15) & 0x00010001u;
+    return mode == BGEMM_WBIT_NONZERO ? nz : (nz & s);
+}
+
 // ---- weights -> tiled plane (+ rowpop, alpha) ---------------------------------------------------------------
 // One warp per row of the padded matrix. Lane L reads elements k = 256 kb + 8 L + e (e = 0..7): slice
 // j = L / 4, words c = 2 (L % 4) + e / 4, byte b = e % 4 -> bit 8 b + j. Words are completed by OR-ing
@@ -100,7 +109,18 @@ __global__ void __launch_bounds__(256) pack_weights_kernel(const T* __restrict__
             if (kb >= kblocks) break;
             const long long k0 = kb * 256 + lane * 8;
             uint32_t w0 = 0, w1 = 0;
-            if (live && k0 < K) {
+            if (live && vec_ok && k0 + 8 <= K) {
+                // element e of the lane -> bit 8 (e % 4) + j of word e / 4, two elements per operation
+                const uint4 raw = *reinterpret_cast<const uint4*>(v[u]);
+                const uint32_t q0 = weight_bits_x2(raw.x, mode), q1 = weight_bits_x2(raw.y, mode);
+                const uint32_t q2 = weight_bits_x2(raw.z, mode), q3 = weight_bits_x2(raw.w, mode);
+                w0 = ((((q0 | (q0 >> 8)) & 0x101u) | (((q1 | (q1 >> 8)) & 0x101u) << 16))) << j;
+                w1 = ((((q2 | (q2 >> 8)) & 0x101u) | (((q3 | (q3 >> 8)) & 0x101u) << 16))) << j;
+                if (alpha) {
+#pragma unroll
+                    for (int e = 0; e < 8; e++) mag += Elem<T>::mag(v[u][e]);
+                }
+            } else if (live && k0 < K) {
 #pragma unroll
                 for (int e = 0; e < 8; e++) {
                     if (k0 + e < K) {
@@ -143,53 +163,108 @@ __device__ __forceinline__ int8_t act_value(const T& v, int mode) {
     return (int8_t)neg;
 }
 
-// One warp per row; lane handles 8 consecutive elements per step and writes them as one 8-byte store.
+// Eight 16-bit floats (fp16 or bf16: same sign / zero tests) -> eight int8 activation values, two elements per 32-bit
+// operation. Per 16-bit lane: t = "not +-0", s = sign bit; the value byte is 0x00, 0x01 or 0xFF (= 0x01 | 0xFE).
+// Returns the signed sum of the eight values as well (dp4a).
+__device__ __forceinline__ uint2 act_values_x8(const uint4& w, int mode, int& sum) {
+    const uint32_t in[4] = {w.x, w.y, w.z, w.w};
+    uint32_t b[4];
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        const uint32_t s = (in[i] >> 15) & 0x00010001u;
+        if (mode == BGEMM_ACT_NEG01) {
+            b[i] = s;
+        } else {
+            const uint32_t mag = in[i] & 0x7fff7fffu;
+            const uint32_t t = mode == BGEMM_ACT_SIGN ? 0x00010001u : (((mag + 0x7fff7fffu) >> 15) & 0x00010001u);
+            const uint32_t m = t & s;
+            b[i] = t | ((m << 8) - (m << 1));
+        }
+    }
+    uint2 o;
+    o.x = __byte_perm(b[0], b[1], 0x6420);      // low bytes of the four 16-bit lanes, in element order
+    o.y = __byte_perm(b[2], b[3], 0x6420);
+    sum = __dp4a((int)o.x, 0x01010101, sum);
+    sum = __dp4a((int)o.y, 0x01010101, sum);
+    return o;
+}
+
+// Activation rows (rows of all batches numbered through) -> int8 rows + column sums. The launcher picks the split:
+// many rows: a warp converts `rows_per_warp` consecutive rows, sized so that the launch is one resident wave (with
+// one short row per warp a launch of 1.3 waves ran its last third on a nearly idle GPU); few rows: `warps_per_row`
+// (2, 4 or 8) warps of a CTA share a row by 256-column blocks and add their partial sums through shared memory, so
+// that a handful of long rows still puts loads from every SM in flight. A lane handles 8 consecutive elements per
+// step (one 16-byte streaming load for 2-byte types, one 8-byte store) and keeps eight such loads in flight.
 template <typename T>
-__global__ void __launch_bounds__(256) prepare_acts_kernel(const T* __restrict__ src, long long N, long long K, long long ld, int mode,
+__global__ void __launch_bounds__(256, 4) prepare_acts_kernel(const T* __restrict__ src, long long N, long long K, long long ld, int mode,
                                                            int8_t* __restrict__ dst, int32_t* __restrict__ colsum,
-                                                           long long src_batch_stride) {
+                                                           long long src_batch_stride, long long total_rows, int rows_per_warp,
+                                                           int warps_per_row) {
+    __shared__ int part[8];
     grid_launch_dependents();
     grid_dependency_wait();
-    const int lane = threadIdx.x & 31;
-    const long long row = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-    const long long batch = blockIdx.y;
-    if (row >= N) return;
+    const int lane = threadIdx.x & 31, wib = threadIdx.x >> 5;
     const long long kld = (K + 255) / 256 * 256;
-    const T* rp = src + batch * src_batch_stride + row * ld;
-    int8_t* dp = dst + (batch * N + row) * kld;
-    const bool vec_ok = (sizeof(T) == 2) && ((reinterpret_cast<uintptr_t>(rp) & 15) == 0);
-    int sum = 0;
-    constexpr int U = 4;        // four independent 16-byte streaming loads per lane in flight
-    for (long long kbase = lane * 8; kbase < kld; kbase += 256 * U) {
-        T v[U][8];
+    const long long kblocks = kld / 256;
+    constexpr int U = 8;
+    // rows [r0, r1) and 256-column blocks [b0, b1) of this warp
+    long long r0, r1, b0 = 0, b1 = kblocks;
+    if (warps_per_row > 1) {
+        const int rows_per_cta = 8 / warps_per_row, slice = wib % warps_per_row;
+        r0 = (long long)blockIdx.x * rows_per_cta + wib / warps_per_row;
+        r1 = r0 + 1;
+        const long long per = (kblocks + warps_per_row - 1) / warps_per_row;
+        b0 = slice * per;
+        b1 = b0 + per < kblocks ? b0 + per : kblocks;
+    } else {
+        r0 = ((long long)blockIdx.x * 8 + wib) * rows_per_warp;
+        r1 = r0 + rows_per_warp;
+    }
+    for (long long gr = r0; gr < r1; gr++) {
+        int sum = 0;
+        if (gr < total_rows) {
+            const long long batch = gr / N, row = gr - batch * N;
+            const T* rp = src + batch * src_batch_stride + row * ld;
+            int8_t* dp = dst + gr * kld;
+            const bool vec_ok = (sizeof(T) == 2) && ((reinterpret_cast<uintptr_t>(rp) & 15) == 0);
+            for (long long kbase = b0 * 256 + lane * 8; kbase < b1 * 256; kbase += 256 * U) {
+                if (vec_ok && kbase + 256 * (U - 1) + 8 <= K && kbase + 256 * (U - 1) < b1 * 256) {
+                    // all U blocks inside the row and the slice: loads first, then two elements per operation
+                    uint4 v[U];
 #pragma unroll
-        for (int u = 0; u < U; u++) {
-            const long long k0 = kbase + 256 * u;
-            if (k0 < K) {
-                if (vec_ok && k0 + 8 <= K) {
-                    *reinterpret_cast<uint4*>(v[u]) = __ldcs(reinterpret_cast<const uint4*>(rp + k0));
-                } else {
+                    for (int u = 0; u < U; u++) v[u] = __ldcs(reinterpret_cast<const uint4*>(rp + kbase + 256 * u));
 #pragma unroll
-                    for (int e = 0; e < 8; e++) v[u][e] = (k0 + e < K) ? rp[k0 + e] : T();
+                    for (int u = 0; u < U; u++) *reinterpret_cast<uint2*>(dp + kbase + 256 * u) = act_values_x8(v[u], mode, sum);
+                    continue;
+                }
+#pragma unroll 1
+                for (int u = 0; u < U; u++) {                     // ragged tail, other element types, unaligned rows
+                    const long long k0 = kbase + 256 * u;
+                    if (k0 >= b1 * 256) break;
+                    int8_t o[8];
+#pragma unroll
+                    for (int e = 0; e < 8; e++) {
+                        o[e] = (k0 + e < K) ? act_value<T>(rp[k0 + e], mode) : (int8_t)0;
+                        sum += o[e];
+                    }
+                    *reinterpret_cast<uint2*>(dp + k0) = *reinterpret_cast<const uint2*>(o);
                 }
             }
         }
 #pragma unroll
-        for (int u = 0; u < U; u++) {
-            const long long k0 = kbase + 256 * u;
-            if (k0 >= kld) break;
-            int8_t o[8];
-#pragma unroll
-            for (int e = 0; e < 8; e++) {
-                o[e] = (k0 + e < K) ? act_value<T>(v[u][e], mode) : (int8_t)0;
-                sum += o[e];
+        for (int off = 16; off > 0; off >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, off);
+        if (warps_per_row > 1) {          // one row per warp group, one pass: every warp of the CTA reaches the barriers
+            if (lane == 0) part[wib] = sum;
+            __syncthreads();
+            if (lane == 0 && wib % warps_per_row == 0 && gr < total_rows) {
+                int tot = 0;
+                for (int i = 0; i < warps_per_row; i++) tot += part[wib + i];
+                colsum[gr] = tot;
             }
-            *reinterpret_cast<uint2*>(dp + k0) = *reinterpret_cast<const uint2*>(o);
+        } else if (lane == 0 && gr < total_rows) {
+            colsum[gr] = sum;
         }
     }
-#pragma unroll
-    for (int off = 16; off > 0; off >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, off);
-    if (lane == 0) colsum[batch * N + row] = sum;
 }
 
 // Transposing variant: source is [K, N]; a block owns 32 output rows (n) and walks K in 32-wide tiles.
@@ -307,9 +382,20 @@ int launch_prepare_acts(cudaStream_t stream, const void* src, int dtype, long lo
         BGEMM_DISPATCH_DTYPE(dtype, (e = launch_pdl(prepare_acts_t_kernel<T>, grid, dim3(256), stream, static_cast<const T*>(src), N, K, ld, act_mode,
                                                     dst, colsum, src_batch_stride)));
     } else {
-        dim3 grid((unsigned)((N + 7) / 8), (unsigned)batch);
+        // At most one resident wave of 8-warp CTAs (4 per SM): longer launches give every warp several rows, launches
+        // far below a wave split every row over 2, 4 or 8 warps.
+        const long long total_rows = N * batch, wave_warps = (long long)sm_count() * 32;
+        int rows_per_warp = 1, warps_per_row = 1;
+        if (total_rows > wave_warps) {
+            rows_per_warp = (int)((total_rows + wave_warps - 1) / wave_warps);
+        } else {
+            const long long kblocks = (K + 255) / 256;
+            while (warps_per_row < 8 && total_rows * warps_per_row * 2 <= wave_warps && kblocks >= warps_per_row * 2 * 2) warps_per_row *= 2;
+        }
+        const long long ctas = warps_per_row > 1 ? (total_rows * warps_per_row + 7) / 8 : ((total_rows + rows_per_warp - 1) / rows_per_warp + 7) / 8;
+        dim3 grid((unsigned)ctas);
         BGEMM_DISPATCH_DTYPE(dtype, (e = launch_pdl(prepare_acts_kernel<T>, grid, dim3(256), stream, static_cast<const T*>(src), N, K, ld, act_mode, dst,
-                                                    colsum, src_batch_stride)));
+                                                    colsum, src_batch_stride, total_rows, rows_per_warp, warps_per_row)));
     }
     count_launch();
     return (int)(e != cudaSuccess ? e : cudaGetLastError());
