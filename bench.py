@@ -47,9 +47,10 @@ WORKLOADS = {
     "c5n4096": (28672, 8192, 4096, "bwta", "LLM projection 28672x8192, ternary X, N=4096"),
 }
 L2_BYTES = 126 * 1024 * 1024
-# dram__bytes_read.sum + dram__bytes_write.sum per layer of a batched gemm_kernel launch, from the ncu capture summarised
-# under profiles/ (80 layers captured; traffic grows in proportion to the layer count). Workloads without a capture: null.
-NCU_DRAM_BYTES_PER_LAYER = {"c2": 269.76e6 / 80}     # profiles/gemm_kernel_bwta_4096x4096x128_batched80.md
+# dram__bytes_read.sum + dram__bytes_write.sum per layer of the batched GEMM launch (gemm_persist_kernel), from the ncu
+# capture summarised under profiles/ (80 layers captured; traffic grows in proportion to the layer count). Workloads
+# without a capture: null.
+NCU_DRAM_BYTES_PER_LAYER = {"c2": 268.95e6 / 80}     # profiles/gemm_persist_kernel_bwta_4096x4096x128_batched80.md
 METRIC = "bwta_effective_tops"
 UNIT = "TOPS (2*M*N*K/s)"
 
@@ -367,7 +368,7 @@ def main():
     else:
         roofline = {"bound": "hbm", "achieved": gemm_gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": gemm_gbs / peaks["hbm_gbs"],
                     "traffic": (NCU_DRAM_BYTES_PER_LAYER[args.workload] * layers if args.workload in NCU_DRAM_BYTES_PER_LAYER else None), "peak_source": peaks["source"]}
-    roofline.update({"kernel": "gemm_kernel (tcgen05 kind::i8, A operand unpacked into tensor memory)", "launch_us": launch_us,
+    roofline.update({"kernel": "gemm_persist_kernel for pools with one tile across N, else gemm_kernel (tcgen05 kind::i8, A operand unpacked into tensor memory)", "launch_us": launch_us,
                      "layers_per_launch": layers, "bytes_alg_per_launch": bytes_layer * layers, "ops_per_launch": ops_layer * layers,
                      "kernel_gbs": gemm_gbs, "kernel_tops": gemm_tops})
     lsteps = max(3, args.steps // 5)

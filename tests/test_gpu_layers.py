@@ -153,6 +153,18 @@ def test_binary_mlp_matches_oracle(L):
     assert torch.equal(mlp2(cfg["x"].cuda()).cpu(), want)
 
 
+def test_binary_mlp_graph_replay_equals_eager(L):
+    """The CUDA-graph mode replays exactly the eager launches: same bits, for several inputs and two batch sizes."""
+    cfg = O.config4(batch=64, dims=(256, 512, 384, 10))
+    ws = [w.cuda() for w in cfg["ws"]]
+    eager, replay = L.BinaryMLP(ws), L.BinaryMLP(ws, graph=True)
+    g = O._gen(9)
+    for batch in (64, 64, 17, 64):
+        x = torch.randn(batch, 256, generator=g).to(torch.float16).cuda()
+        assert torch.equal(replay(x), eager(x))
+    assert len(replay._captured) == 2
+
+
 def test_sharded_rows_single_gpu_matches_unsharded():
     import bgemm_b200 as B
     from sharded import ShardedRows, make_gpu_shard, row_shards
