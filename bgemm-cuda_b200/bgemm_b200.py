@@ -47,6 +47,7 @@ lib.bgemm_pack_weights.argtypes = [_vp, _vp, _int, _i64, _i64, _i64, _int, _vp, 
 lib.bgemm_pack_weights_host.argtypes = [_vp, _int, _i64, _i64, _i64, _int, _vp, _vp, _vp]
 lib.bgemm_prepare_acts.argtypes = [_vp, _vp, _int, _i64, _i64, _i64, _int, _int, _vp, _vp, _i64, _i64]
 lib.bgemm_gemm.argtypes = [_vp, _vp, _i64, _i64, _vp, _vp, _i64, _int, _vp, _int, _int, _vp, _int, _vp, _sz, _i64]
+lib.bgemm_gemm_to_acts.argtypes = [_vp, _vp, _i64, _i64, _vp, _vp, _i64, _int, _vp, _int, _vp, _vp, _int, _vp, _sz, _i64]
 lib.bgemm_gemm_workspace_bytes.restype = _sz
 lib.bgemm_gemm_workspace_bytes.argtypes = [_i64, _i64, _i64, _int, _i64]
 lib.bgemm_gemm_auto_split_k.argtypes = [_i64, _i64, _i64, _i64]
@@ -176,6 +177,27 @@ def gemm(plane: torch.Tensor, M: int, K: int, acts: torch.Tensor, colsum: torch.
         check(lib.bgemm_gemm(_stream(), plane.data_ptr(), M, K, acts.data_ptr(), colsum.data_ptr(), N, op, out.data_ptr(), out_kind,
                              out_layout, _ptr(alpha), split_k, _ptr(ws) if need else None, ws.numel() if need else 0, B), "bgemm_gemm")
     return out
+
+
+def gemm_to_acts(plane: torch.Tensor, M: int, K: int, acts: torch.Tensor, colsum: torch.Tensor, op: int, next_act_mode: int,
+                 alpha: torch.Tensor | None = None, split_k: int = 0, ws: torch.Tensor | None = None):
+    """GEMM whose result becomes the next layer's prepared activations: (int8 [.., N, act_ld(M)], colsum int32 [.., N])."""
+    _require_cuda(plane, acts, colsum, alpha)
+    batched = acts.dim() == 3
+    B = acts.shape[0] if batched else 1
+    N = acts.shape[-2]
+    assert acts.shape[-1] == act_ld(K) and acts.is_contiguous() and colsum.is_contiguous()
+    lead = (B,) if batched else ()
+    nxt = torch.empty(lead + (N, act_ld(M)), dtype=torch.int8, device=acts.device)
+    ncs = torch.empty(lead + (N,), dtype=torch.int32, device=acts.device)
+    need = lib.bgemm_gemm_workspace_bytes(M, N, K, split_k, B)
+    if need and ws is None:
+        ws = workspace(acts.device, need)
+    with torch.cuda.device(acts.device):
+        check(lib.bgemm_gemm_to_acts(_stream(), plane.data_ptr(), M, K, acts.data_ptr(), colsum.data_ptr(), N, op, _ptr(alpha), next_act_mode,
+                                     nxt.data_ptr(), ncs.data_ptr(), split_k, _ptr(ws) if need else None, ws.numel() if need else 0, B),
+              "bgemm_gemm_to_acts")
+    return nxt, ncs
 
 
 def linear_forward(weight_f16: torch.Tensor, acts_f16: torch.Tensor, op: int = OP_XOR, out_kind: int = OUT_F16,

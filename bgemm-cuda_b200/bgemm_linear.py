@@ -28,7 +28,7 @@ __all__ = [
 ]
 
 AND_POP, XOR_POP, ATTN_MM, BWTA = 0, 1, 2, 3
-_ACT_TERNARY = 1
+_ACT_SIGN, _ACT_TERNARY = 0, 1
 _WBIT_NONZERO, _WBIT_NEGATIVE_NZ = 2, 3
 _OUT_I32, _OUT_F16, _OUT_F16_SCALED = 0, 1, 2
 
@@ -366,25 +366,58 @@ class BinaryLinear(nn.Module):
             BWTA if self.ternary else XOR_POP, _OUT_F16_SCALED)
         return out.reshape(*lead, self.out_features)
 
+    @property
+    def op(self) -> int:
+        return BWTA if self.ternary else XOR_POP
+
+    @property
+    def act_mode(self) -> int:
+        return _ACT_TERNARY if self.ternary else _ACT_SIGN
+
+    def prepare(self, x: torch.Tensor):
+        """fp16 [N, in_features] -> this layer's prepared activations (int8 rows, row sums)."""
+        return lowbit_kernel.prepare_acts(x.reshape(-1, self.in_features), self.act_mode, False)
+
+    def forward_prepared(self, acts: torch.Tensor, colsum: torch.Tensor, next_layer: "BinaryLinear | None" = None):
+        """GEMM on prepared activations. With next_layer the scaled result is turned into that layer's prepared
+        activations inside the GEMM epilogue (no fp16 round trip) and (acts, colsum) is returned; else fp16 [N, out]."""
+        if next_layer is None:
+            return lowbit_kernel.gemm_prepared(self.plane, self.out_features, self.in_features, acts, colsum, self.op, _OUT_F16_SCALED, 0,
+                                               self.alpha, 0)
+        assert next_layer.in_features == self.out_features
+        return lowbit_kernel.gemm_prepared_to_acts(self.plane, self.out_features, self.in_features, acts, colsum, self.op,
+                                                   next_layer.act_mode, self.alpha, 0)
+
 
 class BinaryMLP(nn.Module):
     """Stack of BinaryLinear layers; the sign of each fp16 output is the next layer's binary input.
 
-    graph=True replays the whole forward (two launches per layer) from a CUDA graph captured per input shape:
+    fused=True (default) keeps activations on the int8 path between layers: one activation pass for the input,
+    then one GEMM per layer whose epilogue writes the next layer's activations (same bits as the unfused chain).
+    graph=True replays the whole forward from a CUDA graph captured per input shape:
     a small MLP is bound by launch latency, not by the kernels. The input is copied into the graph's static
     buffer and the result is returned as a copy.
     """
 
-    def __init__(self, weights, graph: bool = False):
+    def __init__(self, weights, graph: bool = False, fused: bool = True):
         super().__init__()
         self.layers = nn.ModuleList(BinaryLinear(w) for w in weights)
         self.graph = graph
+        self.fused = fused      # hidden layers produce the next layer's int8 activations in their GEMM epilogue
         self._captured = {}
 
     def _eager(self, x: torch.Tensor) -> torch.Tensor:
-        for layer in self.layers:
-            x = layer(x)
-        return x
+        if not self.fused:
+            for layer in self.layers:
+                x = layer(x)
+            return x
+        # one activation pass for the input, then every hidden layer hands int8 activations to the next one
+        lead = x.shape[:-1]
+        acts, colsum = self.layers[0].prepare(x)
+        for i, layer in enumerate(self.layers[:-1]):
+            acts, colsum = layer.forward_prepared(acts, colsum, self.layers[i + 1])
+        y = self.layers[-1].forward_prepared(acts, colsum)
+        return y.reshape(*lead, self.layers[-1].out_features)
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         if not self.graph:

@@ -208,6 +208,59 @@ int bgemm_gemm(void* stream, const void* plane, int64_t M, int64_t K, const int8
     return launch_gemm((cudaStream_t)stream, p, acts, bgemm_act_ld(K), batch);
 }
 
+int bgemm_gemm_to_acts(void* stream, const void* plane, int64_t M, int64_t K, const int8_t* acts, const int32_t* colsum, int64_t N, int op,
+                       const void* alpha, int next_act_mode, int8_t* next_acts, int32_t* next_colsum, int split_k, void* workspace,
+                       size_t workspace_bytes, int64_t batch) {
+    if (!plane || !acts || !colsum || !next_acts || !next_colsum) return BGEMM_ERR_NULL;
+    if (op < BGEMM_OP_AND || op > BGEMM_OP_BWTA || next_act_mode < BGEMM_ACT_SIGN || next_act_mode > BGEMM_ACT_NEG01) return BGEMM_ERR_ENUM;
+    if (M < 1 || N < 1 || K < 1 || batch < 1 || batch > 65535 || M > kMaxDim || N > kMaxDim || K > kMaxDim || split_k < 0 ||
+        split_k > kMaxSplitK)
+        return BGEMM_ERR_SHAPE;
+    if (!aligned(plane, 16) || !aligned(acts, 16) || !aligned(colsum, 4) || !aligned(next_acts, 16) || !aligned(next_colsum, 4))
+        return BGEMM_ERR_ALIGN;
+    const int s = resolve_split_k(M, N, K, batch, split_k);
+    const long long mtiles = (M + 127) / 128;
+    if (mtiles * s > 65535) return BGEMM_ERR_SHAPE;
+    const long long ld = bgemm_act_ld(M);
+    cudaStream_t st = (cudaStream_t)stream;
+    // the kernel adds row sums with atomics and writes whole 8-column chunks: sums and the padding beyond them start at zero
+    cudaError_t e = cudaMemsetAsync(next_colsum, 0, (size_t)N * (size_t)batch * sizeof(int32_t), st);
+    const long long written = (M + 7) / 8 * 8;
+    if (e == cudaSuccess && written < ld)
+        e = cudaMemset2DAsync(next_acts + written, (size_t)ld, 0, (size_t)(ld - written), (size_t)N * (size_t)batch, st);
+    if (e != cudaSuccess) return (int)e;
+
+    GemmParams p{};
+    p.plane = static_cast<const uint8_t*>(plane);
+    p.colsum = colsum;
+    p.out = next_acts;
+    p.alpha = static_cast<const __half*>(alpha);
+    p.status = device_status_word();
+    p.prof = debug_profile_buffer();
+    p.M = (int)M; p.N = (int)N; p.K = (int)K;
+    p.kblocks = (int)((K + 255) / 256);
+    p.mtiles = (int)mtiles;
+    p.split_k = s;
+    p.epi = (op == BGEMM_OP_XOR || op == BGEMM_OP_BWTA) ? 1 : 0;
+    p.out_kind = kOutActs;
+    p.out_layout = BGEMM_LAYOUT_NM;
+    p.plane_batch_bytes = (long long)bgemm_plane_bytes(M, K);
+    p.cluster = (s > 1 && s <= kMaxClusterSplit) ? 1 : 0;
+    p.colsum_next = next_colsum;
+    p.out_ld = ld;
+    p.act_mode = next_act_mode;
+    if (s > kMaxClusterSplit) {
+        const size_t need = bgemm_gemm_workspace_bytes(M, N, K, s, batch);
+        if (!workspace || workspace_bytes < need) return BGEMM_ERR_WORKSPACE;
+        if (!aligned(workspace, 256)) return BGEMM_ERR_ALIGN;
+        const int NT = gemm_tile_n(N);
+        const long long tiles = mtiles * ((N + NT - 1) / NT) * batch;
+        p.ws_counters = static_cast<unsigned int*>(workspace);
+        p.ws_partial = reinterpret_cast<int32_t*>(static_cast<char*>(workspace) + counter_bytes(tiles));
+    }
+    return launch_gemm(st, p, acts, bgemm_act_ld(K), batch);
+}
+
 // Workspace of the unpacked-operand entry point: [gemm workspace][plane][acts int8][colsum].
 static void linear_ws_layout(int64_t M, int64_t N, int64_t K, int s, size_t* off_plane, size_t* off_acts, size_t* off_colsum,
                              size_t* total) {

@@ -1,6 +1,7 @@
 // Epilogue helpers shared by the GEMM kernels: an accumulator tile staged in shared (or global) memory as
 // int32 [columns][128] is summed over K partitions, mapped to the op's result (D or colsum - 2 D), scaled per row
-// where asked, and stored with 16-byte coalesced stores in either output layout.
+// where asked, and stored with 16-byte coalesced stores in either output layout -- or turned straight into the next
+// layer's int8 activations and their row sums.
 #pragma once
 #include <cuda_fp16.h>
 
@@ -27,6 +28,7 @@ __device__ __forceinline__ void store8_rows(const TileOut& t, int n, int m0, con
     for (int q = 0; q < 8; q++) val[q] = p.epi ? cs - 2 * acc[q] : acc[q];
     const size_t idx = (size_t)t.batch * p.M * p.N + (size_t)gn * p.M + gm;
     const bool full = gm + 8 <= p.M;
+    if (p.out_kind == kOutActs) return;       // handled by store8_rows_as_acts
     if (p.out_kind == BGEMM_OUT_I32) {
         int* o = reinterpret_cast<int*>(p.out) + idx;
         if (full && (reinterpret_cast<uintptr_t>(o) & 15) == 0) {
@@ -49,6 +51,33 @@ __device__ __forceinline__ void store8_rows(const TileOut& t, int n, int m0, con
             for (int q = 0; q < 8; q++) if (gm + q < p.M) o[q] = h[q];
         }
     }
+}
+
+// The same 8 results written as the next layer's activations: act(fp16 result) as int8 at row n of an [N, out_ld]
+// matrix (columns = this GEMM's rows m). The fp16 result is rounded exactly as the fp16 output kinds round it, so
+// the bytes equal prepare_acts applied to that output. Returns the sum of the 8 values (0 for a unit outside the
+// matrix); rows beyond M inside the chunk are written as zero padding.
+__device__ __forceinline__ int store8_rows_as_acts(const TileOut& t, int n, int m0, const int (&acc)[8], bool valid) {
+    const GemmParams& p = *t.p;
+    const int gn = t.n_base + n, gm = t.m_base + m0;
+    if (!valid) return 0;
+    const int cs = t.s_colsum[n];
+    int sum = 0;
+    uint32_t w[2] = {0u, 0u};
+#pragma unroll
+    for (int q = 0; q < 8; q++) {
+        const int val = p.epi ? cs - 2 * acc[q] : acc[q];
+        const __half hv = __float2half_rn(p.alpha ? (float)val * t.s_alpha[m0 + q] : (float)val);
+        const uint32_t bits = __half_as_ushort(hv);
+        const int neg = (int)(bits >> 15), zero = (bits & 0x7fffu) == 0;
+        int v = p.act_mode == BGEMM_ACT_SIGN ? 1 - 2 * neg : (p.act_mode == BGEMM_ACT_TERNARY ? (zero ? 0 : 1 - 2 * neg) : neg);
+        if (gm + q >= p.M) v = 0;
+        sum += v;
+        w[q >> 2] |= (uint32_t)(v & 0xff) << (8 * (q & 3));
+    }
+    int8_t* o = reinterpret_cast<int8_t*>(p.out) + ((size_t)t.batch * p.N + gn) * p.out_ld + gm;
+    *reinterpret_cast<uint2*>(o) = make_uint2(w[0], w[1]);      // gm is a multiple of 8, the pitch of 256
+    return sum;
 }
 
 // 8 consecutive columns n0..n0+7 (tile-local) of row m (tile-local): the [M, N] layout.
@@ -120,6 +149,24 @@ __device__ __forceinline__ void write_tile(const TileOut& t, const int* base, in
     const GemmParams& p = *t.p;
     if (p.out_layout == BGEMM_LAYOUT_NM) {
         const int units = ncols * 16;                           // (column, 8-row chunk)
+        if (p.out_kind == kOutActs) {
+            // Every lane runs every iteration (the row sums are reduced with warp shuffles over the 16 lanes that
+            // share a column); one atomic per column and tile.
+#pragma unroll 1
+            for (int u0 = 0; u0 < units; u0 += nthreads) {
+                const int u = u0 + et;
+                const int c = u >> 4, m0 = (u & 15) * 8;
+                const bool valid = u < units && t.n_base + n_first + c < p.N && t.m_base + m0 < p.M;
+                int acc[8];
+                if (valid) gather8_rows<GLOBAL>(base, parts, stride, c * 128 + m0, acc);
+                int sum = store8_rows_as_acts(t, n_first + c, m0, acc, valid);
+#pragma unroll
+                for (int off = 8; off > 0; off >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, off);
+                if ((et & 15) == 0 && u < units && t.n_base + n_first + c < p.N)
+                    atomicAdd(p.colsum_next + (size_t)t.batch * p.N + t.n_base + n_first + c, sum);
+            }
+            return;
+        }
 #pragma unroll 1
         for (int u = et; u < units; u += nthreads) {
             const int c = u >> 4, m0 = (u & 15) * 8;

@@ -289,7 +289,7 @@ __global__ void __launch_bounds__(kPThreads, 1) gemm_persist_kernel(const __grid
             tout.batch = batch; tout.m_base = mt * 128; tout.n_base = nt * NT;
             {
                 const int m = mt * 128 + et;
-                s_alpha[et] = (p.out_kind == BGEMM_OUT_F16_SCALED && m < p.M) ? __half2float(p.alpha[(size_t)batch * p.M + m]) : 1.f;
+                s_alpha[et] = ((p.out_kind == BGEMM_OUT_F16_SCALED || (p.out_kind == kOutActs && p.alpha)) && m < p.M) ? __half2float(p.alpha[(size_t)batch * p.M + m]) : 1.f;
             }
             for (int i = et; i < NT; i += kPEpiThreads) {
                 const int n = nt * NT + i;

@@ -255,7 +255,7 @@ __global__ void __launch_bounds__(kGemmThreads, Cfg<NT, POW2, DEEP>::MIN_CTAS) g
         // the first weight load)
         if (tid < 128) {
             const int m = mt * 128 + tid;
-            s_alpha[tid] = (p.out_kind == BGEMM_OUT_F16_SCALED && m < p.M) ? __half2float(p.alpha[(size_t)batch * p.M + m]) : 1.f;
+            s_alpha[tid] = ((p.out_kind == BGEMM_OUT_F16_SCALED || (p.out_kind == kOutActs && p.alpha)) && m < p.M) ? __half2float(p.alpha[(size_t)batch * p.M + m]) : 1.f;
         }
         for (int i = tid; i < NT; i += kUnpackThreads) {
             const int n = nt * NT + i;

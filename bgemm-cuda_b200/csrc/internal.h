@@ -26,7 +26,14 @@ struct GemmParams {
     int epi;                      // 0: result = D, 1: result = colsum[n] - 2 D
     int out_kind, out_layout;
     long long plane_batch_bytes;
+    // kOutActs only: the result becomes the next layer's prepared activations (int8 rows of pitch out_ld in `out`,
+    // row sums accumulated into colsum_next, which the launcher has zeroed)
+    int32_t* colsum_next;
+    long long out_ld;
+    int act_mode;
 };
+
+constexpr int kOutActs = 100;     // internal out_kind of bgemm_gemm_to_acts
 
 void count_launch();
 bool programmatic_launch_enabled();   // BGEMM_PDL=0 in the environment switches it off

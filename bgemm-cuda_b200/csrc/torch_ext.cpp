@@ -175,6 +175,39 @@ torch::Tensor gemm_prepared(torch::Tensor plane, int64_t M, int64_t K, torch::Te
     return out;
 }
 
+// GEMM on prepared operands whose result becomes the next layer's prepared activations (see bgemm_gemm_to_acts):
+// returns (int8 [N, act_ld(M)], colsum int32 [N]) = prepare_acts(fp16 result, next_act_mode) without the round trip.
+std::vector<torch::Tensor> gemm_prepared_to_acts(torch::Tensor plane, int64_t M, int64_t K, torch::Tensor acts, torch::Tensor colsum,
+                                                 int64_t op, int64_t next_act_mode, c10::optional<torch::Tensor> alpha, int64_t splitK) {
+    TORCH_CHECK(plane.is_cuda() && acts.is_cuda() && colsum.is_cuda(), "gemm_prepared_to_acts: CUDA tensors required");
+    TORCH_CHECK(acts.is_contiguous() && colsum.is_contiguous() && plane.is_contiguous(), "gemm_prepared_to_acts: contiguous tensors required");
+    TORCH_CHECK(acts.scalar_type() == at::kChar && colsum.scalar_type() == at::kInt, "gemm_prepared_to_acts: acts int8 / colsum int32 required");
+    TORCH_CHECK(acts.size(-1) == bgemm_act_ld(K), "gemm_prepared_to_acts: activation row pitch must be bgemm_act_ld(K)");
+    c10::cuda::CUDAGuard guard(acts.device());
+    const bool batched = acts.dim() == 3;
+    const int64_t B = batched ? acts.size(0) : 1, N = acts.size(-2);
+    TORCH_CHECK((size_t)plane.numel() >= (size_t)B * bgemm_plane_bytes(M, K), "gemm_prepared_to_acts: plane too small for M, K");
+    std::vector<int64_t> ashape = batched ? std::vector<int64_t>{B, N, bgemm_act_ld(M)} : std::vector<int64_t>{N, bgemm_act_ld(M)};
+    std::vector<int64_t> cshape = batched ? std::vector<int64_t>{B, N} : std::vector<int64_t>{N};
+    auto next_acts = torch::empty(ashape, torch::TensorOptions().dtype(at::kChar).device(acts.device()));
+    auto next_colsum = torch::empty(cshape, torch::TensorOptions().dtype(at::kInt).device(acts.device()));
+    const void* alpha_ptr = nullptr;
+    torch::Tensor a;
+    if (alpha.has_value()) {
+        a = alpha->to(at::kHalf).contiguous();
+        TORCH_CHECK(a.is_cuda() && a.numel() == B * M, "gemm_prepared_to_acts: alpha must hold M values per batch on the GPU");
+        alpha_ptr = a.data_ptr();
+    }
+    const size_t need = bgemm_gemm_workspace_bytes(M, N, K, (int)splitK, B);
+    torch::Tensor ws;
+    if (need) ws = workspace(acts.device(), need);
+    check(bgemm_gemm_to_acts(stream_of(acts), plane.data_ptr(), M, K, acts.data_ptr<int8_t>(), colsum.data_ptr<int>(), N, (int)op, alpha_ptr,
+                             (int)next_act_mode, next_acts.data_ptr<int8_t>(), next_colsum.data_ptr<int>(), (int)splitK,
+                             need ? ws.data_ptr() : nullptr, need ? (size_t)ws.numel() : 0, B),
+          "bgemm_gemm_to_acts");
+    return {next_acts, next_colsum};
+}
+
 // x [N, K] unpacked x prepacked weights -> [N, M]. INSTR as in the reference; out_kind 1 = fp16, 0 = int32,
 // 2 = fp16 scaled by alpha (required then).
 torch::Tensor bgemm_linear_forward_packed(torch::Tensor x, torch::Tensor plane, int64_t M, int64_t K, c10::optional<torch::Tensor> alpha,
@@ -218,6 +251,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
           py::arg("transpose") = false);
     m.def("gemm_prepared", &gemm_prepared, "GEMM on prepared operands.", py::arg("plane"), py::arg("M"), py::arg("K"), py::arg("acts"),
           py::arg("colsum"), py::arg("op"), py::arg("out_kind") = 0, py::arg("out_layout") = 0, py::arg("alpha") = py::none(),
+          py::arg("splitK") = 0);
+    m.def("gemm_prepared_to_acts", &gemm_prepared_to_acts, "GEMM whose result becomes the next layer's prepared activations.", py::arg("plane"),
+          py::arg("M"), py::arg("K"), py::arg("acts"), py::arg("colsum"), py::arg("op"), py::arg("next_act_mode"), py::arg("alpha") = py::none(),
           py::arg("splitK") = 0);
     m.def("bgemm_linear_forward_packed", &bgemm_linear_forward_packed, "x x prepacked weights.", py::arg("x"), py::arg("plane"), py::arg("M"),
           py::arg("K"), py::arg("alpha") = py::none(), py::arg("splitK") = 0, py::arg("INSTR") = 1, py::arg("out_kind") = 1);

@@ -148,6 +148,19 @@ int bgemm_gemm(void* stream, const void* plane, int64_t M, int64_t K,
                int op, void* out, int out_kind, int out_layout, const void* alpha,
                int split_k, void* workspace, size_t workspace_bytes, int64_t batch);
 size_t bgemm_gemm_workspace_bytes(int64_t M, int64_t N, int64_t K, int split_k, int64_t batch);
+
+/* The same GEMM with a fused activation producer: the result is not stored, it becomes the NEXT layer's prepared
+ * activations. next_acts int8 [N, bgemm_act_ld(M)] (this GEMM's M is the next layer's K) receives
+ * act(fp16 result) under next_act_mode (BGEMM_ACT_*), where the fp16 result is rne(acc) or, with alpha != NULL,
+ * rne(float(acc) * float(alpha[m])) -- bit for bit what bgemm_gemm (BGEMM_OUT_F16 / _SCALED, BGEMM_LAYOUT_NM)
+ * followed by bgemm_prepare_acts would produce -- and next_colsum int32 [N] its row sums. Both buffers are
+ * fully written (padding zeroed) by the call. Batched like bgemm_gemm (problem i: next_acts + i*N*act_ld(M),
+ * next_colsum + i*N). Replaces the per-layer elementwise chain between two binary layers of the reference
+ * (sign / scale / cast of the fp16 output, tests/python/bgemm_linear.py:479-484 and :357-378).               */
+int bgemm_gemm_to_acts(void* stream, const void* plane, int64_t M, int64_t K,
+                       const int8_t* acts, const int32_t* colsum, int64_t N, int op, const void* alpha,
+                       int next_act_mode, int8_t* next_acts, int32_t* next_colsum,
+                       int split_k, void* workspace, size_t workspace_bytes, int64_t batch);
 /* The split_k the library would pick for split_k = 0.                                                 */
 int bgemm_gemm_auto_split_k(int64_t M, int64_t N, int64_t K, int64_t batch);
 

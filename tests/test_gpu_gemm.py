@@ -302,6 +302,36 @@ def test_persistent_kernel_under_graph_replay(B):
     assert B.lib.bgemm_device_status(1) == 0
 
 
+@pytest.mark.parametrize("M,K,N,batch,split_k", [(384, 1024, 40, 1, 1), (1000, 2048, 100, 1, 0), (300, 4096, 17, 3, 4), (256, 8192, 64, 1, 12),
+                                                  (512, 2048, 128, 80, 1)])
+@pytest.mark.parametrize("next_mode", [0, 1, 2])
+def test_gemm_to_acts_equals_gemm_then_prepare(B, M, K, N, batch, split_k, next_mode):
+    """The fused activation producer writes exactly what the fp16 output followed by prepare_acts gives (ragged M:
+    zero padding up to the 256-column pitch; every K partitioning; the persistent kernel for the pool case)."""
+    g = O._gen(M + K + N + batch + next_mode)
+    shape_w, shape_x = ((batch, M, K), (batch, N, K)) if batch > 1 else ((M, K), (N, K))
+    w = O.rand_pm1(shape_w, g)
+    x = O.rand_ternary(shape_x, g)
+    alpha = (torch.rand((batch, M) if batch > 1 else (M,), generator=g) * 0.5).to(torch.float16)
+    alpha.view(-1)[3] = 0.0                                               # a dead row: results +-0, sign bit decides
+    plane, _, _ = B.pack_weights(w.cuda(), B.WBIT_OF_OP[O.OP_BWTA])
+    acts, colsum = B.prepare_acts(x.cuda(), B.ACT_MODE_OF_OP[O.OP_BWTA])
+    for a in (alpha.cuda(), None):
+        y = B.gemm(plane, M, K, acts, colsum, O.OP_BWTA, O.OUT_F16_SCALED if a is not None else O.OUT_F16, 0, a, split_k)
+        want_acts, want_cs = B.prepare_acts(y, next_mode)
+        got_acts, got_cs = B.gemm_to_acts(plane, M, K, acts, colsum, O.OP_BWTA, next_mode, a, split_k)
+        assert got_acts.shape == want_acts.shape
+        assert torch.equal(got_acts, want_acts)
+        assert torch.equal(got_cs, want_cs)
+    # and against the oracle's definition of the activation mapping
+    acc = O.ref_acc(w, x, O.OP_BWTA)
+    yref = O.ref_out(acc, O.OUT_F16_SCALED, alpha.unsqueeze(-2) if batch > 1 else alpha)
+    np_acts, np_cs = O.np_prepare_acts(yref.reshape(-1, M), next_mode)
+    got_acts, got_cs = B.gemm_to_acts(plane, M, K, acts, colsum, O.OP_BWTA, next_mode, alpha.cuda(), split_k)
+    assert np.array_equal(got_acts.cpu().numpy().reshape(-1, got_acts.shape[-1]), np_acts)
+    assert np.array_equal(got_cs.cpu().numpy().reshape(-1), np_cs)
+
+
 def test_argument_errors(B):
     x = torch.zeros(4, 256, dtype=torch.float16, device="cuda")
     assert B.lib.bgemm_pack_weights(None, None, 0, 4, 256, 256, 0, x.data_ptr(), None, None, 1, 0) == -1

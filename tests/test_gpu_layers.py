@@ -157,7 +157,7 @@ def test_binary_mlp_graph_replay_equals_eager(L):
     """The CUDA-graph mode replays exactly the eager launches: same bits, for several inputs and two batch sizes."""
     cfg = O.config4(batch=64, dims=(256, 512, 384, 10))
     ws = [w.cuda() for w in cfg["ws"]]
-    eager, replay = L.BinaryMLP(ws), L.BinaryMLP(ws, graph=True)
+    eager, replay = L.BinaryMLP(ws, fused=False), L.BinaryMLP(ws, graph=True)      # unfused eager chain vs fused graph replay
     g = O._gen(9)
     for batch in (64, 64, 17, 64):
         x = torch.randn(batch, 256, generator=g).to(torch.float16).cuda()
