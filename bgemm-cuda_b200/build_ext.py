@@ -22,7 +22,8 @@ def _newer(target: Path, sources) -> bool:
 
 
 def build_library(verbose: bool = False) -> Path:
-    subprocess.run(["make", "-C", str(HERE), "-j4", "libbgemm_b200.so"], check=True,
+    # the library and the native command line (bgemm_cli) that links against it
+    subprocess.run(["make", "-C", str(HERE), "-j4", "libbgemm_b200.so", "bgemm_cli"], check=True,
                    stdout=None if verbose else subprocess.DEVNULL)
     return HERE / "libbgemm_b200.so"
 
