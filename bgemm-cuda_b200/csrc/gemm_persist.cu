@@ -196,9 +196,10 @@ __global__ void __launch_bounds__(kPThreads, 1) gemm_persist_kernel(const __grid
                 // commutes, so no other order is needed.
                 // Parity waits must not name a phase the barrier has not reached. d_empty[buf]: phase k - 2 was
                 // awaited by the opener of tile lt - 2 and the other issuer waited for that tile to be opened.
-                // first_done[buf]: the waiter either waited for phase k - 1 itself (tile lt - 2) or committed it and
-                // has since reused one of its operand stages (tiles have at least STAGES K blocks, checked by the
-                // launcher), whose release was committed after first_done. Neither barrier can be two phases
+                // first_done[buf]: the waiter either waited for phase k - 1 itself (tile lt - 2; always so when tiles
+                // have an even number of K blocks) or committed it and has since reused one of its operand stages
+                // (odd K-block counts are only launched with at least STAGES K blocks per tile), whose release was
+                // committed after first_done. Neither barrier can be two phases
                 // ahead: that needs the epilogue of tile lt, which needs this issuer's d_full commit below.
                 const bool opener = (int)(g & 1) == me;
                 if (opener) {
@@ -342,7 +343,7 @@ __global__ void __launch_bounds__(kPThreads, 1) gemm_persist_kernel(const __grid
 template <int NT>
 static int launch_persist_variant(cudaStream_t stream, const CUtensorMap& tmap, const GemmParams& p, long long total_tiles, int ctas) {
     using C = PCfg<NT>;
-    if (p.kblocks < C::STAGES) return BGEMM_ERR_UNSUPPORTED;   // see the issuers' note on first_done
+    if (!persistent_kblocks_ok(NT, p.kblocks)) return BGEMM_ERR_UNSUPPORTED;
     static bool configured[64] = {};
     int dev = 0;
     cudaGetDevice(&dev);
@@ -369,6 +370,14 @@ static int launch_persist_variant(cudaStream_t stream, const CUtensorMap& tmap, 
 }
 
 bool persistent_supported(int NT) { return NT == 64 || NT == 128; }
+
+// With an even number of K blocks per tile issuer 0 opens every tile and issuer 1 waits for every phase of
+// first_done itself. With an odd number the opener alternates, and the argument in the issuer loop needs tiles of at
+// least STAGES K blocks.
+bool persistent_kblocks_ok(int NT, int kblocks) {
+    const int stages = NT == 64 ? PCfg<64>::STAGES : PCfg<128>::STAGES;
+    return kblocks >= 2 && (kblocks % 2 == 0 || kblocks >= stages);
+}
 
 int launch_gemm_persistent(cudaStream_t stream, const void* tensor_map, const GemmParams& p, int NT, long long total_tiles, int ctas) {
     const CUtensorMap& tmap = *static_cast<const CUtensorMap*>(tensor_map);

@@ -499,8 +499,8 @@ static int env_int(const char* name) {
 static int forced_nt() { static const int v = env_int("BGEMM_FORCE_NT"); return v; }
 static int forced_deep() { static const int v = env_int("BGEMM_FORCE_DEEP"); return v; }
 static int forced_persist() { static const int v = env_int("BGEMM_PERSIST"); return v; }   // 0: never the persistent kernel, 1: whenever it applies
-// With few K blocks per tile the epilogue (four warps in the persistent kernel) outweighs the mainloop.
-constexpr int kPersistMinKBlocks = 8;
+// Fewest K blocks per tile for the persistent kernel (tuning override: BGEMM_PERSIST_MIN_KB).
+static int persist_min_kblocks() { static const int v = env_int("BGEMM_PERSIST_MIN_KB"); return v > 0 ? v : 2; }
 
 int gemm_tile_n(long long N) {
     const int f = forced_nt();
@@ -535,7 +535,8 @@ int launch_gemm(cudaStream_t stream, GemmParams p, const int8_t* acts, long long
     // SM, measured 3-4 % faster (co-resident CTAs share activation tiles in L2), so it keeps those.
     const long long total_tiles = (long long)p.ntiles * p.mtiles * batch;
     const int persist = forced_persist() >= 0 ? forced_persist() : (p.ntiles == 1 ? 1 : 0);
-    if (persist && p.split_k == 1 && persistent_supported(NT) && total_tiles > sm_count() && p.kblocks >= kPersistMinKBlocks)
+    if (persist && p.split_k == 1 && persistent_supported(NT) && total_tiles > sm_count() && p.kblocks >= persist_min_kblocks() &&
+        persistent_kblocks_ok(NT, p.kblocks))
         return launch_gemm_persistent(stream, &tmap, p, NT, total_tiles, sm_count());
 
     dim3 grid((unsigned)p.ntiles, (unsigned)(p.mtiles * p.split_k), (unsigned)batch);

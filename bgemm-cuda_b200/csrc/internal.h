@@ -46,6 +46,7 @@ int launch_gemm(cudaStream_t stream, GemmParams p, const int8_t* acts, long long
 
 // Persistent variant (gemm_persist.cu); `tensor_map` points to the CUtensorMap of the activations.
 bool persistent_supported(int NT);
+bool persistent_kblocks_ok(int NT, int kblocks);   // K-block counts per tile the issuers' hand-over protocol covers
 int launch_gemm_persistent(cudaStream_t stream, const void* tensor_map, const GemmParams& p, int NT, long long total_tiles, int ctas);
 
 int launch_pack_weights(cudaStream_t stream, const void* src, int dtype, long long M, long long K, long long ld, int wbit_mode,
