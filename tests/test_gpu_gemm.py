@@ -334,6 +334,46 @@ def test_gemm_to_acts_equals_gemm_then_prepare(B, M, K, N, batch, split_k, next_
     assert np.array_equal(got_cs.cpu().numpy().reshape(-1), np_cs)
 
 
+def test_seeded_random_shapes(B):
+    """Sixty seeded random problems over every knob of bgemm_gemm (op, shape, batch, K partitioning, output kind and
+    layout) and of bgemm_gemm_to_acts, each against the oracle."""
+    rng = np.random.default_rng(20240611)
+    for case in range(60):
+        op = int(rng.choice(OPS))
+        M = int(rng.choice([1, 37, 128, 129, 300, 512, 1000]))
+        K = int(rng.choice([1, 100, 256, 257, 768, 1024, 2304, 4096]))
+        N = int(rng.choice([1, 5, 16, 40, 64, 65, 128, 130, 300]))
+        batch = int(rng.choice([1, 1, 1, 3, 40, 170]))
+        if batch * M * K > (1 << 26) or batch * M * N > (1 << 24):
+            batch = 1
+        split_k = int(rng.choice([0, 1, 1, 2, 5, 8, 11]))
+        layout = int(rng.integers(0, 2))
+        kind = int(rng.choice([O.OUT_I32, O.OUT_F16, O.OUT_F16_SCALED]))
+        g = O._gen(1000 + case)
+        shape_w, shape_x = ((batch, M, K), (batch, N, K)) if batch > 1 else ((M, K), (N, K))
+        w = torch.randn(shape_w, generator=g).to(torch.float16)
+        x = O.rand_ternary(shape_x, g) if op == O.OP_BWTA else torch.randn(shape_x, generator=g).to(torch.float16)
+        alpha = (torch.rand((batch, M) if batch > 1 else (M,), generator=g) + 0.25).to(torch.float16)
+        acc = O.ref_acc(w, x, op)
+        plane, _, _ = B.pack_weights(w.cuda(), B.WBIT_OF_OP[op])
+        acts, colsum = B.prepare_acts(x.cuda(), B.ACT_MODE_OF_OP[op])
+        got = B.gemm(plane, M, K, acts, colsum, op, kind, layout, alpha.cuda(), split_k).cpu()
+        want = O.ref_out(acc, kind, alpha.unsqueeze(-2) if batch > 1 else alpha)
+        if layout == 1:
+            want = want.transpose(-1, -2)
+        tag = (case, op, M, K, N, batch, split_k, layout, kind)
+        assert got.shape == want.shape, tag
+        assert torch.equal(got, want), tag
+        if case % 3 == 0:
+            mode = int(rng.integers(0, 3))
+            na, ncs = B.gemm_to_acts(plane, M, K, acts, colsum, op, mode, alpha.cuda(), split_k)
+            y = O.ref_out(acc, O.OUT_F16_SCALED, alpha.unsqueeze(-2) if batch > 1 else alpha)
+            ra, rcs = O.np_prepare_acts(y.reshape(-1, M), mode)
+            assert np.array_equal(na.cpu().numpy().reshape(-1, na.shape[-1]), ra), tag
+            assert np.array_equal(ncs.cpu().numpy().reshape(-1), rcs), tag
+    assert B.lib.bgemm_device_status(1) == 0
+
+
 def test_argument_errors(B):
     x = torch.zeros(4, 256, dtype=torch.float16, device="cuda")
     assert B.lib.bgemm_pack_weights(None, None, 0, 4, 256, 256, 0, x.data_ptr(), None, None, 1, 0) == -1
