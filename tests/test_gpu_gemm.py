@@ -334,6 +334,31 @@ def test_gemm_to_acts_equals_gemm_then_prepare(B, M, K, N, batch, split_k, next_
     assert np.array_equal(got_cs.cpu().numpy().reshape(-1), np_cs)
 
 
+@pytest.mark.parametrize("M,K,N,batch,layout", [(20000, 2304, 9, 1, 1), (1000, 4096, 16, 25, 0), (28672, 2048, 1, 1, 0), (19000, 2560, 16, 1, 0)])
+def test_weight_streaming_shapes(B, M, K, N, batch, layout):
+    """N <= 16 with more row tiles than SMs (the weight-streaming regime of the N = 1 / 16 sweep points): odd and
+    even K-block counts, ragged M, batches, all output kinds, automatic and forced K partitioning, repeated."""
+    g = O._gen(M + K + N + batch)
+    shape_w, shape_x = ((batch, M, K), (batch, N, K)) if batch > 1 else ((M, K), (N, K))
+    w = O.rand_pm1(shape_w, g)
+    x = O.rand_ternary(shape_x, g)
+    alpha = (torch.rand((batch, M) if batch > 1 else (M,), generator=g) + 0.5).to(torch.float16)
+    acc = O.ref_acc(w, x, O.OP_BWTA)
+    plane, _, _ = B.pack_weights(w.cuda(), B.WBIT_OF_OP[O.OP_BWTA])
+    acts, colsum = B.prepare_acts(x.cuda(), B.ACT_MODE_OF_OP[O.OP_BWTA])
+    for kind in (O.OUT_I32, O.OUT_F16_SCALED, O.OUT_I32):
+        want = O.ref_out(acc, kind, alpha.unsqueeze(-2) if batch > 1 else alpha)
+        if layout == 1:
+            want = want.transpose(-1, -2)
+        got = B.gemm(plane, M, K, acts, colsum, O.OP_BWTA, kind, layout, alpha.cuda(), 0).cpu()
+        assert torch.equal(got, want), (kind, int((got != want).sum()))
+        assert torch.equal(B.gemm(plane, M, K, acts, colsum, O.OP_BWTA, kind, layout, alpha.cuda(), 1).cpu(), want)
+    na, ncs = B.gemm_to_acts(plane, M, K, acts, colsum, O.OP_BWTA, 1, alpha.cuda(), 0)
+    ra, rcs = O.np_prepare_acts(O.ref_out(acc, O.OUT_F16_SCALED, alpha.unsqueeze(-2) if batch > 1 else alpha).reshape(-1, M), 1)
+    assert np.array_equal(na.cpu().numpy().reshape(-1, na.shape[-1]), ra) and np.array_equal(ncs.cpu().numpy().reshape(-1), rcs)
+    assert B.lib.bgemm_device_status(1) == 0
+
+
 def test_seeded_random_shapes(B):
     """Sixty seeded random problems over every knob of bgemm_gemm (op, shape, batch, K partitioning, output kind and
     layout) and of bgemm_gemm_to_acts, each against the oracle."""
