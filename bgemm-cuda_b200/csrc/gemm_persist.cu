@@ -137,7 +137,7 @@ __global__ void __launch_bounds__(kPThreads, 1) gemm_persist_kernel(const __grid
                 const uint8_t* src = p.plane + (size_t)batch * p.plane_batch_bytes + (size_t)mt * nkb * 4096;
                 for (int i = 0; i < nkb; i++, g++) {
                     const int s = (int)(g % C::W_STAGES);
-                    if (g >= C::W_STAGES) BGEMM_TIMED(tw, ok = mbar_wait(w_empty + 8 * s, (uint32_t)((g / C::W_STAGES) - 1) & 1, abort_flag, p.status, 21));
+                    if (g >= C::W_STAGES) BGEMM_TIMED(tw, ok = mbar_wait_relaxed(w_empty + 8 * s, (uint32_t)((g / C::W_STAGES) - 1) & 1, abort_flag, p.status, 21));
                     if (!ok) break;
                     mbar_arrive_expect_tx(w_full + 8 * s, 4096);
                     bulk_g2s(smem_u32(sW + s * 4096), src + (size_t)i * 4096, 4096, w_full + 8 * s);
@@ -161,7 +161,7 @@ __global__ void __launch_bounds__(kPThreads, 1) gemm_persist_kernel(const __grid
                 const int batch = (int)(t / p.ntiles / p.mtiles);
                 for (int i = 0; i < nkb; i++, g++) {
                     const int s = (int)(g % C::STAGES);
-                    if (g >= C::STAGES) BGEMM_TIMED(tw, ok = mbar_wait(empty + 8 * s, (uint32_t)((g / C::STAGES) - 1) & 1, abort_flag, p.status, 22));
+                    if (g >= C::STAGES) BGEMM_TIMED(tw, ok = mbar_wait_relaxed(empty + 8 * s, (uint32_t)((g / C::STAGES) - 1) & 1, abort_flag, p.status, 22));
                     if (!ok) break;
                     BGEMM_TRACE(4, g);
                     mbar_arrive_expect_tx(full + 8 * s, C::B_STAGE_BYTES);
@@ -254,7 +254,7 @@ __global__ void __launch_bounds__(kPThreads, 1) gemm_persist_kernel(const __grid
             if (lane == 0) mbar_arrive(w_empty + 8 * ws);
             const uint32_t w[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
             const int as = (int)(g % C::STAGES);
-            if (g >= C::STAGES) BGEMM_TIMED(twe, ok = mbar_wait(empty + 8 * as, (uint32_t)((g / C::STAGES) - 1) & 1, abort_flag, p.status, 28));
+            if (g >= C::STAGES) BGEMM_TIMED(twe, ok = mbar_wait_relaxed(empty + 8 * as, (uint32_t)((g / C::STAGES) - 1) & 1, abort_flag, p.status, 28));
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
             if ((tid & 127) == 0) BGEMM_TRACE(2, g);
@@ -297,7 +297,7 @@ __global__ void __launch_bounds__(kPThreads, 1) gemm_persist_kernel(const __grid
                 s_colsum[i] = (p.epi && n < p.N) ? __ldg(p.colsum + (size_t)batch * p.N + n) : 0;
             }
             bool ok;
-            BGEMM_TIMED(twd, ok = mbar_wait(d_full + 8 * buf, (uint32_t)(lt >> 1) & 1, abort_flag, p.status, 29));
+            BGEMM_TIMED(twd, ok = mbar_wait_relaxed(d_full + 8 * buf, (uint32_t)(lt >> 1) & 1, abort_flag, p.status, 29));
             ok = __all_sync(0xffffffffu, ok);
             const long long tb0 = p.prof ? clock64() : 0;
             if (ok) {

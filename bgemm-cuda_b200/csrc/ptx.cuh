@@ -68,6 +68,25 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     return true;
 }
 
+// The same for waiters that are not on the critical path (producers waiting for a free stage, epilogue warps waiting
+// for the next accumulator): they back off between probes instead of polling, which leaves issue slots and power to
+// the warps that feed the tensor pipe.
+__device__ __forceinline__ bool mbar_wait_relaxed(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status_word,
+                                                  int where) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const long long t0 = clock64();
+    while (!mbar_try_wait(bar, parity)) {
+        __nanosleep(64);
+        if (*abort_flag) return false;
+        if (clock64() - t0 > kWaitBudgetClocks) {
+            *abort_flag = 1;
+            if (status_word) atomicCAS(status_word, 0, where);
+            return false;
+        }
+    }
+    return true;
+}
+
 // ---- bulk (TMA) copies: every CTA fetches its own tiles -----------------------------------------------
 __device__ __forceinline__ void bulk_g2s(uint32_t dst_smem, const void* src, uint32_t bytes, uint32_t bar) {
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst_smem),
