@@ -1,6 +1,6 @@
 """Regenerates the golden fixtures in this directory FROM THE REFERENCE ITSELF.
 
-Needs a checkout of yifu-ding/BGEMM-CUDA (default /root/reference) and, for the prepack vectors,
+Needs a checkout of yifu-ding/BGEMM-CUDA (first argument; the default is the REF path below) and, for the prepack vectors,
 oracle/_ref/libref_prepack.so (built by `make -C oracle ref` from the reference's own header).
 It imports the reference's tests/python/bgemm_linear.py with a stub `lowbit_kernel` module -- the
 classes used here are the reference's pure-torch CPU paths and never call the extension:
