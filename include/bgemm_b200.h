@@ -209,9 +209,10 @@ int bgemm_linear_forward_noalloc(void* stream, const void* weight_f16, const voi
                                  int64_t M, int64_t N, int64_t K, int op, int out_kind, int out_layout,
                                  const void* alpha);
 
-/* Every wait inside the kernels is time-bounded (about one second). A wait that runs out makes its kernel
- * drain and exit normally and records a small positive code in a per-device status word; the results of
- * that launch are then undefined. This call synchronises with the device, returns the word (0 = no wait
+/* Every wait inside the kernels is time-bounded (about 0.2 s of SM clock). A wait that runs out makes its kernel
+ * drain and exit normally and records a small positive code in a per-device status word (11-18: tile-per-CTA
+ * GEMM, 21-29: persistent GEMM; the number names the barrier that was not reached); the results of that launch
+ * are then undefined. This call synchronises with the device, returns the word (0 = no wait
  * ever ran out) and clears it when `reset` is non-zero. The reference has no counterpart: its kernels
  * have no inter-thread waits beyond __syncthreads (kernel_matmul.cuh:458-459,507-508).                   */
 int bgemm_device_status(int reset);
