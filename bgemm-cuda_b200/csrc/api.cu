@@ -82,8 +82,9 @@ size_t bgemm_plane_bytes(int64_t M, int64_t K) {
 int64_t bgemm_act_ld(int64_t K) { return K < 1 ? 0 : (K + 255) / 256 * 256; }
 
 int bgemm_version(void) { return 100; }
-// Tuning aid (not declared in the public header): device buffer of 16 int64 per CTA that the GEMM fills
-// with phase stamps; pass NULL to switch it off again.
+// Tuning aid (not declared in the public header): device buffer that the GEMM kernels fill with phase stamps and
+// wait-time counters, 32 int64 per CTA; the persistent kernel appends an event trace of its CTA 0 (8 x 1024 int64
+// behind the per-CTA slots), so size it for (CTAs of the launch) * 32 + 8192 entries. Pass NULL to switch it off.
 void bgemm_debug_set_profile_buffer(void* dev_buffer) { g_prof = static_cast<long long*>(dev_buffer); }
 uint64_t bgemm_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
 
