@@ -25,7 +25,7 @@ lib = ctypes.CDLL(str(_LIB_PATH))
 DT_F16, DT_BF16, DT_F32, DT_I8 = 0, 1, 2, 3
 OP_AND, OP_XOR, OP_ATTN, OP_BWTA = 0, 1, 2, 3
 WBIT_NEGATIVE, WBIT_NONNEGATIVE, WBIT_NONZERO, WBIT_NEGATIVE_NZ = 0, 1, 2, 3
-ACT_SIGN, ACT_TERNARY, ACT_NEG01 = 0, 1, 2
+ACT_SIGN, ACT_TERNARY, ACT_NEG01, ACT_INT8 = 0, 1, 2, 3
 OUT_I32, OUT_F16, OUT_F16_SCALED = 0, 1, 2
 LAYOUT_NM, LAYOUT_MN = 0, 1
 ACT_MODE_OF_OP = {OP_AND: ACT_NEG01, OP_XOR: ACT_SIGN, OP_ATTN: ACT_SIGN, OP_BWTA: ACT_TERNARY}

@@ -142,7 +142,8 @@ int bgemm_pack_weights(void* stream, const void* src, int src_dtype, int64_t M, 
 int bgemm_prepare_acts(void* stream, const void* src, int src_dtype, int64_t N, int64_t K, int64_t ld, int act_mode, int transpose,
                        int8_t* dst, int32_t* colsum, int64_t batch, int64_t src_batch_stride) {
     if (!src || !dst || !colsum) return BGEMM_ERR_NULL;
-    if (!valid_dtype(src_dtype) || act_mode < 0 || act_mode > 2) return BGEMM_ERR_ENUM;
+    if (!valid_dtype(src_dtype) || act_mode < 0 || act_mode > BGEMM_ACT_INT8) return BGEMM_ERR_ENUM;
+    if (act_mode == BGEMM_ACT_INT8 && src_dtype != BGEMM_DT_I8) return BGEMM_ERR_UNSUPPORTED;
     if (N < 1 || K < 1 || batch < 1 || batch > 65535 || N > kMaxDim || K > kMaxDim) return BGEMM_ERR_SHAPE;
     if (ld < (transpose ? N : K)) return BGEMM_ERR_SHAPE;
     if (!aligned(dst, 16) || !aligned(src, dt_size(src_dtype))) return BGEMM_ERR_ALIGN;

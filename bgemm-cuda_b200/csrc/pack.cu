@@ -22,21 +22,25 @@ template <> struct Elem<__half> {
     static __host__ __device__ __forceinline__ int neg(const __half& v) { return (reinterpret_cast<const uint16_t&>(v) >> 15) & 1; }
     static __host__ __device__ __forceinline__ int zero(const __half& v) { return (reinterpret_cast<const uint16_t&>(v) & 0x7fffu) == 0; }
     static __device__ __forceinline__ float mag(const __half& v) { return fabsf(__half2float(v)); }
+    static __host__ __device__ __forceinline__ int8_t as_int8(const __half&) { return 0; }
 };
 template <> struct Elem<__nv_bfloat16> {
     static __host__ __device__ __forceinline__ int neg(const __nv_bfloat16& v) { return (reinterpret_cast<const uint16_t&>(v) >> 15) & 1; }
     static __host__ __device__ __forceinline__ int zero(const __nv_bfloat16& v) { return (reinterpret_cast<const uint16_t&>(v) & 0x7fffu) == 0; }
     static __device__ __forceinline__ float mag(const __nv_bfloat16& v) { return fabsf(__bfloat162float(v)); }
+    static __host__ __device__ __forceinline__ int8_t as_int8(const __nv_bfloat16&) { return 0; }
 };
 template <> struct Elem<float> {
     static __host__ __device__ __forceinline__ int neg(const float& v) { return (reinterpret_cast<const uint32_t&>(v) >> 31) & 1; }
     static __host__ __device__ __forceinline__ int zero(const float& v) { return (reinterpret_cast<const uint32_t&>(v) & 0x7fffffffu) == 0; }
     static __device__ __forceinline__ float mag(const float& v) { return fabsf(v); }
+    static __host__ __device__ __forceinline__ int8_t as_int8(const float&) { return 0; }
 };
 template <> struct Elem<int8_t> {
     static __host__ __device__ __forceinline__ int neg(const int8_t& v) { return v < 0; }
     static __host__ __device__ __forceinline__ int zero(const int8_t& v) { return v == 0; }
     static __device__ __forceinline__ float mag(const int8_t& v) { return fabsf((float)v); }
+    static __host__ __device__ __forceinline__ int8_t as_int8(const int8_t& v) { return v; }
 };
 
 // Byte offset of word c (0..7) of row r (0..127) inside a 4096-byte tile: two 2 KB halves, each holding
@@ -160,6 +164,7 @@ __device__ __forceinline__ int8_t act_value(const T& v, int mode) {
     const int neg = Elem<T>::neg(v);
     if (mode == BGEMM_ACT_SIGN) return (int8_t)(1 - 2 * neg);
     if (mode == BGEMM_ACT_TERNARY) return Elem<T>::zero(v) ? (int8_t)0 : (int8_t)(1 - 2 * neg);
+    if (mode == BGEMM_ACT_INT8) return Elem<T>::as_int8(v);        // int8 sources only (checked at the entry point)
     return (int8_t)neg;
 }
 

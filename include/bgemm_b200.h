@@ -66,6 +66,9 @@ extern "C" {
 #define BGEMM_ACT_SIGN      0   /* -1 if sign bit else +1          (ops XOR, ATTN)                     */
 #define BGEMM_ACT_TERNARY   1   /* -1 / 0 / +1 = torch.sign        (op BWTA)                           */
 #define BGEMM_ACT_NEG01     2   /* 1 if sign bit else 0            (op AND)                            */
+#define BGEMM_ACT_INT8      3   /* int8 source values as they are: binary weight x int8 activation ("W1A8", listed as to-do
+                                   in the reference's README.md:29). Source dtype must be BGEMM_DT_I8; use with op BWTA
+                                   (result = sum_k sign(w) * x, exact in int32).                                          */
 
 /* ---- how the int32 result is stored ------------------------------------------------------------- */
 #define BGEMM_OUT_I32         0   /* int32 accumulators, untouched                                     */

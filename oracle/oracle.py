@@ -27,7 +27,7 @@ _HERE = Path(__file__).resolve().parent
 
 OP_AND, OP_XOR, OP_ATTN, OP_BWTA = 0, 1, 2, 3
 OUT_I32, OUT_F16, OUT_F16_SCALED = 0, 1, 2
-ACT_SIGN, ACT_TERNARY, ACT_NEG01 = 0, 1, 2
+ACT_SIGN, ACT_TERNARY, ACT_NEG01, ACT_INT8 = 0, 1, 2, 3
 ACT_MODE_OF_OP = {OP_AND: ACT_NEG01, OP_XOR: ACT_SIGN, OP_ATTN: ACT_SIGN, OP_BWTA: ACT_TERNARY}
 WBIT_OF_OP = {OP_AND: 0, OP_XOR: 0, OP_ATTN: 1, OP_BWTA: 0}
 
@@ -259,6 +259,8 @@ def np_prepare_acts(x, act_mode: int):
         v = (1 - 2 * s.to(torch.int8))
     elif act_mode == ACT_TERNARY:
         v = torch.sign(xt.float()).to(torch.int8)
+    elif act_mode == ACT_INT8:
+        v = xt.to(torch.int8)
     else:
         v = s.to(torch.int8)
     N, K = v.shape

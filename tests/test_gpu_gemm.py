@@ -359,6 +359,27 @@ def test_weight_streaming_shapes(B, M, K, N, batch, layout):
     assert B.lib.bgemm_device_status(1) == 0
 
 
+@pytest.mark.parametrize("M,K,N,split_k", [(256, 512, 33, 1), (1000, 4096, 128, 0), (4096, 2048, 16, 4), (130, 300, 7, 0)])
+def test_binary_weight_int8_activation(B, M, K, N, split_k):
+    """W1A8: int8 activations go through prepare_acts unchanged (BGEMM_ACT_INT8) and op BWTA gives
+    sum_k sign(w) * x exactly (|acc| <= 127 K)."""
+    g = O._gen(M + K + N)
+    w = torch.randn(M, K, generator=g).to(torch.float16)
+    x = torch.randint(-127, 128, (N, K), generator=g, dtype=torch.int8)
+    want = (x.to(torch.float64) @ O.map_weight(w, O.OP_BWTA).to(torch.float64).t()).to(torch.int32)
+    plane, _, _ = B.pack_weights(w.cuda(), B.WBIT_OF_OP[O.OP_BWTA])
+    acts, colsum = B.prepare_acts(x.cuda(), B.ACT_INT8)
+    ra, rcs = O.np_prepare_acts(x, O.ACT_INT8)
+    assert np.array_equal(acts.cpu().numpy(), ra) and np.array_equal(colsum.cpu().numpy(), rcs)
+    got = B.gemm(plane, M, K, acts, colsum, O.OP_BWTA, O.OUT_I32, 0, None, split_k).cpu()
+    assert torch.equal(got, want)
+    # fp16 activations are refused for this mode before anything is launched
+    xh = torch.zeros(4, 256, dtype=torch.float16, device="cuda")
+    dst = torch.empty(4, 256, dtype=torch.int8, device="cuda")
+    cs = torch.empty(4, dtype=torch.int32, device="cuda")
+    assert B.lib.bgemm_prepare_acts(None, xh.data_ptr(), 0, 4, 256, 256, B.ACT_INT8, 0, dst.data_ptr(), cs.data_ptr(), 1, 0) == -6
+
+
 def test_seeded_random_shapes(B):
     """Sixty seeded random problems over every knob of bgemm_gemm (op, shape, batch, K partitioning, output kind and
     layout) and of bgemm_gemm_to_acts, each against the oracle."""
