@@ -50,7 +50,7 @@ L2_BYTES = 126 * 1024 * 1024
 # dram__bytes_read.sum + dram__bytes_write.sum per layer of the batched GEMM launch (gemm_persist_kernel), from the ncu
 # capture summarised under profiles/ (80 layers captured; traffic grows in proportion to the layer count). Workloads
 # without a capture: null.
-NCU_DRAM_BYTES_PER_LAYER = {"c2": 268.95e6 / 80}     # profiles/gemm_persist_kernel_bwta_4096x4096x128_batched80.md
+NCU_DRAM_BYTES_PER_LAYER = {"c2": 270.15e6 / 80}     # profiles/gemm_persist_kernel_bwta_4096x4096x128_batched80.md
 METRIC = "bwta_effective_tops"
 UNIT = "TOPS (2*M*N*K/s)"
 
