@@ -23,13 +23,13 @@ lib = ctypes.CDLL(str(_LIB_PATH))
 
 # ---- constants of include/bgemm_b200.h ----
 DT_F16, DT_BF16, DT_F32, DT_I8 = 0, 1, 2, 3
-OP_AND, OP_XOR, OP_ATTN, OP_BWTA = 0, 1, 2, 3
+OP_AND, OP_XOR, OP_ATTN, OP_BWTA, OP_W1A8 = 0, 1, 2, 3, 4
 WBIT_NEGATIVE, WBIT_NONNEGATIVE, WBIT_NONZERO, WBIT_NEGATIVE_NZ = 0, 1, 2, 3
 ACT_SIGN, ACT_TERNARY, ACT_NEG01, ACT_INT8 = 0, 1, 2, 3
 OUT_I32, OUT_F16, OUT_F16_SCALED = 0, 1, 2
 LAYOUT_NM, LAYOUT_MN = 0, 1
-ACT_MODE_OF_OP = {OP_AND: ACT_NEG01, OP_XOR: ACT_SIGN, OP_ATTN: ACT_SIGN, OP_BWTA: ACT_TERNARY}
-WBIT_OF_OP = {OP_AND: WBIT_NEGATIVE, OP_XOR: WBIT_NEGATIVE, OP_ATTN: WBIT_NONNEGATIVE, OP_BWTA: WBIT_NEGATIVE}
+ACT_MODE_OF_OP = {OP_AND: ACT_NEG01, OP_XOR: ACT_SIGN, OP_ATTN: ACT_SIGN, OP_BWTA: ACT_TERNARY, OP_W1A8: ACT_INT8}
+WBIT_OF_OP = {OP_AND: WBIT_NEGATIVE, OP_XOR: WBIT_NEGATIVE, OP_ATTN: WBIT_NONNEGATIVE, OP_BWTA: WBIT_NEGATIVE, OP_W1A8: WBIT_NEGATIVE}
 
 _i64, _int, _vp, _sz = ctypes.c_int64, ctypes.c_int, ctypes.c_void_p, ctypes.c_size_t
 lib.bgemm_plane_bytes.restype = _sz

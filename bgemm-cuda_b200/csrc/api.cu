@@ -169,7 +169,7 @@ int bgemm_gemm(void* stream, const void* plane, int64_t M, int64_t K, const int8
                void* out, int out_kind, int out_layout, const void* alpha, int split_k, void* workspace, size_t workspace_bytes,
                int64_t batch) {
     if (!plane || !acts || !colsum || !out) return BGEMM_ERR_NULL;
-    if (op < BGEMM_OP_AND || op > BGEMM_OP_BWTA || out_kind < BGEMM_OUT_I32 || out_kind > BGEMM_OUT_F16_SCALED ||
+    if (op < BGEMM_OP_AND || op > BGEMM_OP_W1A8 || out_kind < BGEMM_OUT_I32 || out_kind > BGEMM_OUT_F16_SCALED ||
         out_layout < BGEMM_LAYOUT_NM || out_layout > BGEMM_LAYOUT_MN)
         return BGEMM_ERR_ENUM;
     if (out_kind == BGEMM_OUT_F16_SCALED && !alpha) return BGEMM_ERR_NULL;
@@ -193,7 +193,8 @@ int bgemm_gemm(void* stream, const void* plane, int64_t M, int64_t K, const int8
     p.kblocks = (int)((K + 255) / 256);
     p.mtiles = (int)mtiles;
     p.split_k = s;
-    p.epi = (op == BGEMM_OP_XOR || op == BGEMM_OP_BWTA) ? 1 : 0;
+    p.epi = (op == BGEMM_OP_XOR || op == BGEMM_OP_BWTA || op == BGEMM_OP_W1A8) ? 1 : 0;
+    p.acts_general = op == BGEMM_OP_W1A8 ? 1 : 0;
     p.out_kind = out_kind;
     p.out_layout = out_layout;
     p.plane_batch_bytes = (long long)bgemm_plane_bytes(M, K);

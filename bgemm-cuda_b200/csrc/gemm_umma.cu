@@ -514,6 +514,9 @@ int gemm_tile_n(long long N) {
 }
 
 int launch_gemm(cudaStream_t stream, GemmParams p, const int8_t* acts, long long act_ld, long long batch) {
+    // A handful of activation rows: pure weight streaming, served by the CUDA-core kernel (no tensor-memory set-up,
+    // no 16-column tile, no cluster reduction).
+    if (skinny_supported(p, batch, !p.acts_general)) return launch_gemm_skinny(stream, p, acts, act_ld, batch);
     EncodeTiledFn encode = get_encode_fn();
     if (!encode) return BGEMM_ERR_DRIVER;
     const int NT = gemm_tile_n(p.N);

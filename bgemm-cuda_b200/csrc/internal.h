@@ -31,6 +31,7 @@ struct GemmParams {
     int32_t* colsum_next;
     long long out_ld;
     int act_mode;
+    int acts_general;             // 1: the caller declared general int8 activations (op W1A8); 0: at most ternary expected
 };
 
 constexpr int kOutActs = 100;     // internal out_kind of bgemm_gemm_to_acts
@@ -48,6 +49,10 @@ int launch_gemm(cudaStream_t stream, GemmParams p, const int8_t* acts, long long
 bool persistent_supported(int NT);
 bool persistent_kblocks_ok(int NT, int kblocks);   // K-block counts per tile the issuers' hand-over protocol covers
 int launch_gemm_persistent(cudaStream_t stream, const void* tensor_map, const GemmParams& p, int NT, long long total_tiles, int ctas);
+
+// Weight-streaming CUDA-core kernel for N <= 8 (gemm_skinny.cu).
+bool skinny_supported(const GemmParams& p, long long batch, bool ternary_acts_expected);
+int launch_gemm_skinny(cudaStream_t stream, const GemmParams& p, const int8_t* acts, long long act_ld, long long batch);
 
 int launch_pack_weights(cudaStream_t stream, const void* src, int dtype, long long M, long long K, long long ld, int wbit_mode,
                         void* plane, int32_t* rowpop, void* alpha, long long batch, long long src_batch_stride);

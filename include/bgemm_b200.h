@@ -55,6 +55,9 @@ extern "C" {
 #define BGEMM_OP_XOR   1   /* C[n,m] = sum_k sgn(w) sgn(x), both in {-1,+1}  (ptx_mma.cuh:212-250)     */
 #define BGEMM_OP_ATTN  2   /* C[n,m] = sum_k [w >= 0] sgn(x): w-slot is a {0,1} mask (ptx_mma.cuh:252-337) */
 #define BGEMM_OP_BWTA  3   /* C[n,m] = sum_k sgn(w) t(x), t = torch.sign in {-1,0,+1} (bgemm_linear.py:241,270-272) */
+#define BGEMM_OP_W1A8  4   /* C[n,m] = sum_k sgn(w) x, x any int8 (prepared with BGEMM_ACT_INT8). Same arithmetic as BWTA, which
+                              also returns exact results for such x; this code only tells bgemm_gemm not to expect ternary
+                              activations, which keeps N = 3..8 on the tensor-core kernel (accepted by bgemm_gemm only) */
 
 /* ---- how a weight-slot row is turned into a bit (bgemm_pack_weights mode) ----------------------- */
 #define BGEMM_WBIT_NEGATIVE     0   /* bit = sign bit            (ops AND, XOR, BWTA)                   */

@@ -26,6 +26,7 @@ import torch
 _HERE = Path(__file__).resolve().parent
 
 OP_AND, OP_XOR, OP_ATTN, OP_BWTA = 0, 1, 2, 3
+OP_W1A8 = 4          # BWTA's arithmetic on general int8 activations (a routing hint of the library, not a new formula)
 OUT_I32, OUT_F16, OUT_F16_SCALED = 0, 1, 2
 ACT_SIGN, ACT_TERNARY, ACT_NEG01, ACT_INT8 = 0, 1, 2, 3
 ACT_MODE_OF_OP = {OP_AND: ACT_NEG01, OP_XOR: ACT_SIGN, OP_ATTN: ACT_SIGN, OP_BWTA: ACT_TERNARY}
