@@ -140,6 +140,8 @@ int bgemm_prepare_acts(void* stream, const void* src, int src_dtype, int64_t N, 
  *   acts      int8 [N, bgemm_act_ld(K)] and colsum int32 [N] (bgemm_prepare_acts with the mode of `op`)
  *   out       BGEMM_LAYOUT_NM: [N, M]; BGEMM_LAYOUT_MN: [M, N]; element type per out_kind
  *   alpha     fp16 [M], required for BGEMM_OUT_F16_SCALED, else may be NULL
+ *   N <= 4    (N <= 2 for ops AND / ATTN / W1A8) is served by a weight-streaming kernel on the CUDA cores, for which
+ *             split_k and workspace have no meaning (they are validated and ignored); results are the same bits.
  *   split_k   >= 1 forces that many K partitions, 0 lets the library choose (at most 8). Up to 8 partitions
  *             are reduced on chip (thread-block cluster + distributed shared memory) and need no workspace.
  *   workspace needed only when split_k > 8: bgemm_gemm_workspace_bytes() bytes, 256-byte aligned.
