@@ -3,8 +3,10 @@
 // At N <= 8 the product is pure HBM streaming of the packed weight plane (one bit per weight), and the tensor-core
 // path pays for a 16-column UMMA tile, tensor-memory set-up and a cluster reduction that together cost several
 // times the streaming time (28672 x 8192: 24 us against 4.5 us of HBM time). This kernel keeps the work on the
-// CUDA cores, where it is cheap enough to hide behind the loads. A lane owns one weight row and reads its 32 packed
-// bytes of a 256-column K block with two coalesced 16-byte loads (the tiled plane keeps 128 rows x 16 B contiguous).
+// CUDA cores, where it is cheap enough to hide behind the loads. A lane owns one weight row and fetches its 32 packed
+// bytes of a 256-column K block with two coalesced 16-byte asynchronous copies (the tiled plane keeps 128 rows x 16 B
+// contiguous) into a ring in shared memory that only this lane reads back: up to 12 K blocks per lane, 192 KB per
+// SM, are in flight from the first instruction on, and cp.async group counting is all the synchronisation it needs.
 //
 //   popc path   activations in {-1, 0, +1} and a result of the form colsum - 2 D (ops XOR and BWTA): the CTA first
 //               turns the int8 activations into two bit planes in the weight plane's own bit order (non-zero, negative);
@@ -20,8 +22,8 @@
 // Replaces the same reference functions as gemm_umma.cu (PACK_BGEMM_Kernel, kernel_matmul.cuh:370-547, which does
 // not accept N < 32 at all) for the shapes named above.
 //
-// One CTA of 16 warps per SM (two while shared memory allows) walks over a contiguous range of 32-row groups, so the
-// activations are turned into planes once per CTA; `ks` warps share the K blocks of a group and meet in shared memory.
+// One CTA of 16 warps per SM walks over a contiguous range of 32-row groups, so the activations are turned into
+// planes once per CTA; `ks` warps share the K blocks of a group and meet in shared memory.
 #include <cuda_fp16.h>
 
 #include <cstdlib>
@@ -31,7 +33,7 @@
 
 namespace bgemm {
 
-constexpr int kSkinnyMaxSmem = 160 * 1024;
+constexpr int kSkinnyMaxSmem = 224 * 1024;
 
 __device__ __forceinline__ int dp4a_u8s8(uint32_t a, uint32_t b, int c) {
     int d;
@@ -117,12 +119,19 @@ __device__ __forceinline__ bool skinny_is_ternary(uint32_t x4) {      // every b
     return __vcmpgtu4(__vadd4(x4, 0x01010101u), 0x02020202u) == 0u;
 }
 
+__device__ __forceinline__ void cp_async16(uint32_t dst_smem, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst_smem), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
 constexpr int kSkinnyThreads = 512;                // 16 warps = (groups in flight) x (K shares)
 constexpr int kSkinnyPiece = 8 * 1024;             // columns staged per pass and row by the N > 2 variants
 
 // `ks` warps share the K blocks of one 32-row group (ks in {1, 2, 4, 8, 16}); the CTA works on 16 / ks groups at a
 // time and owns the contiguous range of groups [groups * b / gridDim.x, groups * (b + 1) / gridDim.x).
-template <int NN>
+template <int NN, int D>
 __global__ void __launch_bounds__(kSkinnyThreads) gemm_skinny_kernel(const GemmParams p, const int8_t* __restrict__ acts, long long act_ld,
                                                                      int groups, int ks) {
     constexpr bool STAGE = NN <= 2;              // whole int8 activations stay in shared memory (they feed the dp4a path)
@@ -133,6 +142,10 @@ __global__ void __launch_bounds__(kSkinnyThreads) gemm_skinny_kernel(const GemmP
     int* red = reinterpret_cast<int*>(planes + (size_t)p.kblocks * NN * 16); // [16 warps][NN][32]
     int* s_pn = red + 16 * NN * 32;                                         // [8] non-zero activations per row
     int8_t* sx = reinterpret_cast<int8_t*>(s_pn + 8);                       // [NN][x_pitch] (STAGE) or [NN][piece]
+    const int piece = STAGE ? x_pitch : (x_pitch < kSkinnyPiece ? x_pitch : kSkinnyPiece);   // columns staged per pass, all rows at once
+    // Weight ring: D slots of 32 bytes per lane, [slot][lo | hi][thread]. A lane only ever reads what it copied itself,
+    // so cp.async group accounting is all the synchronisation the ring needs.
+    uint4* ring = reinterpret_cast<uint4*>(sx + (size_t)NN * piece);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int batch = blockIdx.y;
     const int gs = 16 / ks;                      // groups in flight
@@ -146,58 +159,66 @@ __global__ void __launch_bounds__(kSkinnyThreads) gemm_skinny_kernel(const GemmP
     const int8_t* src = acts + (size_t)batch * p.N * act_ld;
     const uint8_t* plane = p.plane + (size_t)batch * p.plane_batch_bytes;
 
-    // Loads of one item: U K blocks of this lane's weight row of group g.
-    constexpr int U = NN >= 8 ? 2 : 4;           // K blocks per item
-    auto load_item = [&](uint4 (&l)[U], uint4 (&h)[U], int g, int kb) {
-        const uint8_t* wrow = plane + (size_t)(g >> 2) * p.kblocks * 4096 + (size_t)((g & 3) * 32 + lane) * 16;
-#pragma unroll
-        for (int u = 0; u < U; u++) {
-            if (kb + u < kb1) {
-                l[u] = __ldcs(reinterpret_cast<const uint4*>(wrow + (size_t)(kb + u) * 4096));
-                h[u] = __ldcs(reinterpret_cast<const uint4*>(wrow + (size_t)(kb + u) * 4096 + 2048));
-            }
-        }
-    };
-    // The warp's work is a sequence of items (group, U K blocks), two of them in flight at any time. The first two
-    // leave before the activations are looked at: the weights do not depend on them.
+    // The warp's work is a sequence of units (group, K block). D of them are in flight per lane at any time, as
+    // 16-byte asynchronous copies into the lane's ring slots: with D = 12 that is 192 KB per SM, the SM's whole share
+    // of a 28672 x 8192 plane, so the loads of a launch all leave at its start.
     auto advance = [&](int& g, int& kb) {
-        kb += U;
-        if (kb >= kb1) { kb = kb0; g += gs; }
+        if (++kb >= kb1) { kb = kb0; g += gs; }
     };
-    uint4 loA[U], hiA[U], loB[U], hiB[U];
+    auto issue = [&](int slot, int g, int kb) {      // always closes a group, so that the group count per unit stays one
+        if (g < g_end) {
+            const uint8_t* w = plane + ((size_t)(g >> 2) * p.kblocks + kb) * 4096 + (size_t)((g & 3) * 32 + lane) * 16;
+            cp_async16(smem_u32(ring + (slot * 2 + 0) * kSkinnyThreads + tid), w);
+            cp_async16(smem_u32(ring + (slot * 2 + 1) * kSkinnyThreads + tid), w + 2048);
+        }
+        cp_async_commit();
+    };
+    // The (small) activation loads go first: issued behind two thirds of the weight traffic they would come back last
+    // and hold up the whole CTA.
+    auto load_x = [&](int i, int base, int chunks) {
+        const int n = i / chunks, k0 = base + (i - n * chunks) * 16;
+        return (n < p.N && k0 < p.K) ? *reinterpret_cast<const uint4*>(src + (size_t)n * act_ld + k0) : make_uint4(0u, 0u, 0u, 0u);
+    };
+    constexpr int XR = NN;                       // activation chunks per thread fetched ahead (covers K <= 8192)
+    uint4 xv[XR];
 #pragma unroll
-    for (int u = 0; u < U; u++) loA[u] = hiA[u] = loB[u] = hiB[u] = make_uint4(0u, 0u, 0u, 0u);
-    int gc = g_begin + team, kc = kb0;           // item being computed
-    int gl = gc, kl = kc;                        // next item to load
-    if (gl < g_end) { load_item(loA, hiA, gl, kl); advance(gl, kl); }
-    if (gl < g_end) { load_item(loB, hiB, gl, kl); advance(gl, kl); }
+    for (int r = 0; r < XR; r++) {
+        const int i = tid + r * kSkinnyThreads;
+        xv[r] = i < NN * (piece / 16) ? load_x(i, 0, piece / 16) : make_uint4(0u, 0u, 0u, 0u);
+    }
+    int gc = g_begin + team, kc = kb0;           // unit being computed
+    int gl = gc, kl = kc;                        // next unit to load
+#pragma unroll 1
+    for (int d = 0; d < D; d++) { issue(d, gl, kl); advance(gl, kl); }
 
     // ---- activations: int8 -> shared memory piece by piece (coalesced), checked for values outside {-1, 0, +1}, and
     //      turned into bit planes in the weight plane's bit order. Rows beyond N and columns beyond K become zero.
     bool tern = true;
     {
-        const int piece = STAGE ? x_pitch : (x_pitch < kSkinnyPiece ? x_pitch : kSkinnyPiece);   // columns per pass, all rows at once
         int nonzero[NN];
 #pragma unroll
         for (int n = 0; n < NN; n++) nonzero[n] = 0;
         for (int base = 0; base < x_pitch; base += piece) {
             const int len = x_pitch - base < piece ? x_pitch - base : piece;
             const int chunks = len / 16;
-            for (int i = tid; i < NN * chunks; i += kSkinnyThreads) {
+            auto put_x = [&](int i, uint4 v) {
                 const int n = i / chunks, k0 = base + (i - n * chunks) * 16;
-                uint4 v = make_uint4(0u, 0u, 0u, 0u);
-                if (n < p.N && k0 < p.K) {
-                    v = *reinterpret_cast<const uint4*>(src + (size_t)n * act_ld + k0);
-                    if (k0 + 16 > p.K) {
-                        uint32_t* q = reinterpret_cast<uint32_t*>(&v);
+                if (k0 + 16 > p.K) {                                            // columns from K on read as zero
+                    uint32_t* q = reinterpret_cast<uint32_t*>(&v);
 #pragma unroll
-                        for (int b = 0; b < 16; b++)
-                            if (k0 + b >= p.K) q[b >> 2] &= ~(0xffu << (8 * (b & 3)));
-                    }
+                    for (int b = 0; b < 16; b++)
+                        if (k0 + b >= p.K) q[b >> 2] &= ~(0xffu << (8 * (b & 3)));
                 }
                 tern = tern && skinny_is_ternary(v.x) && skinny_is_ternary(v.y) && skinny_is_ternary(v.z) && skinny_is_ternary(v.w);
                 *reinterpret_cast<uint4*>(sx + (size_t)n * piece + (k0 - base)) = v;
+            };
+            int i = tid;
+            if (base == 0) {                                                    // fetched ahead
+#pragma unroll
+                for (int r = 0; r < XR; r++, i += kSkinnyThreads)
+                    if (i < NN * chunks) put_x(i, xv[r]);
             }
+            for (; i < NN * chunks; i += kSkinnyThreads) put_x(i, load_x(i, base, chunks));
             __syncthreads();
             const int words = len / 32;                                         // items per row: word c of K block kb, both planes
 #pragma unroll
@@ -259,20 +280,22 @@ __global__ void __launch_bounds__(kSkinnyThreads) gemm_skinny_kernel(const GemmP
         for (int n = 0; n < (STAGE ? NN : 1); n++)
 #pragma unroll
             for (int j = 0; j < 8; j++) acc[n][j] = 0;
-        auto step = [&](uint4 (&bl)[U], uint4 (&bh)[U]) {
-#pragma unroll
-            for (int u = 0; u < U; u++) {
-                if (kc + u < kb1) {
-                    if (popc_path) {
-                        skinny_block_popc<NN>(bl[u], bh[u], planes + (size_t)(kc + u) * NN * 16, 16, cnt);
-                    } else if (STAGE) {
-                        skinny_block_dp4a<STAGE ? NN : 1>(bl[u], bh[u], sx + (size_t)(kc + u) * 256, x_pitch, acc);
-                    }
-                }
+        int slot = 0;
+        while (gc < g_end) {
+            cp_async_wait<D - 1>();                                         // the oldest of the D units in flight has landed
+            const uint4 lo = ring[(slot * 2 + 0) * kSkinnyThreads + tid];
+            const uint4 hi = ring[(slot * 2 + 1) * kSkinnyThreads + tid];
+            if (popc_path) {
+                skinny_block_popc<NN>(lo, hi, planes + (size_t)kc * NN * 16, 16, cnt);
+            } else if (STAGE) {
+                skinny_block_dp4a<STAGE ? NN : 1>(lo, hi, sx + (size_t)kc * 256, x_pitch, acc);
             }
-            // the buffer is free again: its next item leaves before this warp may wait at the team's barrier
-            if (gl < g_end) { load_item(bl, bh, gl, kl); advance(gl, kl); }
-            if (kc + U >= kb1) {                                            // the group is complete
+            // The slot's words have been consumed (the arithmetic above waited for them), so the slot may be
+            // overwritten: its next unit leaves before this warp may wait at the team's barrier.
+            issue(slot, gl, kl);
+            advance(gl, kl);
+            slot = slot + 1 == D ? 0 : slot + 1;
+            if (kc + 1 >= kb1) {                                            // the group is complete
 #pragma unroll
                 for (int n = 0; n < NN; n++) {
                     int d;
@@ -289,11 +312,6 @@ __global__ void __launch_bounds__(kSkinnyThreads) gemm_skinny_kernel(const GemmP
                 reduce_store(gc);
             }
             advance(gc, kc);
-        };
-        while (gc < g_end) {
-            step(loA, hiA);
-            if (gc >= g_end) break;
-            step(loB, hiB);
         }
     } else {
         // N = 3..8 with activations that are not ternary after all: correct, not fast. One activation row at a time
@@ -321,6 +339,7 @@ __global__ void __launch_bounds__(kSkinnyThreads) gemm_skinny_kernel(const GemmP
             reduce_store(g);
         }
     }
+    cp_async_wait<0>();                          // nothing of this thread's is in flight when it leaves
 }
 
 static size_t skinny_smem_bytes(int NN, int kblocks) {
@@ -328,9 +347,11 @@ static size_t skinny_smem_bytes(int NN, int kblocks) {
     return (size_t)kblocks * NN * 64 + (size_t)16 * NN * 32 * sizeof(int) + 32 + stage;
 }
 
-template <int NN>
+constexpr size_t kSkinnyRingSlot = (size_t)kSkinnyThreads * 32;   // bytes of one ring slot over the CTA
+
+template <int NN, int D>
 static int launch_skinny_variant(cudaStream_t stream, const GemmParams& p, const int8_t* acts, long long act_ld, long long batch) {
-    const size_t smem = skinny_smem_bytes(NN, p.kblocks);
+    const size_t smem = skinny_smem_bytes(NN, p.kblocks) + D * kSkinnyRingSlot;
     const long long groups = (long long)p.mtiles * 4;
     const int threads = kSkinnyThreads;
     static bool configured[64] = {};
@@ -338,7 +359,7 @@ static int launch_skinny_variant(cudaStream_t stream, const GemmParams& p, const
     cudaGetDevice(&dev);
     if (dev < 0 || dev >= 64) return BGEMM_ERR_DRIVER;
     if (!configured[dev]) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_skinny_kernel<NN>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSkinnyMaxSmem);
+        cudaError_t e = cudaFuncSetAttribute(gemm_skinny_kernel<NN, D>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSkinnyMaxSmem);
         if (e != cudaSuccess) return (int)e;
         configured[dev] = true;
     }
@@ -347,7 +368,7 @@ static int launch_skinny_variant(cudaStream_t stream, const GemmParams& p, const
     static thread_local int cached_threads = 0, cached_dev = -1, cached_per_sm = 0;
     if (cached_smem != smem || cached_threads != threads || cached_dev != dev) {
         int n = 0;
-        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, gemm_skinny_kernel<NN>, threads, smem) != cudaSuccess || n < 1) n = 1;
+        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, gemm_skinny_kernel<NN, D>, threads, smem) != cudaSuccess || n < 1) n = 1;
         cached_smem = smem; cached_threads = threads; cached_dev = dev; cached_per_sm = n;
     }
     const int per_sm = cached_per_sm;
@@ -370,13 +391,13 @@ static int launch_skinny_variant(cudaStream_t stream, const GemmParams& p, const
         cfg.attrs = attr;
         cfg.numAttrs = 1;
     }
-    const cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_skinny_kernel<NN>, p, acts, act_ld, (int)groups, ks);
+    const cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_skinny_kernel<NN, D>, p, acts, act_ld, (int)groups, ks);
     count_launch();
     return (int)(e != cudaSuccess ? e : cudaGetLastError());
 }
 
 // Largest N served here (tuning override: BGEMM_SKINNY_MAX_N, 0 switches the kernel off). Measured against the
-// tensor-core path (24 us at any N <= 16 for 28672 x 8192): N = 1 / 2 / 4 take 11 / 14 / 18 us here, N = 8 takes 26 us.
+// tensor-core path (24 us at any N <= 16 for 28672 x 8192): N = 1 / 2 / 4 take 11 / 13.5 / 17 us here, N = 8 takes 26 us.
 static int skinny_max_n() {
     static const int v = [] {
         const char* e = std::getenv("BGEMM_SKINNY_MAX_N");
@@ -392,14 +413,23 @@ bool skinny_supported(const GemmParams& p, long long batch, bool ternary_acts_ex
     if (p.N > 2 && !(p.epi && ternary_acts_expected)) return false;
     const int NN = p.N <= 1 ? 1 : (p.N <= 2 ? 2 : (p.N <= 4 ? 4 : 8));
     // the activation planes must fit in shared memory, and accumulator 7 (weights of 128) must stay inside int32
-    return skinny_smem_bytes(NN, p.kblocks) <= (size_t)kSkinnyMaxSmem && p.K <= 65536;
+    return skinny_smem_bytes(NN, p.kblocks) + 4 * kSkinnyRingSlot <= (size_t)kSkinnyMaxSmem && p.K <= 65536;
+}
+
+// Deepest weight ring (12, 8 or 4 K blocks per lane) that fits beside the activation planes.
+template <int NN>
+static int launch_skinny_depth(cudaStream_t stream, const GemmParams& p, const int8_t* acts, long long act_ld, long long batch) {
+    const size_t base = skinny_smem_bytes(NN, p.kblocks);
+    if (base + 12 * kSkinnyRingSlot <= (size_t)kSkinnyMaxSmem) return launch_skinny_variant<NN, 12>(stream, p, acts, act_ld, batch);
+    if (base + 8 * kSkinnyRingSlot <= (size_t)kSkinnyMaxSmem) return launch_skinny_variant<NN, 8>(stream, p, acts, act_ld, batch);
+    return launch_skinny_variant<NN, 4>(stream, p, acts, act_ld, batch);
 }
 
 int launch_gemm_skinny(cudaStream_t stream, const GemmParams& p, const int8_t* acts, long long act_ld, long long batch) {
-    if (p.N <= 1) return launch_skinny_variant<1>(stream, p, acts, act_ld, batch);
-    if (p.N <= 2) return launch_skinny_variant<2>(stream, p, acts, act_ld, batch);
-    if (p.N <= 4) return launch_skinny_variant<4>(stream, p, acts, act_ld, batch);
-    return launch_skinny_variant<8>(stream, p, acts, act_ld, batch);
+    if (p.N <= 1) return launch_skinny_depth<1>(stream, p, acts, act_ld, batch);
+    if (p.N <= 2) return launch_skinny_depth<2>(stream, p, acts, act_ld, batch);
+    if (p.N <= 4) return launch_skinny_depth<4>(stream, p, acts, act_ld, batch);
+    return launch_skinny_depth<8>(stream, p, acts, act_ld, batch);
 }
 
 }  // namespace bgemm
