@@ -165,11 +165,17 @@ __global__ void __launch_bounds__(kSkinnyThreads) gemm_skinny_kernel(const GemmP
     auto advance = [&](int& g, int& kb) {
         if (++kb >= kb1) { kb = kb0; g += gs; }
     };
-    auto issue = [&](int slot, int g, int kb) {      // always closes a group, so that the group count per unit stays one
-        if (g < g_end) {
-            const uint8_t* w = plane + ((size_t)(g >> 2) * p.kblocks + kb) * 4096 + (size_t)((g & 3) * 32 + lane) * 16;
-            cp_async16(smem_u32(ring + (slot * 2 + 0) * kSkinnyThreads + tid), w);
-            cp_async16(smem_u32(ring + (slot * 2 + 1) * kSkinnyThreads + tid), w + 2048);
+    // Address of this lane's 16 bytes ("lo" half; "hi" is 2048 further) of unit (g, kb). The loop below keeps a running
+    // pointer instead (next K block: + 4096) and only comes back here when the group changes.
+    auto unit_ptr = [&](int g, int kb) {
+        return plane + ((size_t)(g >> 2) * p.kblocks + kb) * 4096 + (size_t)((g & 3) * 32 + lane) * 16;
+    };
+    constexpr uint32_t kSlotBytes = 2u * kSkinnyThreads * 16u;
+    const uint32_t ring_addr = smem_u32(ring + tid);
+    auto issue = [&](int slot, bool live, const uint8_t* w) {   // always closes a group: one group per unit
+        if (live) {
+            cp_async16(ring_addr + slot * kSlotBytes, w);
+            cp_async16(ring_addr + slot * kSlotBytes + kSlotBytes / 2, w + 2048);
         }
         cp_async_commit();
     };
@@ -188,8 +194,13 @@ __global__ void __launch_bounds__(kSkinnyThreads) gemm_skinny_kernel(const GemmP
     }
     int gc = g_begin + team, kc = kb0;           // unit being computed
     int gl = gc, kl = kc;                        // next unit to load
+    const uint8_t* wl = unit_ptr(gl, kl);        // where unit (gl, kl) lives
+    auto next_load = [&]() {                     // (gl, kl, wl) -> the following unit
+        wl += 4096;
+        if (++kl >= kb1) { kl = kb0; gl += gs; wl = unit_ptr(gl, kl); }
+    };
 #pragma unroll 1
-    for (int d = 0; d < D; d++) { issue(d, gl, kl); advance(gl, kl); }
+    for (int d = 0; d < D; d++) { issue(d, gl < g_end, wl); next_load(); }
 
     // ---- activations: int8 -> shared memory piece by piece (coalesced), checked for values outside {-1, 0, +1}, and
     //      turned into bit planes in the weight plane's bit order. Rows beyond N and columns beyond K become zero.
@@ -283,8 +294,8 @@ __global__ void __launch_bounds__(kSkinnyThreads) gemm_skinny_kernel(const GemmP
         int slot = 0;
         while (gc < g_end) {
             cp_async_wait<D - 1>();                                         // the oldest of the D units in flight has landed
-            const uint4 lo = ring[(slot * 2 + 0) * kSkinnyThreads + tid];
-            const uint4 hi = ring[(slot * 2 + 1) * kSkinnyThreads + tid];
+            const uint4* rs = ring + tid + slot * (2 * kSkinnyThreads);
+            const uint4 lo = rs[0], hi = rs[kSkinnyThreads];
             if (popc_path) {
                 skinny_block_popc<NN>(lo, hi, planes + (size_t)kc * NN * 16, 16, cnt);
             } else if (STAGE) {
@@ -292,8 +303,8 @@ __global__ void __launch_bounds__(kSkinnyThreads) gemm_skinny_kernel(const GemmP
             }
             // The slot's words have been consumed (the arithmetic above waited for them), so the slot may be
             // overwritten: its next unit leaves before this warp may wait at the team's barrier.
-            issue(slot, gl, kl);
-            advance(gl, kl);
+            issue(slot, gl < g_end, wl);
+            next_load();
             slot = slot + 1 == D ? 0 : slot + 1;
             if (kc + 1 >= kb1) {                                            // the group is complete
 #pragma unroll
