@@ -41,6 +41,8 @@ WORKLOADS = {
     # name: (M, K, N, op name, description)
     "c2": (4096, 4096, 128, "bwta", "BWTA GEMM: binary W[4096,4096] x ternary X[4096,128], fp16 alpha epilogue"),
     "c1": (4096, 4096, 64, "xor", "BGEMM: W[4096,4096] x X[4096,64], both {-1,+1}"),
+    "c5n1": (28672, 8192, 1, "bwta", "LLM projection 28672x8192, ternary X, N=1 (single-token decode)"),
+    "c5n4": (28672, 8192, 4, "bwta", "LLM projection 28672x8192, ternary X, N=4"),
     "c5n16": (28672, 8192, 16, "bwta", "LLM projection 28672x8192, ternary X, N=16"),
     "c5n128": (28672, 8192, 128, "bwta", "LLM projection 28672x8192, ternary X, N=128"),
     "c5n1024": (28672, 8192, 1024, "bwta", "LLM projection 28672x8192, ternary X, N=1024"),
@@ -50,7 +52,8 @@ L2_BYTES = 126 * 1024 * 1024
 # dram__bytes_read.sum + dram__bytes_write.sum per layer of the batched GEMM launch (gemm_persist_kernel), from the ncu
 # capture summarised under profiles/ (80 layers captured; traffic grows in proportion to the layer count). Workloads
 # without a capture: null.
-NCU_DRAM_BYTES_PER_LAYER = {"c2": 270.15e6 / 80}     # profiles/gemm_persist_kernel_bwta_4096x4096x128_batched80.md
+NCU_DRAM_BYTES_PER_LAYER = {"c2": 270.15e6 / 80,     # profiles/gemm_persist_kernel_bwta_4096x4096x128_batched80.md
+                            "c5n1": 29.39e6}          # profiles/gemm_skinny_kernel_bwta_28672x8192x1.md
 METRIC = "bwta_effective_tops"
 UNIT = "TOPS (2*M*N*K/s)"
 
@@ -368,7 +371,7 @@ def main():
     else:
         roofline = {"bound": "hbm", "achieved": gemm_gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": gemm_gbs / peaks["hbm_gbs"],
                     "traffic": (NCU_DRAM_BYTES_PER_LAYER[args.workload] * layers if args.workload in NCU_DRAM_BYTES_PER_LAYER else None), "peak_source": peaks["source"]}
-    roofline.update({"kernel": "gemm_persist_kernel for pools with one tile across N, else gemm_kernel (tcgen05 kind::i8, A operand unpacked into tensor memory)", "launch_us": launch_us,
+    roofline.update({"kernel": "gemm_skinny_kernel (CUDA cores, weight streaming) for N <= 4; gemm_persist_kernel for pools with one tile across N, else gemm_kernel (tcgen05 kind::i8, A operand unpacked into tensor memory)", "launch_us": launch_us,
                      "layers_per_launch": layers, "bytes_alg_per_launch": bytes_layer * layers, "ops_per_launch": ops_layer * layers,
                      "kernel_gbs": gemm_gbs, "kernel_tops": gemm_tops})
     lsteps = max(3, args.steps // 5)

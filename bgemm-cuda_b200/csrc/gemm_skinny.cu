@@ -5,8 +5,9 @@
 // times the streaming time (28672 x 8192: 24 us against 4.5 us of HBM time). This kernel keeps the work on the
 // CUDA cores, where it is cheap enough to hide behind the loads. A lane owns one weight row and fetches its 32 packed
 // bytes of a 256-column K block with two coalesced 16-byte asynchronous copies (the tiled plane keeps 128 rows x 16 B
-// contiguous) into a ring in shared memory that only this lane reads back: up to 12 K blocks per lane, 192 KB per
-// SM, are in flight from the first instruction on, and cp.async group counting is all the synchronisation it needs.
+// contiguous) into a ring in shared memory that only this lane reads back: up to 192 KB per SM (12 K blocks per lane
+// with 16 warps, 6 with 32) are in flight from the first instruction on, and cp.async group counting is all the
+// synchronisation it needs.
 //
 //   popc path   activations in {-1, 0, +1} and a result of the form colsum - 2 D (ops XOR and BWTA): the CTA first
 //               turns the int8 activations into two bit planes in the weight plane's own bit order (non-zero, negative);
@@ -22,7 +23,7 @@
 // Replaces the same reference functions as gemm_umma.cu (PACK_BGEMM_Kernel, kernel_matmul.cuh:370-547, which does
 // not accept N < 32 at all) for the shapes named above.
 //
-// One CTA of 16 warps per SM walks over a contiguous range of 32-row groups, so the activations are turned into
+// One CTA of 16 or 32 warps per SM walks over a contiguous range of 32-row groups, so the activations are turned into
 // planes once per CTA; `ks` warps share the K blocks of a group and meet in shared memory.
 #include <cuda_fp16.h>
 
@@ -126,21 +127,22 @@ __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commi
 template <int N>
 __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
-constexpr int kSkinnyThreads = 512;                // 16 warps = (groups in flight) x (K shares)
+constexpr int kSkinnyMaxWarps = 32;            // CTAs have 16 or 32 warps = (groups in flight) x (K shares)                // 16 warps = (groups in flight) x (K shares)
 constexpr int kSkinnyPiece = 8 * 1024;             // columns staged per pass and row by the N > 2 variants
 
-// `ks` warps share the K blocks of one 32-row group (ks in {1, 2, 4, 8, 16}); the CTA works on 16 / ks groups at a
+// `ks` warps share the K blocks of one 32-row group (ks a power of two up to W); the CTA works on W / ks groups at a
 // time and owns the contiguous range of groups [groups * b / gridDim.x, groups * (b + 1) / gridDim.x).
-template <int NN, int D>
-__global__ void __launch_bounds__(kSkinnyThreads) gemm_skinny_kernel(const GemmParams p, const int8_t* __restrict__ acts, long long act_ld,
+template <int NN, int D, int W>
+__global__ void __launch_bounds__(32 * W) gemm_skinny_kernel(const GemmParams p, const int8_t* __restrict__ acts, long long act_ld,
                                                                      int groups, int ks) {
+    constexpr int T = 32 * W;                    // threads of the CTA
     constexpr bool STAGE = NN <= 2;              // whole int8 activations stay in shared memory (they feed the dp4a path)
     grid_launch_dependents();
     extern __shared__ __align__(16) uint8_t skinny_smem[];
     const int x_pitch = p.kblocks * 256;                                    // == act_ld
     uint32_t* planes = reinterpret_cast<uint32_t*>(skinny_smem);            // [kblocks][NN][8 nz + 8 neg]
-    int* red = reinterpret_cast<int*>(planes + (size_t)p.kblocks * NN * 16); // [16 warps][NN][32]
-    int* s_pn = red + 16 * NN * 32;                                         // [8] non-zero activations per row
+    int* red = reinterpret_cast<int*>(planes + (size_t)p.kblocks * NN * 16); // [warps][NN][32]
+    int* s_pn = red + W * NN * 32;                                         // [8] non-zero activations per row
     int8_t* sx = reinterpret_cast<int8_t*>(s_pn + 8);                       // [NN][x_pitch] (STAGE) or [NN][piece]
     const int piece = STAGE ? x_pitch : (x_pitch < kSkinnyPiece ? x_pitch : kSkinnyPiece);   // columns staged per pass, all rows at once
     // Weight ring: D slots of 32 bytes per lane, [slot][lo | hi][thread]. A lane only ever reads what it copied itself,
@@ -148,7 +150,7 @@ __global__ void __launch_bounds__(kSkinnyThreads) gemm_skinny_kernel(const GemmP
     uint4* ring = reinterpret_cast<uint4*>(sx + (size_t)NN * piece);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int batch = blockIdx.y;
-    const int gs = 16 / ks;                      // groups in flight
+    const int gs = W / ks;            // groups in flight
     const int team = warp / ks, share = warp - team * ks;
     const int kb0 = (int)(((long long)p.kblocks * share) / ks);
     const int kb1 = (int)(((long long)p.kblocks * (share + 1)) / ks);
@@ -170,7 +172,7 @@ __global__ void __launch_bounds__(kSkinnyThreads) gemm_skinny_kernel(const GemmP
     auto unit_ptr = [&](int g, int kb) {
         return plane + ((size_t)(g >> 2) * p.kblocks + kb) * 4096 + (size_t)((g & 3) * 32 + lane) * 16;
     };
-    constexpr uint32_t kSlotBytes = 2u * kSkinnyThreads * 16u;
+    constexpr uint32_t kSlotBytes = 2u * T * 16u;
     const uint32_t ring_addr = smem_u32(ring + tid);
     auto issue = [&](int slot, bool live, const uint8_t* w) {   // always closes a group: one group per unit
         if (live) {
@@ -189,7 +191,7 @@ __global__ void __launch_bounds__(kSkinnyThreads) gemm_skinny_kernel(const GemmP
     uint4 xv[XR];
 #pragma unroll
     for (int r = 0; r < XR; r++) {
-        const int i = tid + r * kSkinnyThreads;
+        const int i = tid + r * T;
         xv[r] = i < NN * (piece / 16) ? load_x(i, 0, piece / 16) : make_uint4(0u, 0u, 0u, 0u);
     }
     int gc = g_begin + team, kc = kb0;           // unit being computed
@@ -226,15 +228,15 @@ __global__ void __launch_bounds__(kSkinnyThreads) gemm_skinny_kernel(const GemmP
             int i = tid;
             if (base == 0) {                                                    // fetched ahead
 #pragma unroll
-                for (int r = 0; r < XR; r++, i += kSkinnyThreads)
+                for (int r = 0; r < XR; r++, i += T)
                     if (i < NN * chunks) put_x(i, xv[r]);
             }
-            for (; i < NN * chunks; i += kSkinnyThreads) put_x(i, load_x(i, base, chunks));
+            for (; i < NN * chunks; i += T) put_x(i, load_x(i, base, chunks));
             __syncthreads();
             const int words = len / 32;                                         // items per row: word c of K block kb, both planes
 #pragma unroll
             for (int n = 0; n < NN; n++) {
-                for (int i = tid; i < words; i += kSkinnyThreads) {
+                for (int i = tid; i < words; i += T) {
                     const int c = i & 7, kbl = i >> 3, kb = base / 256 + kbl;
                     uint32_t nzw = 0u, ngw = 0u;
 #pragma unroll
@@ -294,8 +296,8 @@ __global__ void __launch_bounds__(kSkinnyThreads) gemm_skinny_kernel(const GemmP
         int slot = 0;
         while (gc < g_end) {
             cp_async_wait<D - 1>();                                         // the oldest of the D units in flight has landed
-            const uint4* rs = ring + tid + slot * (2 * kSkinnyThreads);
-            const uint4 lo = rs[0], hi = rs[kSkinnyThreads];
+            const uint4* rs = ring + tid + slot * (2 * T);
+            const uint4 lo = rs[0], hi = rs[T];
             if (popc_path) {
                 skinny_block_popc<NN>(lo, hi, planes + (size_t)kc * NN * 16, 16, cnt);
             } else if (STAGE) {
@@ -353,46 +355,34 @@ __global__ void __launch_bounds__(kSkinnyThreads) gemm_skinny_kernel(const GemmP
     cp_async_wait<0>();                          // nothing of this thread's is in flight when it leaves
 }
 
-static size_t skinny_smem_bytes(int NN, int kblocks) {
+static size_t skinny_smem_bytes(int NN, int kblocks) {      // everything but the weight ring
     const size_t stage = (size_t)NN * (NN <= 2 ? (size_t)kblocks * 256 : ((size_t)kblocks * 256 < (size_t)kSkinnyPiece ? (size_t)kblocks * 256 : (size_t)kSkinnyPiece));
-    return (size_t)kblocks * NN * 64 + (size_t)16 * NN * 32 * sizeof(int) + 32 + stage;
+    return (size_t)kblocks * NN * 64 + (size_t)kSkinnyMaxWarps * NN * 32 * sizeof(int) + 32 + stage;
 }
+constexpr size_t kSkinnyRingBytes = 192 * 1024;        // ring of the deepest variants: 12 K blocks x 16 warps or 6 x 32 warps
 
-constexpr size_t kSkinnyRingSlot = (size_t)kSkinnyThreads * 32;   // bytes of one ring slot over the CTA
-
-template <int NN, int D>
-static int launch_skinny_variant(cudaStream_t stream, const GemmParams& p, const int8_t* acts, long long act_ld, long long batch) {
-    const size_t smem = skinny_smem_bytes(NN, p.kblocks) + D * kSkinnyRingSlot;
+template <int NN, int D, int W>
+static int launch_skinny_variant(cudaStream_t stream, const GemmParams& p, const int8_t* acts, long long act_ld, long long batch, long long ctas) {
+    const size_t smem = skinny_smem_bytes(NN, p.kblocks) + (size_t)D * W * 32 * 32;
     const long long groups = (long long)p.mtiles * 4;
-    const int threads = kSkinnyThreads;
     static bool configured[64] = {};
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev < 0 || dev >= 64) return BGEMM_ERR_DRIVER;
     if (!configured[dev]) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_skinny_kernel<NN, D>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSkinnyMaxSmem);
+        cudaError_t e = cudaFuncSetAttribute(gemm_skinny_kernel<NN, D, W>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSkinnyMaxSmem);
         if (e != cudaSuccess) return (int)e;
         configured[dev] = true;
     }
-    // Resident CTAs per SM at this shared-memory size: the grid is one wave, every CTA walks over row groups.
-    static thread_local size_t cached_smem = 0;
-    static thread_local int cached_threads = 0, cached_dev = -1, cached_per_sm = 0;
-    if (cached_smem != smem || cached_threads != threads || cached_dev != dev) {
-        int n = 0;
-        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, gemm_skinny_kernel<NN, D>, threads, smem) != cudaSuccess || n < 1) n = 1;
-        cached_smem = smem; cached_threads = threads; cached_dev = dev; cached_per_sm = n;
-    }
-    const int per_sm = cached_per_sm;
-    // One wave: at most two CTAs per SM (every CTA converts the activations for itself), fewer with a batch in grid.y.
-    long long ctas = ((long long)sm_count() * (per_sm < 2 ? per_sm : 2) + batch - 1) / batch;
-    if (ctas > groups) ctas = groups;
     // K shares per group: at least four K blocks per warp while that leaves every team of the launch a group to work on
     int ks = 1;
-    while (ks < 16 && p.kblocks / (ks * 2) >= 4) ks *= 2;
-    while (ks < 16 && ks * 2 <= p.kblocks && groups < ctas * (16 / ks)) ks *= 2;
+    while (ks < W && p.kblocks / (ks * 2) >= 4) ks *= 2;
+    while (ks < W && ks * 2 <= p.kblocks && groups < ctas * (W / ks)) ks *= 2;
+    // teams of two or more warps meet at named barriers 1..15: at most 8 teams then (a team of one warp needs none)
+    if (ks > 1 && W / ks > 8) ks = W / 8 <= p.kblocks ? W / 8 : 1;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)ctas, (unsigned)batch, 1);
-    cfg.blockDim = dim3((unsigned)threads, 1, 1);
+    cfg.blockDim = dim3(32u * W, 1, 1);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = stream;
     cudaLaunchAttribute attr[1];
@@ -402,13 +392,13 @@ static int launch_skinny_variant(cudaStream_t stream, const GemmParams& p, const
         cfg.attrs = attr;
         cfg.numAttrs = 1;
     }
-    const cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_skinny_kernel<NN, D>, p, acts, act_ld, (int)groups, ks);
+    const cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_skinny_kernel<NN, D, W>, p, acts, act_ld, (int)groups, ks);
     count_launch();
     return (int)(e != cudaSuccess ? e : cudaGetLastError());
 }
 
 // Largest N served here (tuning override: BGEMM_SKINNY_MAX_N, 0 switches the kernel off). Measured against the
-// tensor-core path (24 us at any N <= 16 for 28672 x 8192): N = 1 / 2 / 4 take 11 / 13.5 / 17 us here, N = 8 takes 26 us.
+// tensor-core path (24 us at any N <= 16 for 28672 x 8192): N = 1 / 2 / 4 take 9.5 / 13.5 / 15.4 us here, N = 8 takes 26 us.
 static int skinny_max_n() {
     static const int v = [] {
         const char* e = std::getenv("BGEMM_SKINNY_MAX_N");
@@ -424,16 +414,29 @@ bool skinny_supported(const GemmParams& p, long long batch, bool ternary_acts_ex
     if (p.N > 2 && !(p.epi && ternary_acts_expected)) return false;
     const int NN = p.N <= 1 ? 1 : (p.N <= 2 ? 2 : (p.N <= 4 ? 4 : 8));
     // the activation planes must fit in shared memory, and accumulator 7 (weights of 128) must stay inside int32
-    return skinny_smem_bytes(NN, p.kblocks) + 4 * kSkinnyRingSlot <= (size_t)kSkinnyMaxSmem && p.K <= 65536;
+    return skinny_smem_bytes(NN, p.kblocks) + kSkinnyRingBytes / 3 <= (size_t)kSkinnyMaxSmem && p.K <= 65536;
 }
 
-// Deepest weight ring (12, 8 or 4 K blocks per lane) that fits beside the activation planes.
+// One CTA per SM (the ring takes most of its shared memory), fewer per problem with a batch in grid.y. CTAs with
+// plenty to stream (128 KB of plane or more each) get 32 warps, which hide the arithmetic's dependent chains better
+// (28672 x 8192 x 1: 9.5 against 11.1 us); smaller problems get 16, whose fixed costs are lower (4096 x 4096 x 1: 3.1
+// against 4.1 us). The ring is as deep as fits beside the activation planes: 192, 128 or 64 KB.
 template <int NN>
 static int launch_skinny_depth(cudaStream_t stream, const GemmParams& p, const int8_t* acts, long long act_ld, long long batch) {
+    const long long groups = (long long)p.mtiles * 4;
+    long long ctas = (sm_count() + batch - 1) / batch;
+    if (ctas > groups) ctas = groups;
     const size_t base = skinny_smem_bytes(NN, p.kblocks);
-    if (base + 12 * kSkinnyRingSlot <= (size_t)kSkinnyMaxSmem) return launch_skinny_variant<NN, 12>(stream, p, acts, act_ld, batch);
-    if (base + 8 * kSkinnyRingSlot <= (size_t)kSkinnyMaxSmem) return launch_skinny_variant<NN, 8>(stream, p, acts, act_ld, batch);
-    return launch_skinny_variant<NN, 4>(stream, p, acts, act_ld, batch);
+    const int depth = base + kSkinnyRingBytes <= (size_t)kSkinnyMaxSmem ? 3 : (base + kSkinnyRingBytes * 2 / 3 <= (size_t)kSkinnyMaxSmem ? 2 : 1);
+    const bool wide = (double)p.plane_batch_bytes / (double)ctas >= 128.0 * 1024.0;
+    if (wide) {
+        if (depth == 3) return launch_skinny_variant<NN, 6, 32>(stream, p, acts, act_ld, batch, ctas);
+        if (depth == 2) return launch_skinny_variant<NN, 4, 32>(stream, p, acts, act_ld, batch, ctas);
+        return launch_skinny_variant<NN, 2, 32>(stream, p, acts, act_ld, batch, ctas);
+    }
+    if (depth == 3) return launch_skinny_variant<NN, 12, 16>(stream, p, acts, act_ld, batch, ctas);
+    if (depth == 2) return launch_skinny_variant<NN, 8, 16>(stream, p, acts, act_ld, batch, ctas);
+    return launch_skinny_variant<NN, 4, 16>(stream, p, acts, act_ld, batch, ctas);
 }
 
 int launch_gemm_skinny(cudaStream_t stream, const GemmParams& p, const int8_t* acts, long long act_ld, long long batch) {
