@@ -56,6 +56,8 @@ lib.bgemm_linear_workspace_bytes.restype = _sz
 lib.bgemm_linear_workspace_bytes.argtypes = [_i64, _i64, _i64, _int]
 lib.bgemm_device_status.restype = _int
 lib.bgemm_device_status.argtypes = [_int]
+lib.bgemm_debug_set_wait_test.restype = None
+lib.bgemm_debug_set_wait_test.argtypes = [_i64, _int]
 
 
 class BgemmError(RuntimeError):
@@ -147,11 +149,16 @@ _workspaces: dict = {}
 
 
 def workspace(device: torch.device, nbytes: int) -> torch.Tensor:
-    """Zero-initialised per-device scratch, grown on demand (the library keeps its counter prefix zero)."""
-    key = (device.type, device.index if device.index is not None else torch.cuda.current_device())
+    """Zero-initialised scratch per (device, current stream), grown on demand (the library keeps its counter prefix
+    zero). One buffer per stream: calls on one stream run in order and may share it, calls on different streams may
+    overlap on the GPU and must not (bgemm_linear_forward parks its packed operands there)."""
+    index = device.index if device.index is not None else torch.cuda.current_device()
+    key = (device.type, index, torch.cuda.current_stream(index).cuda_stream)
     ws = _workspaces.get(key)
     if ws is None or ws.numel() < nbytes:
         ws = torch.zeros(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
+        if key in _workspaces:
+            _workspaces[key].record_stream(torch.cuda.current_stream(index))   # the smaller buffer may still be in use
         _workspaces[key] = ws
     return ws
 

@@ -348,16 +348,44 @@ class BinaryLinear(nn.Module):
 
     alpha[m] = mean |w[m, :]| (per output channel). Activations are binarised by sign (+0 -> +1) or, with
     ternary=True, by torch.sign. The scale is applied inside the GEMM epilogue.
+
+    The layer's only buffer is `packed`: the packed-weight bundle (header with magic and layout version, tiled
+    bit plane, row bit counts, scales), so `state_dict()` round trips carry their own layout description and a
+    bundle written by another layout version is refused when it is loaded. `plane` and `alpha` are views into it.
     """
 
     def __init__(self, weight: torch.Tensor, ternary: bool = False, alpha: torch.Tensor | None = None):
         super().__init__()
         assert weight.is_cuda and weight.dim() == 2
         self.out_features, self.in_features = weight.shape
-        plane, a, _ = lowbit_kernel.binary_weight_prepacking_scaled_cuda(weight)
-        self.register_buffer("plane", plane)
-        self.register_buffer("alpha", a if alpha is None else alpha.to(torch.half).to(weight.device))
+        self.register_buffer("packed", lowbit_kernel.binary_weight_prepacking_bundle_cuda(weight, 0))
         self.ternary = ternary
+        self._views = None
+        if alpha is not None:
+            self.alpha.copy_(alpha.to(torch.half).to(weight.device))
+
+    def _open(self):
+        key = (self.packed.data_ptr(), self.packed.numel())
+        if self._views is None or self._views[0] != key:
+            plane, alpha, rowpop, M, K, wbit = lowbit_kernel.unpack_bundle(self.packed)       # validates magic / version / sizes
+            if (M, K) != (self.out_features, self.in_features) or wbit != 0:
+                raise RuntimeError(f"packed weights describe a {M} x {K} matrix (bit mode {wbit}), the layer is "
+                                   f"{self.out_features} x {self.in_features}")
+            self._views = (key, plane, alpha, rowpop)
+        return self._views
+
+    @property
+    def plane(self) -> torch.Tensor:
+        return self._open()[1]
+
+    @property
+    def alpha(self) -> torch.Tensor:
+        return self._open()[2]
+
+    def _load_from_state_dict(self, state_dict, prefix, *args, **kwargs):
+        super()._load_from_state_dict(state_dict, prefix, *args, **kwargs)
+        self._views = None
+        self._open()                      # a bundle of another layout version or shape fails here, not in a kernel
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         lead = x.shape[:-1]

@@ -2,6 +2,7 @@
 // Declared and documented in include/bgemm_b200.h.
 #include <atomic>
 #include <cstdlib>
+#include <cstring>
 
 #include "internal.h"
 
@@ -18,8 +19,10 @@ bool programmatic_launch_enabled() {
     return on;
 }
 
+#ifdef BGEMM_TUNING
 static long long* g_prof = nullptr;
 long long* debug_profile_buffer() { return g_prof; }
+#endif
 
 // Device status word: kernels record here which bounded wait ran out (0 = never). One word per device,
 // addressed through cudaGetSymbolAddress with that device current.
@@ -36,11 +39,23 @@ int* device_status_word() {
     return cache[dev];
 }
 
+// Test settings of bgemm_debug_set_wait_test (process-wide; 0 / -1 = none).
+static std::atomic<long long> g_test_wait_budget{0};
+static std::atomic<int> g_test_skip_kblock{-1};
+void apply_test_hooks(GemmParams& p) {
+    p.wait_budget = g_test_wait_budget.load(std::memory_order_relaxed);
+    p.test_skip_kblock = g_test_skip_kblock.load(std::memory_order_relaxed);
+}
+
 static bool aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) % a) == 0; }
 static bool valid_dtype(int d) { return d >= BGEMM_DT_F16 && d <= BGEMM_DT_I8; }
 static size_t dt_size(int d) { return d == BGEMM_DT_F32 ? 4 : (d == BGEMM_DT_I8 ? 1 : 2); }
 
-constexpr long long kMaxDim = 1LL << 24;      // keeps every int32 accumulator and index computation exact
+// Largest M, N, K: keeps index computations and the int32 accumulators of binary / ternary activations exact
+// (|acc| <= K). General int8 activations (|acc| <= 128 K) are exact up to K = 2^24 as well on tiles of 64 columns or
+// more; narrower tiles are limited to kMaxKGeneralNarrow (see bgemm_gemm).
+constexpr long long kMaxDim = 1LL << 24;
+constexpr long long kMaxKGeneralNarrow = 65536;
 constexpr int kMaxSplitK = 64;
 constexpr int kMaxClusterSplit = 8;           // portable thread-block cluster size
 // Split-K beyond the cluster limit keeps one arrival counter per output tile in a FIXED-size prefix of the
@@ -60,7 +75,7 @@ static int resolve_split_k(long long M, long long N, long long K, long long batc
         return (int)(split_k > kblocks ? kblocks : split_k);
     }
     // auto: fill the SMs once (one deep-pipeline CTA per SM measured best), keep at least 2 K blocks per partition
-    const long long target = 148LL;
+    const long long target = sm_count();
     long long s = target / (tiles > 0 ? tiles : 1);
     if (s < 1) s = 1;
     if (s > kblocks / 2) s = kblocks / 2;
@@ -81,12 +96,74 @@ size_t bgemm_plane_bytes(int64_t M, int64_t K) {
 }
 int64_t bgemm_act_ld(int64_t K) { return K < 1 ? 0 : (K + 255) / 256 * 256; }
 
-int bgemm_version(void) { return 100; }
-// Tuning aid (not declared in the public header): device buffer that the GEMM kernels fill with phase stamps and
-// wait-time counters, 32 int64 per CTA; the persistent kernel appends an event trace of its CTA 0 (8 x 1024 int64
-// behind the per-CTA slots), so size it for (CTAs of the launch) * 32 + 8192 entries. Pass NULL to switch it off.
+int bgemm_version(void) { return 200; }
+
+// ---- packed-weight bundle (host-side bookkeeping only) ---------------------------------------------------------
+namespace {
+struct BundleHeader {
+    uint32_t magic, version;
+    int64_t M, K;
+    int32_t wbit_mode, reserved;
+    int64_t plane_off, rowpop_off, alpha_off, total;
+};
+static_assert(sizeof(BundleHeader) == BGEMM_BUNDLE_HEADER_BYTES, "bundle header is 64 bytes");
+constexpr uint32_t kBundleMagic = 0x4B504742u;     // "BGPK"
+bool bundle_layout(int64_t M, int64_t K, BundleHeader* h) {
+    if (M < 1 || K < 1 || M > kMaxDim || K > kMaxDim) return false;
+    size_t o = 256;
+    h->plane_off = (int64_t)o; o += align_up(bgemm_plane_bytes(M, K), 256);
+    h->rowpop_off = (int64_t)o; o += align_up((size_t)M * 4, 256);
+    h->alpha_off = (int64_t)o; o += align_up((size_t)M * 2, 256);
+    h->total = (int64_t)o;
+    return true;
+}
+}  // namespace
+
+size_t bgemm_bundle_bytes(int64_t M, int64_t K) {
+    BundleHeader h{};
+    return bundle_layout(M, K, &h) ? (size_t)h.total : 0;
+}
+int bgemm_bundle_header_host(void* header_host, int64_t M, int64_t K, int wbit_mode) {
+    if (!header_host) return BGEMM_ERR_NULL;
+    if (wbit_mode < BGEMM_WBIT_NEGATIVE || wbit_mode > BGEMM_WBIT_NEGATIVE_NZ) return BGEMM_ERR_ENUM;
+    BundleHeader h{};
+    if (!bundle_layout(M, K, &h)) return BGEMM_ERR_SHAPE;
+    h.magic = kBundleMagic; h.version = BGEMM_LAYOUT_VERSION; h.M = M; h.K = K; h.wbit_mode = wbit_mode;
+    std::memcpy(header_host, &h, sizeof(h));
+    return BGEMM_OK;
+}
+int bgemm_bundle_parse_host(const void* header_host, size_t bundle_bytes, int64_t* M, int64_t* K, int* wbit_mode, size_t* plane_offset,
+                            size_t* rowpop_offset, size_t* alpha_offset) {
+    if (!header_host) return BGEMM_ERR_NULL;
+    BundleHeader h;
+    std::memcpy(&h, header_host, sizeof(h));
+    if (h.magic != kBundleMagic || h.version != BGEMM_LAYOUT_VERSION) return BGEMM_ERR_UNSUPPORTED;
+    BundleHeader want{};
+    if (!bundle_layout(h.M, h.K, &want) || h.wbit_mode < BGEMM_WBIT_NEGATIVE || h.wbit_mode > BGEMM_WBIT_NEGATIVE_NZ) return BGEMM_ERR_SHAPE;
+    if (h.plane_off != want.plane_off || h.rowpop_off != want.rowpop_off || h.alpha_off != want.alpha_off || h.total != want.total ||
+        (size_t)h.total > bundle_bytes)
+        return BGEMM_ERR_SHAPE;
+    if (M) *M = h.M;
+    if (K) *K = h.K;
+    if (wbit_mode) *wbit_mode = h.wbit_mode;
+    if (plane_offset) *plane_offset = (size_t)h.plane_off;
+    if (rowpop_offset) *rowpop_offset = (size_t)h.rowpop_off;
+    if (alpha_offset) *alpha_offset = (size_t)h.alpha_off;
+    return BGEMM_OK;
+}
+#ifdef BGEMM_TUNING
+// Tuning builds only (-DBGEMM_TUNING; not declared in the public header): device buffer that the GEMM kernels fill with
+// phase stamps and wait-time counters, 32 int64 per CTA; the persistent kernel appends an event trace of its CTA 0
+// (8 x 1024 int64 behind the per-CTA slots), so size it for (CTAs of the launch) * 32 + 8192 entries. NULL = off.
+// One process-wide pointer: set it from one thread, for one device.
 void bgemm_debug_set_profile_buffer(void* dev_buffer) { g_prof = static_cast<long long*>(dev_buffer); }
+#endif
 uint64_t bgemm_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
+
+void bgemm_debug_set_wait_test(int64_t wait_budget_clocks, int skip_kblock) {
+    g_test_wait_budget.store(wait_budget_clocks > 0 ? wait_budget_clocks : 0, std::memory_order_relaxed);
+    g_test_skip_kblock.store(skip_kblock >= 0 ? skip_kblock : -1, std::memory_order_relaxed);
+}
 
 int bgemm_device_status(int reset) {
     int* w = device_status_word();
@@ -178,6 +255,9 @@ int bgemm_gemm(void* stream, const void* plane, int64_t M, int64_t K, const int8
         return BGEMM_ERR_SHAPE;
     if (!aligned(plane, 16) || !aligned(acts, 16) || !aligned(colsum, 4) || !aligned(out, out_kind == BGEMM_OUT_I32 ? 4 : 2))
         return BGEMM_ERR_ALIGN;
+    // Tiles of 16 and 32 columns keep bit j of a weight byte at value 2^j and shift the sums down afterwards: with
+    // general int8 activations accumulator 7 holds up to 128 * 128 * K, which leaves int32 beyond K = 65536.
+    if (op == BGEMM_OP_W1A8 && N <= 32 && K > kMaxKGeneralNarrow) return BGEMM_ERR_UNSUPPORTED;
     const int s = resolve_split_k(M, N, K, batch, split_k);
     const long long mtiles = (M + 127) / 128;
     if (mtiles * s > 65535) return BGEMM_ERR_SHAPE;
@@ -188,7 +268,10 @@ int bgemm_gemm(void* stream, const void* plane, int64_t M, int64_t K, const int8
     p.out = out;
     p.alpha = static_cast<const __half*>(alpha);
     p.status = device_status_word();
+    apply_test_hooks(p);
+#ifdef BGEMM_TUNING
     p.prof = debug_profile_buffer();
+#endif
     p.M = (int)M; p.N = (int)N; p.K = (int)K;
     p.kblocks = (int)((K + 255) / 256);
     p.mtiles = (int)mtiles;
@@ -226,6 +309,12 @@ int bgemm_gemm_to_acts(void* stream, const void* plane, int64_t M, int64_t K, co
     if (mtiles * s > 65535) return BGEMM_ERR_SHAPE;
     const long long ld = bgemm_act_ld(M);
     cudaStream_t st = (cudaStream_t)stream;
+    // every check comes before the first memset or launch: a negative status means nothing was enqueued
+    if (s > kMaxClusterSplit) {
+        const size_t need = bgemm_gemm_workspace_bytes(M, N, K, s, batch);
+        if (!workspace || workspace_bytes < need) return BGEMM_ERR_WORKSPACE;
+        if (!aligned(workspace, 256)) return BGEMM_ERR_ALIGN;
+    }
     // the kernel adds row sums with atomics and writes whole 8-column chunks: sums and the padding beyond them start at zero
     cudaError_t e = cudaMemsetAsync(next_colsum, 0, (size_t)N * (size_t)batch * sizeof(int32_t), st);
     const long long written = (M + 7) / 8 * 8;
@@ -239,7 +328,10 @@ int bgemm_gemm_to_acts(void* stream, const void* plane, int64_t M, int64_t K, co
     p.out = next_acts;
     p.alpha = static_cast<const __half*>(alpha);
     p.status = device_status_word();
+    apply_test_hooks(p);
+#ifdef BGEMM_TUNING
     p.prof = debug_profile_buffer();
+#endif
     p.M = (int)M; p.N = (int)N; p.K = (int)K;
     p.kblocks = (int)((K + 255) / 256);
     p.mtiles = (int)mtiles;
@@ -253,9 +345,6 @@ int bgemm_gemm_to_acts(void* stream, const void* plane, int64_t M, int64_t K, co
     p.out_ld = ld;
     p.act_mode = next_act_mode;
     if (s > kMaxClusterSplit) {
-        const size_t need = bgemm_gemm_workspace_bytes(M, N, K, s, batch);
-        if (!workspace || workspace_bytes < need) return BGEMM_ERR_WORKSPACE;
-        if (!aligned(workspace, 256)) return BGEMM_ERR_ALIGN;
         const int NT = gemm_tile_n(N);
         const long long tiles = mtiles * ((N + NT - 1) / NT) * batch;
         p.ws_counters = static_cast<unsigned int*>(workspace);
@@ -288,10 +377,16 @@ size_t bgemm_linear_workspace_bytes(int64_t M, int64_t N, int64_t K, int split_k
 int bgemm_linear_forward(void* stream, const void* weight_f16, const void* acts_f16, void* out, int64_t M, int64_t N, int64_t K, int op,
                          int out_kind, int out_layout, const void* alpha, int split_k, void* workspace, size_t workspace_bytes) {
     if (!weight_f16 || !acts_f16 || !out || !workspace) return weight_f16 && acts_f16 && out ? BGEMM_ERR_WORKSPACE : BGEMM_ERR_NULL;
-    if (op < BGEMM_OP_AND || op > BGEMM_OP_BWTA) return BGEMM_ERR_ENUM;
+    if (op < BGEMM_OP_AND || op > BGEMM_OP_BWTA || out_kind < BGEMM_OUT_I32 || out_kind > BGEMM_OUT_F16_SCALED ||
+        out_layout < BGEMM_LAYOUT_NM || out_layout > BGEMM_LAYOUT_MN)
+        return BGEMM_ERR_ENUM;
+    if (out_kind == BGEMM_OUT_F16_SCALED && !alpha) return BGEMM_ERR_NULL;
     if (M < 1 || N < 1 || K < 1 || M > kMaxDim || N > kMaxDim || K > kMaxDim || split_k < 0 || split_k > kMaxSplitK) return BGEMM_ERR_SHAPE;
-    if (!aligned(workspace, 256)) return BGEMM_ERR_ALIGN;
+    // everything the three calls below would refuse is refused here, before the first launch
+    if (!aligned(workspace, 256) || !aligned(weight_f16, 2) || !aligned(acts_f16, 2) || !aligned(out, out_kind == BGEMM_OUT_I32 ? 4 : 2))
+        return BGEMM_ERR_ALIGN;
     const int s = resolve_split_k(M, N, K, 1, split_k);
+    if (((M + 127) / 128) * s > 65535) return BGEMM_ERR_SHAPE;
     size_t off_plane, off_acts, off_colsum, total;
     linear_ws_layout(M, N, K, s, &off_plane, &off_acts, &off_colsum, &total);
     if (workspace_bytes < total) return BGEMM_ERR_WORKSPACE;

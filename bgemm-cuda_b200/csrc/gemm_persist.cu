@@ -26,12 +26,6 @@
 
 namespace bgemm {
 
-// Event trace of CTA 0 (tuning aid, behind the per-CTA slots of the profile buffer): event `ev`, occurrence `idx`.
-#define BGEMM_TRACE(ev, idx)                                                                                        \
-    do {                                                                                                            \
-        if (p.prof && blockIdx.x == 0 && (idx) < 1024) p.prof[(size_t)gridDim.x * 32 + (ev) * 1024 + (idx)] = clock64() - t_cta0; \
-    } while (0)
-
 constexpr int kPThreads = 512;
 constexpr int kPEpiThreads = 128;
 constexpr int kPWarpEpi = 8, kPWarpMma0 = 12, kPWarpW = 13, kPWarpB = 14, kPWarpMma1 = 15;
@@ -70,7 +64,7 @@ struct PCfg {
 template <int NT>
 __global__ void __launch_bounds__(kPThreads, 1) gemm_persist_kernel(const __grid_constant__ CUtensorMap tmap_acts, const GemmParams p, const long long total_tiles) {
     using C = PCfg<NT>;
-    const long long t_cta0 = clock64();
+    BGEMM_TUNING_ONLY(const long long t_cta0 = clock64();)
     grid_launch_dependents();
     if (threadIdx.x == 0) BGEMM_STAMP(10);
     extern __shared__ uint8_t smem_raw[];
@@ -110,7 +104,7 @@ __global__ void __launch_bounds__(kPThreads, 1) gemm_persist_kernel(const __grid
             else if (i == d0 + 6) count = 2;                                  // drained: both issuers
             mbar_init(w_full + 8 * i, count);
         }
-        if (lane == 0) *abort_flag = 0;
+        if (lane == 0) { *abort_flag = 0; set_wait_budget(abort_flag, p.wait_budget); }
         mbar_fence_init();
     } else if (warp == kPWarpB) {
         if (lane == 0) tma_prefetch_desc(&tmap_acts);
@@ -129,7 +123,8 @@ __global__ void __launch_bounds__(kPThreads, 1) gemm_persist_kernel(const __grid
     if (warp == kPWarpW) {
         // ---------------- weight producer ----------------
         if (lane == 0) {
-            long long g = 0, tw = 0;
+            long long g = 0;
+            BGEMM_TUNING_ONLY(long long tw = 0;)
             bool ok = true;
             for (long long t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
                 const long long bm = t / p.ntiles;                      // batch * mtiles + mt
@@ -139,6 +134,7 @@ __global__ void __launch_bounds__(kPThreads, 1) gemm_persist_kernel(const __grid
                     const int s = (int)(g % C::W_STAGES);
                     if (g >= C::W_STAGES) BGEMM_TIMED(tw, ok = mbar_wait_relaxed(w_empty + 8 * s, (uint32_t)((g / C::W_STAGES) - 1) & 1, abort_flag, p.status, 21));
                     if (!ok) break;
+                    if (g == p.test_skip_kblock) continue;          // test hook: this K block never arrives, its consumers' waits run out
                     mbar_arrive_expect_tx(w_full + 8 * s, 4096);
                     bulk_g2s(smem_u32(sW + s * 4096), src + (size_t)i * 4096, 4096, w_full + 8 * s);
                 }
@@ -147,14 +143,15 @@ __global__ void __launch_bounds__(kPThreads, 1) gemm_persist_kernel(const __grid
             if (*abort_flag) {  // drain own copies before the CTA may exit
                 for (long long i = g - 1; i >= 0 && i >= g - C::W_STAGES; i--) {
                     const long long t0 = clock64();
-                    while (!mbar_test(w_full + 8 * (int)(i % C::W_STAGES), (uint32_t)(i / C::W_STAGES) & 1) && clock64() - t0 < kWaitBudgetClocks) {}
+                    while (!mbar_test(w_full + 8 * (int)(i % C::W_STAGES), (uint32_t)(i / C::W_STAGES) & 1) && clock64() - t0 < wait_budget_of(abort_flag)) {}
                 }
             }
         }
     } else if (warp == kPWarpB) {
         // ---------------- activation producer ----------------
         if (lane == 0) {
-            long long g = 0, tw = 0;
+            long long g = 0;
+            BGEMM_TUNING_ONLY(long long tw = 0;)
             bool ok = true;
             for (long long t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
                 const int nt = (int)(t % p.ntiles);
@@ -184,8 +181,9 @@ __global__ void __launch_bounds__(kPThreads, 1) gemm_persist_kernel(const __grid
         if (lane == 0) {
             constexpr uint32_t idesc = umma_idesc_u8s8(NT);
             bool ok = true;
-            long long twf = 0, twd = 0, g = 0;
-            const long long tloop0 = clock64();
+            long long g = 0;
+            BGEMM_TUNING_ONLY(long long twf = 0, twd = 0;)
+            BGEMM_TUNING_ONLY(const long long tloop0 = clock64();)
             for (long long lt = 0; lt < my_tiles && ok; lt++) {
                 const int buf = (int)(lt & 1);
                 const uint32_t k = (uint32_t)(lt >> 1);             // use number of this accumulator buffer
@@ -239,8 +237,8 @@ __global__ void __launch_bounds__(kPThreads, 1) gemm_persist_kernel(const __grid
         const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
         const long long total_kb = my_tiles * nkb;
         bool ok = true;
-        long long tww = 0, twe = 0;
-        const long long tloop0 = clock64();
+        BGEMM_TUNING_ONLY(long long tww = 0, twe = 0;)
+        BGEMM_TUNING_ONLY(const long long tloop0 = clock64();)
         for (long long g = set; g < total_kb && ok; g += 2) {
             const int ws = (int)(g % C::W_STAGES);
             BGEMM_TIMED(tww, ok = mbar_wait(w_full + 8 * ws, (uint32_t)(g / C::W_STAGES) & 1, abort_flag, p.status, 27));
@@ -280,7 +278,7 @@ __global__ void __launch_bounds__(kPThreads, 1) gemm_persist_kernel(const __grid
         const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
         TileOut tout;
         tout.p = &p; tout.s_alpha = s_alpha; tout.s_colsum = s_colsum;
-        long long twd = 0, tbusy = 0;
+        BGEMM_TUNING_ONLY(long long twd = 0, tbusy = 0;)
         long long lt = 0;
         for (long long t = blockIdx.x; t < total_tiles; t += gridDim.x, lt++) {
             const int nt = (int)(t % p.ntiles);
@@ -299,7 +297,9 @@ __global__ void __launch_bounds__(kPThreads, 1) gemm_persist_kernel(const __grid
             bool ok;
             BGEMM_TIMED(twd, ok = mbar_wait_relaxed(d_full + 8 * buf, (uint32_t)(lt >> 1) & 1, abort_flag, p.status, 29));
             ok = __all_sync(0xffffffffu, ok);
+#ifdef BGEMM_TUNING
             const long long tb0 = p.prof ? clock64() : 0;
+#endif
             if (ok) {
                 tc_fence_after();
 #pragma unroll 1
@@ -321,7 +321,9 @@ __global__ void __launch_bounds__(kPThreads, 1) gemm_persist_kernel(const __grid
             if (named_bar_or(2, kPEpiThreads, !ok)) break;
             write_tile<false>(tout, sP, 1, 0, 0, NT, et, kPEpiThreads);
             named_bar_sync(3, kPEpiThreads);                      // staging tile and scales are free for the next tile
+#ifdef BGEMM_TUNING
             if (p.prof) tbusy += clock64() - tb0;
+#endif
         }
         if (et == 0) { BGEMM_PUT(28, twd); BGEMM_PUT(29, tbusy); }
     }
@@ -331,7 +333,7 @@ __global__ void __launch_bounds__(kPThreads, 1) gemm_persist_kernel(const __grid
     if (warp == kPWarpMma0) {
         if (lane == 0) {   // every UMMA has been executed before the columns are freed (immediate unless a wait ran out)
             const long long t0 = clock64();
-            while (!mbar_test(drained, 0) && clock64() - t0 < kWaitBudgetClocks) {}
+            while (!mbar_test(drained, 0) && clock64() - t0 < wait_budget_of(abort_flag)) {}
         }
         __syncwarp();
         tc_fence_after();

@@ -94,7 +94,7 @@ struct Cfg {
 template <int NT, bool POW2, bool DEEP>
 __global__ void __launch_bounds__(kGemmThreads, Cfg<NT, POW2, DEEP>::MIN_CTAS) gemm_kernel(const __grid_constant__ CUtensorMap tmap_acts, const GemmParams p) {
     using C = Cfg<NT, POW2, DEEP>;
-    const long long t_cta0 = clock64();
+    BGEMM_TUNING_ONLY(const long long t_cta0 = clock64();)
     grid_launch_dependents();
     if (threadIdx.x == 0) BGEMM_STAMP(10);
     extern __shared__ uint8_t smem_raw[];
@@ -136,7 +136,7 @@ __global__ void __launch_bounds__(kGemmThreads, Cfg<NT, POW2, DEEP>::MIN_CTAS) g
                                     (i >= 2 * C::W_STAGES + C::B_STAGES && i < 2 * C::W_STAGES + 2 * C::B_STAGES);   // b_empty
             mbar_init(w_full + 8 * i, four ? 4 : (per_issuer ? C::NMMA : 1));
         }
-        if (lane == 0) { *abort_flag = 0; *last_flag = 0; }
+        if (lane == 0) { *abort_flag = 0; *last_flag = 0; set_wait_budget(abort_flag, p.wait_budget); }
         mbar_fence_init();
     } else if (warp == kWarpB) {
         if (lane == 0) tma_prefetch_desc(&tmap_acts);
@@ -159,12 +159,13 @@ __global__ void __launch_bounds__(kGemmThreads, Cfg<NT, POW2, DEEP>::MIN_CTAS) g
         if (lane == 0) {
             const uint8_t* src = p.plane + (size_t)batch * p.plane_batch_bytes + ((size_t)mt * p.kblocks + kb0) * 4096;
             int issued = 0;
-            long long tw = 0;
+            BGEMM_TUNING_ONLY(long long tw = 0;)
             for (int i = 0; i < nkb; i++) {
                 const int s = i % C::W_STAGES;
                 bool okw = true;
                 if (i >= C::W_STAGES) BGEMM_TIMED(tw, okw = mbar_wait(w_empty + 8 * s, ((i / C::W_STAGES) - 1) & 1, abort_flag, p.status, 11));
                 if (!okw) break;
+                if (kb0 + i == p.test_skip_kblock) continue;      // test hook: this K block never arrives, its consumers' waits run out
                 mbar_arrive_expect_tx(w_full + 8 * s, 4096);
                 bulk_g2s(smem_u32(sW + s * 4096), src + (size_t)i * 4096, 4096, w_full + 8 * s);
                 if (i == 0) BGEMM_STAMP(2);
@@ -174,7 +175,7 @@ __global__ void __launch_bounds__(kGemmThreads, Cfg<NT, POW2, DEEP>::MIN_CTAS) g
             if (*abort_flag) {  // drain own copies before the CTA may exit
                 for (int i = issued - 1; i >= 0 && i >= issued - C::W_STAGES; i--) {
                     const long long t0 = clock64();
-                    while (!mbar_test(w_full + 8 * (i % C::W_STAGES), (i / C::W_STAGES) & 1) && clock64() - t0 < kWaitBudgetClocks) {}
+                    while (!mbar_test(w_full + 8 * (i % C::W_STAGES), (i / C::W_STAGES) & 1) && clock64() - t0 < wait_budget_of(abort_flag)) {}
                 }
             }
         }
@@ -182,7 +183,7 @@ __global__ void __launch_bounds__(kGemmThreads, Cfg<NT, POW2, DEEP>::MIN_CTAS) g
         // ---------------- activation producer ----------------
         if (lane == 0) {
             int issued = 0;
-            long long tw = 0;
+            BGEMM_TUNING_ONLY(long long tw = 0;)
             for (int i = 0; i < nkb; i++) {
                 const int s = i % C::B_STAGES;
                 bool okb = true;
@@ -198,7 +199,7 @@ __global__ void __launch_bounds__(kGemmThreads, Cfg<NT, POW2, DEEP>::MIN_CTAS) g
             if (*abort_flag) {
                 for (int i = issued - 1; i >= 0 && i >= issued - C::B_STAGES; i--) {
                     const long long t0 = clock64();
-                    while (!mbar_test(b_full + 8 * (i % C::B_STAGES), (i / C::B_STAGES) & 1) && clock64() - t0 < kWaitBudgetClocks) {}
+                    while (!mbar_test(b_full + 8 * (i % C::B_STAGES), (i / C::B_STAGES) & 1) && clock64() - t0 < wait_budget_of(abort_flag)) {}
                 }
             }
         }
@@ -208,8 +209,8 @@ __global__ void __launch_bounds__(kGemmThreads, Cfg<NT, POW2, DEEP>::MIN_CTAS) g
         if (lane == 0 && me < C::NMMA) {
             constexpr uint32_t idesc = umma_idesc_u8s8(NT);
             bool ok = true;
-            long long twa = 0, twb = 0;
-            const long long tloop0 = clock64();
+            BGEMM_TUNING_ONLY(long long twa = 0, twb = 0;)
+            BGEMM_TUNING_ONLY(const long long tloop0 = clock64();)
             // Integer accumulation commutes, so the two issuers need no mutual order -- except that the UMMAs of K
             // block 0 overwrite the accumulators (accumulate = 0) and must run before anything is added.
             if (me == 1 && nkb > 1) ok = mbar_wait(first_done, 0, abort_flag, p.status, 18);
@@ -262,8 +263,8 @@ __global__ void __launch_bounds__(kGemmThreads, Cfg<NT, POW2, DEEP>::MIN_CTAS) g
             s_colsum[i] = (p.epi && n < p.N) ? __ldg(p.colsum + (size_t)batch * p.N + n) : 0;
         }
         bool ok = true;
-        long long tww = 0, twe = 0, tst = 0;
-        const long long tloop0 = clock64();
+        BGEMM_TUNING_ONLY(long long tww = 0, twe = 0, tst = 0;)
+        BGEMM_TUNING_ONLY(const long long tloop0 = clock64();)
         for (int i = set; i < nkb && ok; i += 2) {
             const int ws = i % C::W_STAGES;
             BGEMM_TIMED(tww, ok = mbar_wait(w_full + 8 * ws, (i / C::W_STAGES) & 1, abort_flag, p.status, 15));
@@ -411,7 +412,7 @@ __global__ void __launch_bounds__(kGemmThreads, Cfg<NT, POW2, DEEP>::MIN_CTAS) g
     if (warp == kWarpMma) {
         if (*abort_flag && lane == 0) {   // a wait ran out: let the issued UMMAs finish before the columns are freed
             const long long t0 = clock64();
-            while (!mbar_test(d_full, 0) && clock64() - t0 < kWaitBudgetClocks) {}
+            while (!mbar_test(d_full, 0) && clock64() - t0 < wait_budget_of(abort_flag)) {}
         }
         __syncwarp();
         tc_fence_after();

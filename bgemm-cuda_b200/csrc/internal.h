@@ -17,7 +17,9 @@ struct GemmParams {
     int32_t* ws_partial;          // split-K slabs [tile][split][NT][128], null when split_k == 1
     unsigned int* ws_counters;    // split-K arrival counters [tile]
     int* status;                  // device status word (0 = fine), may be null
-    long long* prof;              // optional phase stamps, 16 slots per CTA (tuning aid), normally null
+#ifdef BGEMM_TUNING
+    long long* prof;              // phase stamps, 32 slots per CTA (tuning builds only)
+#endif
     int M, N, K;
     int kblocks;                  // ceil(K / 256)
     int mtiles, ntiles;
@@ -32,14 +34,21 @@ struct GemmParams {
     long long out_ld;
     int act_mode;
     int acts_general;             // 1: the caller declared general int8 activations (op W1A8); 0: at most ternary expected
+    // Test hooks (bgemm_debug_set_wait_test): budget of every bounded wait in SM clocks (0 = the default) and the
+    // K block (CTA-relative stream position) whose weight tile the producer withholds (-1 = none).
+    long long wait_budget;
+    int test_skip_kblock;
 };
 
 constexpr int kOutActs = 100;     // internal out_kind of bgemm_gemm_to_acts
 
 void count_launch();
 bool programmatic_launch_enabled();   // BGEMM_PDL=0 in the environment switches it off
+#ifdef BGEMM_TUNING
 long long* debug_profile_buffer();
+#endif
 int* device_status_word();        // per-device status word, lazily created (cudaGetSymbolAddress)
+void apply_test_hooks(GemmParams& p);   // copies the process-wide test settings (normally: none) into the launch parameters
 
 int sm_count();                   // SMs of the current device (cached)
 int gemm_tile_n(long long N);

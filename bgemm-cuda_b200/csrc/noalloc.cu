@@ -18,6 +18,7 @@ unsigned char* scratch_of_current_device(int* status) {
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) { *status = (int)e; return nullptr; }
     if (dev < 0 || dev >= 64) { *status = BGEMM_ERR_UNSUPPORTED; return nullptr; }
+    // Host threads may race on a cache slot: harmless, every thread computes and stores the same address.
     if (!cache[dev]) {
         unsigned char* ptr = nullptr;
         e = cudaGetSymbolAddress((void**)&ptr, g_noalloc_scratch);

@@ -37,8 +37,16 @@ __device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
     return ok != 0;
 }
 
-// Wait budget in SM clocks (~0.2 s at 2 GHz). Far above any legitimate wait of these kernels.
+// Default wait budget in SM clocks (~0.2 s at 2 GHz). Far above any legitimate wait of these kernels.
 constexpr long long kWaitBudgetClocks = 400000000LL;
+// The budget in force lives in shared memory, 12 bytes behind the CTA's abort flag (8-byte aligned there): the kernel
+// prologue stores the default, or the shorter budget a test asked for (bgemm_debug_set_wait_test).
+__device__ __forceinline__ long long wait_budget_of(volatile int* abort_flag) {
+    return *reinterpret_cast<volatile long long*>(abort_flag + 3);
+}
+__device__ __forceinline__ void set_wait_budget(volatile int* abort_flag, long long requested) {
+    *reinterpret_cast<volatile long long*>(abort_flag + 3) = requested > 0 ? requested : kWaitBudgetClocks;
+}
 
 // One blocking probe: the thread is suspended by the hardware (no issue slots burnt) until the phase
 // completes or a short, implementation-defined time passes.
@@ -56,10 +64,10 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status_word,
                                           int where) {
     if (mbar_try_wait(bar, parity)) return true;
-    const long long t0 = clock64();
+    const long long t0 = clock64(), budget = wait_budget_of(abort_flag);
     while (!mbar_try_wait(bar, parity)) {
         if (*abort_flag) return false;
-        if (clock64() - t0 > kWaitBudgetClocks) {
+        if (clock64() - t0 > budget) {
             *abort_flag = 1;
             if (status_word) atomicCAS(status_word, 0, where);
             return false;
@@ -74,11 +82,11 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
 __device__ __forceinline__ bool mbar_wait_relaxed(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status_word,
                                                   int where) {
     if (mbar_try_wait(bar, parity)) return true;
-    const long long t0 = clock64();
+    const long long t0 = clock64(), budget = wait_budget_of(abort_flag);
     while (!mbar_try_wait(bar, parity)) {
         __nanosleep(64);
         if (*abort_flag) return false;
-        if (clock64() - t0 > kWaitBudgetClocks) {
+        if (clock64() - t0 > budget) {
             *abort_flag = 1;
             if (status_word) atomicCAS(status_word, 0, where);
             return false;

@@ -5,8 +5,7 @@
 #include <c10/cuda/CUDAStream.h>
 #include <torch/extension.h>
 
-#include <mutex>
-#include <unordered_map>
+#include <algorithm>
 
 #include "../../include/bgemm_b200.h"
 
@@ -28,18 +27,14 @@ int dtype_code(const torch::Tensor& t) {
 
 void* stream_of(const torch::Tensor& t) { return c10::cuda::getCurrentCUDAStream(t.get_device()).stream(); }
 
-// Per-device scratch, zero-initialised when (re)allocated; the library keeps its counter prefix zero.
-torch::Tensor workspace(const torch::Device& dev, size_t bytes) {
-    static std::mutex mu;
-    static std::unordered_map<int, torch::Tensor> cache;
-    std::lock_guard<std::mutex> lock(mu);
-    auto it = cache.find(dev.index());
-    if (it == cache.end() || (size_t)it->second.numel() < bytes) {
-        const int64_t n = (int64_t)std::max<size_t>(bytes, (size_t)1 << 20);
-        cache[dev.index()] = torch::zeros({n}, torch::TensorOptions().dtype(torch::kUInt8).device(dev));
-        it = cache.find(dev.index());
-    }
-    return it->second;
+// Scratch for one call, taken from torch's caching allocator on the current stream: stream-ordered like every other
+// temporary of the call (the reference's wrapper does the same, fp6_linear.cu:580-586), so calls on different streams
+// or threads never share operands. Only launches with more than 8 K partitions keep arrival counters in the first
+// 64 KiB, which must start at zero: `zero_counters` clears just that prefix.
+torch::Tensor workspace(const torch::Device& dev, size_t bytes, bool zero_counters) {
+    auto ws = torch::empty({(int64_t)std::max<size_t>(bytes, 256)}, torch::TensorOptions().dtype(torch::kUInt8).device(dev));
+    if (zero_counters) ws.narrow(0, 0, std::min<int64_t>(ws.numel(), 64 * 1024)).zero_();
+    return ws;
 }
 
 int act_mode_of(int op) { return op == BGEMM_OP_AND ? BGEMM_ACT_NEG01 : (op == BGEMM_OP_BWTA ? BGEMM_ACT_TERNARY : BGEMM_ACT_SIGN); }
@@ -60,7 +55,7 @@ torch::Tensor bgemm_linear_forward_cuda(torch::Tensor in_feats, torch::Tensor we
     auto out = torch::empty({N, M}, x.options());
     const int sk = splitK <= 1 ? 0 : (int)splitK;
     const size_t need = bgemm_linear_workspace_bytes(M, N, K, sk);
-    auto ws = workspace(x.device(), need);
+    auto ws = workspace(x.device(), need, bgemm_gemm_workspace_bytes(M, N, K, sk, 1) > 0);
     check(bgemm_linear_forward(stream_of(x), w.data_ptr(), x.data_ptr(), out.data_ptr(), M, N, K, (int)INSTR, BGEMM_OUT_F16,
                                BGEMM_LAYOUT_NM, nullptr, sk, ws.data_ptr(), (size_t)ws.numel()),
           "bgemm_linear_forward");
@@ -98,15 +93,73 @@ std::vector<torch::Tensor> binary_weight_prepacking_scaled_cuda(torch::Tensor w)
     return {plane, alpha, rowpop};
 }
 
-// `weight_prepacking_cpu` keeps the reference's export name (pybind.cpp:10); its FP6 meaning is out of
-// scope, so it is the binary prepack on the CPU: [OC, IC] CPU tensor -> tiled plane (uint8, CPU).
+// ---- packed-weight bundle: header (magic, layout version, M, K, bit mode, offsets) + plane + rowpop + alpha in ONE
+// uint8 tensor, so that a saved layer carries its own description (see bgemm_bundle_* in the C header).
+struct BundleViews {
+    int64_t M, K;
+    int wbit_mode;
+    torch::Tensor plane, rowpop, alpha;
+};
+
+// Validates the header (64 bytes are copied to the host when the bundle lives on a GPU) and returns views of the parts.
+BundleViews open_bundle(const torch::Tensor& bundle) {
+    TORCH_CHECK(bundle.scalar_type() == at::kByte && bundle.dim() == 1 && bundle.is_contiguous() && bundle.numel() >= BGEMM_BUNDLE_HEADER_BYTES,
+                "packed-weight bundle: a contiguous 1-D uint8 tensor is required");
+    auto head = bundle.narrow(0, 0, BGEMM_BUNDLE_HEADER_BYTES).cpu();
+    BundleViews v;
+    size_t po = 0, ro = 0, ao = 0;
+    const int rc = bgemm_bundle_parse_host(head.data_ptr(), (size_t)bundle.numel(), &v.M, &v.K, &v.wbit_mode, &po, &ro, &ao);
+    TORCH_CHECK(rc == 0, "packed-weight bundle: ", rc == BGEMM_ERR_UNSUPPORTED ? "unknown magic or layout version (this library reads version " : "inconsistent header (",
+                BGEMM_LAYOUT_VERSION, ")");
+    v.plane = bundle.narrow(0, (int64_t)po, (int64_t)bgemm_plane_bytes(v.M, v.K));
+    v.rowpop = bundle.narrow(0, (int64_t)ro, v.M * 4).view(at::kInt);
+    v.alpha = bundle.narrow(0, (int64_t)ao, v.M * 2).view(at::kHalf);
+    return v;
+}
+
+torch::Tensor new_bundle(const torch::Device& dev, int64_t M, int64_t K, int wbit_mode) {
+    const size_t bytes = bgemm_bundle_bytes(M, K);
+    TORCH_CHECK(bytes > 0, "packed-weight bundle: bad shape");
+    auto head = torch::zeros({BGEMM_BUNDLE_HEADER_BYTES}, torch::TensorOptions().dtype(torch::kUInt8));
+    check(bgemm_bundle_header_host(head.data_ptr(), M, K, wbit_mode), "bgemm_bundle_header_host");
+    auto bundle = torch::zeros({(int64_t)bytes}, torch::TensorOptions().dtype(torch::kUInt8).device(dev));
+    bundle.narrow(0, 0, BGEMM_BUNDLE_HEADER_BYTES).copy_(head);
+    return bundle;
+}
+
+// `weight_prepacking_cpu` keeps the reference's export name (pybind.cpp:10); its FP6 meaning is out of scope, so it is
+// the binary prepack on the CPU: [OC, IC] CPU tensor -> packed-weight bundle (uint8, CPU): header, tiled bit plane,
+// per-row bit counts, per-row mean-abs scales. `unpack_bundle` gives the parts.
 torch::Tensor weight_prepacking_cpu(torch::Tensor w) {
     TORCH_CHECK(!w.is_cuda() && w.dim() == 2, "weight_prepacking_cpu: 2-D CPU tensor required");
     w = w.contiguous();
     const int64_t M = w.size(0), K = w.size(1);
-    auto plane = torch::empty({(int64_t)bgemm_plane_bytes(M, K)}, torch::TensorOptions().dtype(torch::kUInt8));
-    check(bgemm_pack_weights_host(w.data_ptr(), dtype_code(w), M, K, K, 0, plane.data_ptr(), nullptr, nullptr), "bgemm_pack_weights_host");
-    return plane;
+    auto bundle = new_bundle(w.device(), M, K, BGEMM_WBIT_NEGATIVE);
+    auto v = open_bundle(bundle);
+    check(bgemm_pack_weights_host(w.data_ptr(), dtype_code(w), M, K, K, BGEMM_WBIT_NEGATIVE, v.plane.data_ptr(), v.rowpop.data_ptr<int>(),
+                                  v.alpha.data_ptr()),
+          "bgemm_pack_weights_host");
+    return bundle;
+}
+
+// The same on the GPU (one prepack launch).
+torch::Tensor binary_weight_prepacking_bundle_cuda(torch::Tensor w, int64_t wbit_mode) {
+    TORCH_CHECK(w.is_cuda() && w.dim() == 2, "binary_weight_prepacking_bundle_cuda: 2-D CUDA tensor required");
+    c10::cuda::CUDAGuard guard(w.device());
+    if (w.stride(-1) != 1) w = w.contiguous();
+    const int64_t M = w.size(0), K = w.size(1);
+    auto bundle = new_bundle(w.device(), M, K, (int)wbit_mode);
+    auto v = open_bundle(bundle);
+    check(bgemm_pack_weights(stream_of(w), w.data_ptr(), dtype_code(w), M, K, w.stride(0), (int)wbit_mode, v.plane.data_ptr(),
+                             v.rowpop.data_ptr<int>(), v.alpha.data_ptr(), 1, 0),
+          "bgemm_pack_weights");
+    return bundle;
+}
+
+// (plane uint8, alpha fp16 [M], rowpop int32 [M], M, K, wbit_mode): views into the bundle, header validated first.
+py::tuple unpack_bundle(torch::Tensor bundle) {
+    auto v = open_bundle(bundle);
+    return py::make_tuple(v.plane, v.alpha, v.rowpop, v.M, v.K, v.wbit_mode);
 }
 
 // The reference's row-major format (binary_matrix_prepacking_cpu, fp6_linear.cu:463-485): int32 [rows, K/32],
@@ -168,7 +221,7 @@ torch::Tensor gemm_prepared(torch::Tensor plane, int64_t M, int64_t K, torch::Te
     }
     const size_t need = bgemm_gemm_workspace_bytes(M, N, K, (int)splitK, B);
     torch::Tensor ws;
-    if (need) ws = workspace(acts.device(), need);
+    if (need) ws = workspace(acts.device(), need, true);
     check(bgemm_gemm(stream_of(acts), plane.data_ptr(), M, K, acts.data_ptr<int8_t>(), colsum.data_ptr<int>(), N, (int)op, out.data_ptr(),
                      (int)out_kind, (int)out_layout, alpha_ptr, (int)splitK, need ? ws.data_ptr() : nullptr, need ? (size_t)ws.numel() : 0, B),
           "bgemm_gemm");
@@ -200,7 +253,7 @@ std::vector<torch::Tensor> gemm_prepared_to_acts(torch::Tensor plane, int64_t M,
     }
     const size_t need = bgemm_gemm_workspace_bytes(M, N, K, (int)splitK, B);
     torch::Tensor ws;
-    if (need) ws = workspace(acts.device(), need);
+    if (need) ws = workspace(acts.device(), need, true);
     check(bgemm_gemm_to_acts(stream_of(acts), plane.data_ptr(), M, K, acts.data_ptr<int8_t>(), colsum.data_ptr<int>(), N, (int)op, alpha_ptr,
                              (int)next_act_mode, next_acts.data_ptr<int8_t>(), next_colsum.data_ptr<int>(), (int)splitK,
                              need ? ws.data_ptr() : nullptr, need ? (size_t)ws.numel() : 0, B),
@@ -242,7 +295,11 @@ torch::Tensor fp6_not_provided(py::args, py::kwargs) {
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.def("bgemm_linear_forward_cuda", &bgemm_linear_forward_cuda, "Computes BGEMM.", py::arg("in_feats"), py::arg("weights"),
           py::arg("splitK") = 1, py::arg("INSTR") = 1);
-    m.def("weight_prepacking_cpu", &weight_prepacking_cpu, "Binary weight prepacking on the CPU (tiled 1-bit plane).");
+    m.def("weight_prepacking_cpu", &weight_prepacking_cpu, "Binary weight prepacking on the CPU: packed-weight bundle (header, plane, rowpop, alpha).");
+    m.def("binary_weight_prepacking_bundle_cuda", &binary_weight_prepacking_bundle_cuda, "Binary weight prepacking on the GPU: packed-weight bundle.",
+          py::arg("w"), py::arg("wbit_mode") = 0);
+    m.def("unpack_bundle", &unpack_bundle, "Validate a packed-weight bundle's header and return (plane, alpha, rowpop, M, K, wbit_mode) views.");
+    m.attr("LAYOUT_VERSION") = (int)BGEMM_LAYOUT_VERSION;
     m.def("binary_weight_prepacking_cuda", &binary_weight_prepacking_cuda, "Binary weight prepacking on the GPU.", py::arg("w"),
           py::arg("wbit_mode") = 0);
     m.def("binary_weight_prepacking_scaled_cuda", &binary_weight_prepacking_scaled_cuda, "Prepack + per-row mean-abs scale + bit count.");

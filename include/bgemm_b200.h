@@ -18,7 +18,9 @@
  *     frees or synchronises; the caller owns all buffers and passes a workspace where one is needed.
  *   - `stream` is a cudaStream_t passed as void* (NULL = the legacy default stream).
  *   - Every entry point returns an int: 0 = success, < 0 = BGEMM_ERR_* (bad argument; nothing was
- *     launched), > 0 = a cudaError_t from the CUDA runtime.
+ *     launched or enqueued), > 0 = a cudaError_t from the CUDA runtime.
+ *   - int32 results are exact: |acc| <= K for binary / ternary activations, <= 128 K for general int8 activations
+ *     (op W1A8), for which N <= 32 additionally requires K <= 65536 (BGEMM_ERR_UNSUPPORTED beyond).
  *   - Binary value of an element: -1 if its sign bit is set, else +1 (so +0.0 -> +1, -0.0 -> -1), as in
  *     the reference device code (ptx_mma.cuh:341-399). Ternary value: -1, 0, +1 = torch.sign().
  *   - Result matrices are int32-exact internally; `out_kind` selects how they are stored.
@@ -126,6 +128,28 @@ int bgemm_pack_weights(void* stream, const void* src, int src_dtype, int64_t M, 
 int bgemm_pack_weights_host(const void* src_host, int src_dtype, int64_t M, int64_t K, int64_t ld,
                             int wbit_mode, void* plane_host, int32_t* rowpop_host, void* alpha_host);
 
+/* Packed-weight bundle: ONE byte buffer that holds everything a prepacked layer needs and says which layout it is in,
+ * so that a saved layer can be told from one written by another layout version (the reference's prepack returns a
+ * bare malloc'd word array, fp6_linear.cu:463-485, and saves nothing):
+ *   bytes 0..63   header, little endian: uint32 magic "BGPK" (0x4B504742), uint32 layout version (BGEMM_LAYOUT_VERSION),
+ *                 int64 M, int64 K, int32 wbit_mode, int32 reserved, int64 plane offset, int64 rowpop offset,
+ *                 int64 alpha offset, int64 total bytes
+ *   plane         bgemm_plane_bytes(M, K) bytes at a 256-byte aligned offset (the tiled bit plane above)
+ *   rowpop        int32 [M]   number of 1 bits per row
+ *   alpha         fp16 [M]    mean |w[m, :]|
+ * bgemm_bundle_bytes        total size for an [M, K] matrix (0 for bad sizes)
+ * bgemm_bundle_header_host  writes the 64 header bytes at `header_host`
+ * bgemm_bundle_parse_host   validates 64 header bytes (magic, version, sizes, offsets against `bundle_bytes`) and
+ *                           returns the fields; BGEMM_ERR_UNSUPPORTED for an unknown magic or layout version,
+ *                           BGEMM_ERR_SHAPE for inconsistent sizes. Any out pointer may be NULL.
+ * The parts are filled by bgemm_pack_weights{,_host} called with plane / rowpop / alpha pointing into the bundle. */
+#define BGEMM_LAYOUT_VERSION 1
+#define BGEMM_BUNDLE_HEADER_BYTES 64
+size_t bgemm_bundle_bytes(int64_t M, int64_t K);
+int bgemm_bundle_header_host(void* header_host, int64_t M, int64_t K, int wbit_mode);
+int bgemm_bundle_parse_host(const void* header_host, size_t bundle_bytes, int64_t* M, int64_t* K, int* wbit_mode,
+                            size_t* plane_offset, size_t* rowpop_offset, size_t* alpha_offset);
+
 /* Activation prepare: unpacked [N, K] (leading dimension ld) -> int8 [N, bgemm_act_ld(K)] (zero padded)
  * plus colsum int32 [N] = sum_k of the int8 row. act_mode BGEMM_ACT_*. Batched like the weights:
  * matrix i reads src + i*src_batch_stride and writes dst + i*N*bgemm_act_ld(K), colsum + i*N.
@@ -224,6 +248,14 @@ int bgemm_linear_forward_noalloc(void* stream, const void* weight_f16, const voi
  * ever ran out) and clears it when `reset` is non-zero. The reference has no counterpart: its kernels
  * have no inter-thread waits beyond __syncthreads (kernel_matmul.cuh:458-459,507-508).                   */
 int bgemm_device_status(int reset);
+
+/* Test hook for the wait-expiry path above (no counterpart in the reference; not for production use). The settings
+ * are process-wide and apply to the GEMM launches that follow: `wait_budget_clocks` > 0 shortens every bounded wait
+ * to that many SM clocks (0 = back to the default), and `skip_kblock` >= 0 makes the weight producer of every CTA
+ * of the tensor-core kernels withhold the weight tile of that K block (counted from the start of the CTA's own K
+ * range; -1 = none), so that the consumers' waits run out: the launch then drains, exits normally and reports a
+ * code through bgemm_device_status; its results are undefined. Nothing faults or hangs.                     */
+void bgemm_debug_set_wait_test(int64_t wait_budget_clocks, int skip_kblock);
 
 #ifdef __cplusplus
 }

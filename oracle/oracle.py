@@ -40,8 +40,16 @@ def build(force: bool = False) -> None:
     """Compile liboracle.so (and _ref/ when a reference checkout is present)."""
     if force or not (_HERE / "liboracle.so").exists():
         subprocess.run(["make", "-C", str(_HERE), "liboracle.so"], check=True, capture_output=True)
-    if os.path.isdir("/root/reference") and (force or not (_HERE / "_ref" / "libref_prepack.so").exists()):
-        subprocess.run(["make", "-C", str(_HERE), "ref"], check=True, capture_output=True)
+    ref_root = reference_root()
+    if ref_root and (force or not (_HERE / "_ref" / "libref_prepack.so").exists()):
+        subprocess.run(["make", "-C", str(_HERE), "ref", f"REFERENCE_ROOT={ref_root}"], check=True, capture_output=True)
+
+
+def reference_root():
+    """A checkout of the reference project, if one is reachable: $REFERENCE_ROOT, else a directory named `reference`
+    beside this repository. None when there is none (the GPU box): prebuilt files under _ref/ are then used as they are."""
+    cand = os.environ.get("REFERENCE_ROOT") or str(_HERE.parent.parent / "reference")
+    return cand if os.path.isfile(os.path.join(cand, "lowbit_kernel", "csrc", "utils", "weight_prepacking.h")) else None
 
 
 _lib = None

@@ -13,6 +13,7 @@ classes used here are the reference's pure-torch CPU paths and never call the ex
 Run:  python tests/golden/make_golden.py [reference_root]
 """
 import importlib.util
+import os
 import sys
 import types
 from pathlib import Path
@@ -22,7 +23,8 @@ import torch
 
 HERE = Path(__file__).resolve().parent
 ROOT = HERE.parent.parent
-REF = Path(sys.argv[1]) if len(sys.argv) > 1 else Path("/root/reference")
+# the reference checkout: argv[1], else $REFERENCE_ROOT, else a directory named `reference` beside this repository
+REF = Path(sys.argv[1] if len(sys.argv) > 1 else os.environ.get("REFERENCE_ROOT", Path(__file__).resolve().parents[3] / "reference"))
 
 
 def load_reference_layers():

@@ -70,6 +70,50 @@ def test_arguments_are_validated_before_any_launch(lib):
     assert lib.bgemm_linear_forward(None, None, fake, fake, 4, 4, 4, 1, 1, 0, None, 1, fake, 1 << 20) == -1
 
 
+def test_a_refused_call_enqueues_nothing(lib):
+    """Every argument error is found before the first launch or memset: the launch counter does not move, also for
+    errors that only the last stage of a composite entry point (pack, prepare, GEMM) would notice."""
+    vp, i64, ci, sz = ctypes.c_void_p, ctypes.c_int64, ctypes.c_int, ctypes.c_size_t
+    lib.bgemm_linear_forward.argtypes = [vp, vp, vp, vp, i64, i64, i64, ci, ci, ci, vp, ci, vp, sz]
+    lib.bgemm_gemm_to_acts.argtypes = [vp, vp, i64, i64, vp, vp, i64, ci, vp, ci, vp, vp, ci, vp, sz, i64]
+    lib.bgemm_gemm.argtypes = [vp, vp, i64, i64, vp, vp, i64, ci, vp, ci, ci, vp, ci, vp, sz, i64]
+    lib.bgemm_launch_count.restype = ctypes.c_uint64
+    fake, big = 0x10000, 1 << 30
+    before = lib.bgemm_launch_count()
+    assert lib.bgemm_linear_forward(None, fake, fake, fake, 64, 8, 256, 1, 7, 0, None, 1, fake, big) == -4      # out_kind
+    assert lib.bgemm_linear_forward(None, fake, fake, fake, 64, 8, 256, 1, 1, 3, None, 1, fake, big) == -4      # out_layout
+    assert lib.bgemm_linear_forward(None, fake, fake, fake, 64, 8, 256, 1, 2, 0, None, 1, fake, big) == -1      # scaled, no alpha
+    assert lib.bgemm_linear_forward(None, fake, fake, fake + 2, 64, 8, 256, 1, 0, 0, None, 1, fake, big) == -3  # int32 out misaligned
+    assert lib.bgemm_linear_forward(None, fake, fake, fake, 64, 8, 256, 1, 1, 0, None, 1, fake + 8, big) == -3  # workspace misaligned
+    assert lib.bgemm_gemm_to_acts(None, fake, 64, 8192, fake, fake, 8, 1, None, 0, fake, fake, 16, None, 0, 1) == -5   # needs a workspace
+    assert lib.bgemm_gemm_to_acts(None, fake, 64, 8192, fake, fake, 8, 1, None, 0, fake, fake, 16, fake + 16, big, 1) == -3
+    # general int8 activations on narrow tiles beyond the exact range
+    assert lib.bgemm_gemm(None, fake, 128, 70000, fake, fake, 16, 4, fake, 0, 0, None, 1, None, 0, 1) == -6
+    assert lib.bgemm_launch_count() == before
+
+
+def test_bundle_header_round_trip(lib):
+    vp, i64, ci, sz = ctypes.c_void_p, ctypes.c_int64, ctypes.c_int, ctypes.c_size_t
+    lib.bgemm_bundle_bytes.restype = sz
+    lib.bgemm_bundle_bytes.argtypes = [i64, i64]
+    lib.bgemm_bundle_header_host.argtypes = [vp, i64, i64, ci]
+    lib.bgemm_bundle_parse_host.argtypes = [vp, sz, vp, vp, vp, vp, vp, vp]
+    total = lib.bgemm_bundle_bytes(300, 1000)
+    assert total >= 256 + O.plane_bytes(300, 1000) + 300 * 6 and total % 256 == 0
+    assert lib.bgemm_bundle_bytes(0, 5) == 0
+    head = np.zeros(64, dtype=np.uint8)
+    assert lib.bgemm_bundle_header_host(head.ctypes.data, 300, 1000, 1) == 0
+    assert head[:4].tobytes() == b"BGPK" and int(head[4:8].view(np.uint32)[0]) == 1
+    M, K, po = ctypes.c_int64(), ctypes.c_int64(), ctypes.c_size_t()
+    mode = ctypes.c_int()
+    assert lib.bgemm_bundle_parse_host(head.ctypes.data, total, ctypes.byref(M), ctypes.byref(K), ctypes.byref(mode), ctypes.byref(po), None, None) == 0
+    assert (M.value, K.value, mode.value, po.value) == (300, 1000, 1, 256)
+    assert lib.bgemm_bundle_parse_host(head.ctypes.data, total - 1, None, None, None, None, None, None) == -2     # buffer too short
+    head[4] = 9
+    assert lib.bgemm_bundle_parse_host(head.ctypes.data, total, None, None, None, None, None, None) == -6         # other layout version
+    assert lib.bgemm_bundle_header_host(head.ctypes.data, 300, 1000, 7) == -4
+
+
 def test_workspace_queries(lib):
     i64, ci = ctypes.c_int64, ctypes.c_int
     lib.bgemm_gemm_workspace_bytes.restype = ctypes.c_size_t
@@ -130,7 +174,20 @@ def test_extension_module_surface():
     with pytest.raises(RuntimeError, match="CUDA tensors required"):
         lowbit_kernel.bgemm_linear_forward_cuda(torch.zeros(32, 128).half(), torch.zeros(32, 128).half(), 1, 1)
     w = torch.randn(70, 300, generator=O._gen(1)).half()
-    plane = lowbit_kernel.weight_prepacking_cpu(w)
-    assert np.array_equal(plane.numpy(), O.np_pack_weights(w, 0)[0])
+    bundle = lowbit_kernel.weight_prepacking_cpu(w)                      # header + plane + rowpop + alpha in one tensor
+    plane, alpha, rowpop, M, K, wbit = lowbit_kernel.unpack_bundle(bundle)
+    assert (M, K, wbit) == (70, 300, 0) and lowbit_kernel.LAYOUT_VERSION == 1
+    ref_plane, ref_pop = O.np_pack_weights(w, 0)
+    assert np.array_equal(plane.numpy(), ref_plane) and np.array_equal(rowpop.numpy(), ref_pop)
+    assert np.array_equal(alpha.numpy().view(np.uint16), O.c_rowmeanabs_f16(w).view(np.uint16))
+    # a bundle of another layout version, a damaged magic or a truncated buffer is refused
+    other = bundle.clone(); other[4] = 2
+    with pytest.raises(RuntimeError, match="layout version"):
+        lowbit_kernel.unpack_bundle(other)
+    bad = bundle.clone(); bad[0] = 0
+    with pytest.raises(RuntimeError, match="magic"):
+        lowbit_kernel.unpack_bundle(bad)
+    with pytest.raises(RuntimeError, match="inconsistent"):
+        lowbit_kernel.unpack_bundle(bundle[: bundle.numel() - 256].clone())
     words = lowbit_kernel.binary_matrix_prepacking(torch.randn(8, 128, generator=O._gen(2)).half())
     assert words.shape == (8, 4) and words.dtype == torch.int32

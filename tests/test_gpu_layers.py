@@ -179,3 +179,30 @@ def test_sharded_rows_single_gpu_matches_unsharded():
             parts.append(layer.forward(x))
         full = torch.cat(parts, dim=0).t().cpu()
         assert torch.equal(full, want)
+
+
+def test_binary_linear_state_dict_is_versioned(L):
+    """The layer's only buffer is the packed-weight bundle: a state_dict round trip restores the layer bit for bit, and a
+    bundle that claims another layout version (or another shape) is refused when it is loaded."""
+    import lowbit_kernel
+
+    g = O._gen(61)
+    w = torch.randn(300, 520, generator=g).half()
+    x = torch.randn(40, 520, generator=g).half().cuda()
+    a = L.BinaryLinear(w.cuda())
+    sd = {k: v.clone() for k, v in a.state_dict().items()}
+    assert list(sd) == ["packed"] and sd["packed"].dtype == torch.uint8
+    plane, alpha, rowpop, M, K, wbit = lowbit_kernel.unpack_bundle(sd["packed"])
+    assert (M, K, wbit) == (300, 520, 0)
+    assert np.array_equal(plane.cpu().numpy(), O.np_pack_weights(w, 0)[0])
+    b = L.BinaryLinear(torch.zeros(300, 520, dtype=torch.half, device="cuda"))
+    b.load_state_dict(sd)
+    assert torch.equal(b(x), a(x))
+    want = O.ref_out(O.ref_acc(w, x.cpu(), O.OP_XOR), O.OUT_F16_SCALED, a.alpha.cpu())
+    assert torch.equal(a(x).cpu(), want)
+    newer = {"packed": sd["packed"].clone()}
+    newer["packed"][4] = lowbit_kernel.LAYOUT_VERSION + 1
+    with pytest.raises(RuntimeError, match="layout version"):
+        b.load_state_dict(newer)
+    with pytest.raises(RuntimeError):                              # a 300 x 520 bundle does not fit a 128 x 520 layer
+        L.BinaryLinear(torch.zeros(128, 520, dtype=torch.half, device="cuda")).load_state_dict(sd)
