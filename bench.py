@@ -1,24 +1,29 @@
 #!/usr/bin/env python
 """Benchmark of the binary-weight x ternary-activation (BWTA) linear forward on B200.
 
-One JSON line on stdout (rank 0). A *step* is one pass over a pool of LAYERS independent layers of the
-workload shape, each with its own prepacked weight plane, activations and scales, so that no weight is
-ever served from L2 (the pool is larger than L2). The pool is submitted through the library's batch
-dimension: one activation-prepare launch and one GEMM launch per step. Effective TOPS =
-2*M*N*K*LAYERS / step time.
+One JSON line on stdout (rank 0).
 
-  value     device-resident inputs (prepacked planes, fp16 activations in HBM), the step captured in a
-            CUDA graph: activation prepare + GEMM with fused per-channel scale, fp16 out.
-  e2e       the same step through the `lowbit_kernel` extension calls with HOST activations: pinned
-            host -> device copy of every layer's activations and device -> host copy of every output
-            inside the timed region.
-  roofline  the GEMM kernel alone (graph of the batched GEMM launch only) against the int8 tensor peak.
-  per_layer_launch  the same pool as one GEMM launch per layer (the latency-bound regime), for reference.
-  cpu_baseline  the reference's CPU path (dense torch fp32 matmul on sign / ternary tensors) on this
-            host's cores, on a bounded sample of the same layers.
+Headline workload (all N): ONE logical LLM projection W[28672, 8192] x ternary X[1024, 8192] with a per-channel fp16
+scale, its output rows split over the ranks (`sharded.row_shards`; N = 1 runs the same layer unsharded), activations
+replicated. A *step* is one pass over a pool of distinct layers of that shape whose packed planes exceed L2 on every
+GPU, so no weight is ever served from L2: one batched activation-prepare launch plus one GEMM launch per layer,
+captured in a CUDA graph. Strong scaling: the work per step is fixed, value = 2*M*N*K*layers / max-over-ranks time.
 
-`--impl reference` times only that CPU path. Under torchrun every rank owns the row shard of a
-(M * world) x K layer, i.e. the same per-GPU work (weak scaling, no data-path collective).
+  value        device-resident inputs, no collective (every rank keeps its [rows_r, N] slab)
+  gather       the same step followed, per layer, by the all-gather of the slabs into the full [M, N] result on every
+               rank: plain NCCL all-gather after the GEMM, and split in column chunks with the gather of chunk i on a
+               second stream under the GEMM of chunk i + 1
+  e2e          the same step through the `lowbit_kernel` extension calls with HOST buffers: int8 ternary activations
+               copied from pinned host memory, fp16 output slabs copied back, inside the timed region
+  roofline     the dominant kernel (the GEMM launches of the step, timed alone) against the int8 tensor peak
+               (2 x the measured bf16 peak: burst figure for short windows at full clock, else sustained)
+  c2_pool      the 4096 x 4096 x 128 BWTA pool of the earlier rounds (95 layers in one batched launch, one replica per
+               rank), for continuity; `roofline.per_call` is that configuration as ONE call per layer
+  sweep        (N = 1 only) every other benchmark configuration, one call per layer over a pool > L2
+  verified     outputs of the timed kernels compared with the CPU oracle before timing (first and last layer)
+  cpu_baseline the reference's CPU path (dense torch fp32 matmul on sign / ternary tensors) on this host's cores
+
+`--impl reference` times only that CPU path on the same layer shape.
 """
 from __future__ import annotations
 
@@ -37,23 +42,12 @@ for _p in (ROOT / "bgemm-cuda_b200", ROOT / "oracle"):
     if str(_p) not in sys.path:
         sys.path.insert(0, str(_p))
 
-WORKLOADS = {
-    # name: (M, K, N, op name, description)
-    "c2": (4096, 4096, 128, "bwta", "BWTA GEMM: binary W[4096,4096] x ternary X[4096,128], fp16 alpha epilogue"),
-    "c1": (4096, 4096, 64, "xor", "BGEMM: W[4096,4096] x X[4096,64], both {-1,+1}"),
-    "c5n1": (28672, 8192, 1, "bwta", "LLM projection 28672x8192, ternary X, N=1 (single-token decode)"),
-    "c5n4": (28672, 8192, 4, "bwta", "LLM projection 28672x8192, ternary X, N=4"),
-    "c5n16": (28672, 8192, 16, "bwta", "LLM projection 28672x8192, ternary X, N=16"),
-    "c5n128": (28672, 8192, 128, "bwta", "LLM projection 28672x8192, ternary X, N=128"),
-    "c5n1024": (28672, 8192, 1024, "bwta", "LLM projection 28672x8192, ternary X, N=1024"),
-    "c5n4096": (28672, 8192, 4096, "bwta", "LLM projection 28672x8192, ternary X, N=4096"),
-}
+HEAD = dict(M=28672, K=8192, N=1024, op="bwta", desc="LLM projection: binary W[28672,8192] x ternary X[8192,1024] (P(0)=0.3), fp16 alpha epilogue, rows sharded over the GPUs")
+C2 = dict(M=4096, K=4096, N=128, op="bwta", desc="BWTA GEMM: binary W[4096,4096] x ternary X[4096,128], fp16 alpha epilogue")
 L2_BYTES = 126 * 1024 * 1024
-# dram__bytes_read.sum + dram__bytes_write.sum per layer of the batched GEMM launch (gemm_persist_kernel), from the ncu
-# capture summarised under profiles/ (80 layers captured; traffic grows in proportion to the layer count). Workloads
-# without a capture: null.
-NCU_DRAM_BYTES_PER_LAYER = {"c2": 270.15e6 / 80,     # profiles/gemm_persist_kernel_bwta_4096x4096x128_batched80.md
-                            "c5n1": 29.39e6}          # profiles/gemm_skinny_kernel_bwta_28672x8192x1.md
+I8_MICROBENCH_TOPS = 3873.0          # tcgen05.mma kind::i8 128x256x32 issue-rate microbenchmark on this pool
+# dram__bytes_read.sum + dram__bytes_write.sum per launch from the ncu captures summarised under profiles/
+NCU_TRAFFIC = {"head": None, "c2_pool_per_layer": 270.15e6 / 80}
 METRIC = "bwta_effective_tops"
 UNIT = "TOPS (2*M*N*K/s)"
 
@@ -75,11 +69,11 @@ class ClockSampler:
         self.gpu = gpu_index
         self.samples = []          # (time, sm MHz, throttle mask)
         self.t_begin = self.t_end = None
-        self.reasons = set()
         self.max_mhz = None
         self._stop = False
         self._thread = None
         self._err = None
+        self._names = {}
 
     def _run(self):
         try:
@@ -95,9 +89,8 @@ class ClockSampler:
                     pass
             h = nv.nvmlDeviceGetHandleByIndex(idx)
             self.max_mhz = float(nv.nvmlDeviceGetMaxClockInfo(h, nv.NVML_CLOCK_SM))
-            names = {"hw_slowdown": nv.nvmlClocksThrottleReasonHwSlowdown, "hw_thermal_slowdown": nv.nvmlClocksThrottleReasonHwThermalSlowdown,
-                     "sw_thermal_slowdown": nv.nvmlClocksThrottleReasonSwThermalSlowdown, "sw_power_cap": nv.nvmlClocksThrottleReasonSwPowerCap}
-            self._names = names
+            self._names = {"hw_slowdown": nv.nvmlClocksThrottleReasonHwSlowdown, "hw_thermal_slowdown": nv.nvmlClocksThrottleReasonHwThermalSlowdown,
+                           "sw_thermal_slowdown": nv.nvmlClocksThrottleReasonSwThermalSlowdown, "sw_power_cap": nv.nvmlClocksThrottleReasonSwPowerCap}
             while not self._stop:
                 self.samples.append((time.perf_counter(), float(nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM)),
                                      nv.nvmlDeviceGetCurrentClocksThrottleReasons(h)))
@@ -133,327 +126,637 @@ class ClockSampler:
                 "samples": len(win), "window_ms": (self.t_end - self.t_begin) * 1e3}
 
 
-def cpu_reference_step(ws, xs, alphas, op_name):
-    """The reference's CPU arithmetic for a list of layers: dense fp32 matmul on mapped tensors, scaled, fp16."""
-    import oracle as O
-
-    op = {"bwta": O.OP_BWTA, "xor": O.OP_XOR}[op_name]
-    outs = []
-    for w, x, a in zip(ws, xs, alphas):
-        acc = O.map_act(x, op) @ O.map_weight(w, op).T
-        outs.append((acc * a.float()).to(torch.float16))
-    return outs
-
-
-def make_layer_inputs(M, K, N, op_name, seed):
+# ------------------------------------------------------------------------------------------------------------------
+# CPU arm: the reference's own CPU arithmetic (oracle port), used as `cpu_baseline` and by `--impl reference`
+# ------------------------------------------------------------------------------------------------------------------
+def cpu_layer_operands(M, K, N, op_name, seed):
     import oracle as O
 
     g = O._gen(seed)
     w = O.rand_pm1((M, K), g)
     x = O.rand_ternary((N, K), g) if op_name == "bwta" else O.rand_pm1((N, K), g)
     alpha = (0.01 + 0.09 * torch.rand(M, generator=g)).to(torch.float16)
-    return w, x, alpha
-
-
-def time_cpu_baseline(M, K, N, op_name, budget_s=12.0, min_layers=2, max_layers=100000):
-    torch.set_num_threads(os.cpu_count() or 1)
-    w, x, a = make_layer_inputs(M, K, N, op_name, 1002)
-    import oracle as O
-
     op = {"bwta": O.OP_BWTA, "xor": O.OP_XOR}[op_name]
-    wm, xm = O.map_weight(w, op), O.map_act(x, op)          # mapping once: the matmul is what the reference times
-    cpu_reference_step([w], [x], [a], op_name)              # warm-up (includes mapping)
+    return O.map_weight(w, op), O.map_act(x, op), alpha.float()      # mapping once: the matmul is what the reference times
+
+
+def time_cpu(M, K, N, op_name, warm_s, budget_s, min_layers):
+    """Layers per second of `fp16((x @ w.T) * alpha)` on all host threads: >= warm_s of warm-up, then >= budget_s timed."""
+    torch.set_num_threads(os.cpu_count() or 1)
+    wm, xm, a = cpu_layer_operands(M, K, N, op_name, 1002)
+
+    def layer():
+        return ((xm @ wm.T) * a).to(torch.float16)
+
+    t0 = time.perf_counter()
+    layer()
+    while time.perf_counter() - t0 < warm_s:
+        layer()
     t0 = time.perf_counter()
     n = 0
     while True:
-        acc = xm @ wm.T
-        _ = (acc * a.float()).to(torch.float16)
+        layer()
         n += 1
         dt = time.perf_counter() - t0
-        if (dt > budget_s and n >= min_layers) or n >= max_layers:
+        if dt >= budget_s and n >= min_layers:
             break
     return 2.0 * M * N * K * n / dt / 1e12, n, dt
 
 
-def run_reference_arm(args, M, K, N, op_name, desc):
-    rank = int(os.environ.get("RANK", "0"))
-    if rank != 0:
+def run_reference_arm(args):
+    if int(os.environ.get("RANK", "0")) != 0:
         return
-    torch.set_num_threads(os.cpu_count() or 1)
-    import oracle as O
-
-    op = {"bwta": O.OP_BWTA, "xor": O.OP_XOR}[op_name]
-    sample_layers = 2 if M * K * N <= 4096 * 4096 * 128 else 1
-    layers = [make_layer_inputs(M, K, N, op_name, 1002 + i) for i in range(sample_layers)]
-    mapped = [(O.map_weight(w, op), O.map_act(x, op), a.float()) for w, x, a in layers]
-
-    def step():
-        for wm, xm, a in mapped:
-            _ = ((xm @ wm.T) * a).to(torch.float16)
-
-    for _ in range(args.warmup):
-        step()
-    t0 = time.perf_counter()
-    for _ in range(args.steps):
-        step()
-    dt = time.perf_counter() - t0
-    val = 2.0 * M * N * K * sample_layers * args.steps / dt / 1e12
+    M, K, N, op_name = HEAD["M"], HEAD["K"], HEAD["N"], HEAD["op"]
+    val, n, dt = time_cpu(M, K, N, op_name, warm_s=1.0, budget_s=3.0, min_layers=max(1, args.steps))
+    cores = torch.get_num_threads()
     line = {
         "impl": "reference", "metric": METRIC, "value": val, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
-        "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True, "scaling": "weak",
+        "warmup": args.warmup, "ms_per_step": dt / n * 1e3, "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": "f32 (CPU matmul on {-1,0,+1} tensors)", "data": "synthetic",
-        "config": {"workload": desc, "M": M, "K": K, "N": N, "layers_per_step": sample_layers},
-        "cpu_baseline": {"value": val, "unit": UNIT, "cores": torch.get_num_threads(), "kind": "port",
-                         "sample": f"{sample_layers} layer(s) per step, {args.steps} steps, torch fp32 matmul + scale + fp16 cast"},
+        "config": {"workload": HEAD["desc"], "M": M, "K": K, "N": N, "layers_per_step": 1, "timed_layers": n, "timed_s": dt},
+        "cpu_baseline": {"value": val, "unit": UNIT, "cores": cores, "kind": "port",
+                         "sample": f"{n} layer(s) in {dt:.1f} s after 1 s of warm-up: torch fp32 matmul on mapped tensors + scale + fp16 cast (the reference's CPU path)"},
         "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
     print(json.dumps(line), flush=True)
 
 
-def main():
-    ap = argparse.ArgumentParser()
-    ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=400)
-    ap.add_argument("--warmup", type=int, default=5)
-    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
-    ap.add_argument("--layers", type=int, default=0, help="layers per step (0 = enough that the weight pool exceeds L2)")
-    ap.add_argument("--split-k", type=int, default=0)
-    ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--no-e2e", action="store_true")
-    ap.add_argument("--gather", action="store_true", help="all-gather the row shards' outputs (multi-GPU only)")
-    args = ap.parse_args()
-    args.warmup = max(args.warmup, 3)
-    M, K, N, op_name, desc = WORKLOADS[args.workload]
+# ------------------------------------------------------------------------------------------------------------------
+# GPU arm
+# ------------------------------------------------------------------------------------------------------------------
+class Ctx:
+    """Per-process state: device, stream, distributed group, library bindings."""
 
-    if args.impl == "reference":
-        run_reference_arm(args, M, K, N, op_name, desc)
-        return
+    def __init__(self):
+        import torch.distributed as dist
 
-    import torch.distributed as dist
+        self.dist = dist
+        self.world = int(os.environ.get("WORLD_SIZE", "1"))
+        self.rank = int(os.environ.get("RANK", "0"))
+        self.local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+        assert torch.cuda.is_available(), "bench.py needs a CUDA device (there is no CPU path for the b200 arm)"
+        torch.cuda.set_device(self.local_rank)
+        self.dev = torch.device("cuda", self.local_rank)
+        if self.world > 1:
+            os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+            dist.init_process_group("nccl", device_id=self.dev)
+        import bgemm_b200 as B
 
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
-    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    assert torch.cuda.is_available(), "bench.py needs a CUDA device (there is no CPU path for the b200 arm)"
-    torch.cuda.set_device(local_rank)
-    dev = torch.device("cuda", local_rank)
-    if world > 1:
-        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        dist.init_process_group("nccl", device_id=dev)
+        self.B = B
+        self.stream = torch.cuda.Stream(device=self.dev)
+        self.peaks = measured_peaks()
 
-    import bgemm_b200 as B
-    import lowbit_kernel
-
-    sampler = ClockSampler(local_rank)      # started early: NVML start-up takes longer than a short timed region
-    if rank == 0:
-        sampler.start()
-    op = {"bwta": B.OP_BWTA, "xor": B.OP_XOR}[op_name]
-    act_mode = B.ACT_MODE_OF_OP[op]
-    plane_b = B.plane_bytes(M, K)
-    layers = args.layers or max(8, -(-int(1.5 * L2_BYTES) // plane_b))
-    peaks = measured_peaks()
-
-    # ---- synthetic inputs: one distinct packed weight plane, activation matrix and scale vector per layer ----
-    g = torch.Generator(device=dev)
-    g.manual_seed(1002 + rank)
-    planes = torch.empty(layers * plane_b, dtype=torch.uint8, device=dev)
-    for i in range(layers):
-        w = (torch.randint(0, 2, (M, K), generator=g, device=dev, dtype=torch.int8) * 2 - 1)
-        B.check(B.lib.bgemm_pack_weights(None, w.data_ptr(), B.DT_I8, M, K, K, B.WBIT_NEGATIVE, planes.data_ptr() + i * plane_b,
-                                         None, None, 1, 0), "pack")
-        torch.cuda.synchronize()
-        del w
-    alphas = (0.01 + 0.09 * torch.rand(layers, M, generator=g, device=dev)).to(torch.float16)
-    if op_name == "bwta":
-        u = torch.rand(layers, N, K, generator=g, device=dev)
-        xs_dev = torch.where(u < 0.35, -1.0, torch.where(u < 0.70, 1.0, 0.0)).to(torch.float16)
-        del u
-    else:
-        xs_dev = (torch.randint(0, 2, (layers, N, K), generator=g, device=dev) * 2 - 1).to(torch.float16)
-    xs_host = xs_dev.cpu().pin_memory()
-    outs = torch.empty((layers, N, M), dtype=torch.float16, device=dev)
-    acts = torch.empty((layers, N, B.act_ld(K)), dtype=torch.int8, device=dev)
-    colsum = torch.empty((layers, N), dtype=torch.int32, device=dev)
-    split_k = args.split_k
-    ws = B.workspace(dev, max(B.lib.bgemm_gemm_workspace_bytes(M, N, K, split_k, layers), B.lib.bgemm_gemm_workspace_bytes(M, N, K, split_k, 1), 1))
-    stream = torch.cuda.Stream(device=dev)
-    act_row = N * B.act_ld(K)
-
-    # One step = ONE batched launch of each kernel over the whole pool (the library's batch dimension).
-    def prep_all():
-        B.check(B.lib.bgemm_prepare_acts(stream.cuda_stream, xs_dev.data_ptr(), B.DT_F16, N, K, K, act_mode, 0, acts.data_ptr(),
-                                         colsum.data_ptr(), layers, N * K), "prepare")
-
-    def gemm_all():
-        B.check(B.lib.bgemm_gemm(stream.cuda_stream, planes.data_ptr(), M, K, acts.data_ptr(), colsum.data_ptr(), N, op, outs.data_ptr(),
-                                 B.OUT_F16_SCALED, B.LAYOUT_NM, alphas.data_ptr(), split_k, ws.data_ptr(), ws.numel(), layers), "gemm")
-
-    # The same pool as one launch per layer (latency-bound regime), reported for reference only.
-    def gemm_one(i):
-        B.check(B.lib.bgemm_gemm(stream.cuda_stream, planes.data_ptr() + i * plane_b, M, K, acts.data_ptr() + i * act_row,
-                                 colsum.data_ptr() + 4 * i * N, N, op, outs.data_ptr() + 2 * i * N * M, B.OUT_F16_SCALED, B.LAYOUT_NM,
-                                 alphas.data_ptr() + 2 * i * M, split_k, ws.data_ptr(), ws.numel(), 1), "gemm")
-
-    def full_step():
-        prep_all()
-        gemm_all()
-
-    def per_layer_step():
-        for i in range(layers):
-            gemm_one(i)
-
-    # warm up outside capture (sets function attributes, fills caches), then capture the graphs
-    with torch.cuda.stream(stream):
-        c0 = B.launch_count()
-        full_step()
-        launches_per_step = B.launch_count() - c0
-        per_layer_step()
-        stream.synchronize()
-        g_full, g_gemm, g_layers = torch.cuda.CUDAGraph(), torch.cuda.CUDAGraph(), torch.cuda.CUDAGraph()
-        with torch.cuda.graph(g_full, stream=stream):
-            full_step()
-        with torch.cuda.graph(g_gemm, stream=stream):
-            gemm_all()
-        with torch.cuda.graph(g_layers, stream=stream):
-            per_layer_step()
-    torch.cuda.synchronize()
-
-    def barrier():
-        if world > 1:
-            dist.barrier()
+    def barrier(self):
+        if self.world > 1:
+            self.dist.barrier()
         torch.cuda.synchronize()
 
-    def timed(graph, steps, warmup):
-        with torch.cuda.stream(stream):
-            for _ in range(warmup):
-                graph.replay()
-            barrier()
-            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            e0.record(stream)
-            for _ in range(steps):
-                graph.replay()
-            e1.record(stream)
-            barrier()
-        ms = e0.elapsed_time(e1)
-        if world > 1:
-            t = torch.tensor([ms], device=dev)
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    def max_over_ranks(self, ms):
+        if self.world > 1:
+            t = torch.tensor([ms], device=self.dev, dtype=torch.float64)
+            self.dist.all_reduce(t, op=self.dist.ReduceOp.MAX)
             ms = float(t.item())
         return ms
 
-    if rank == 0:
+    def timed(self, fn, steps, warmup):
+        """max-over-ranks device time (ms) of `steps` calls of fn() on self.stream, barrier + synchronize on both sides."""
+        with torch.cuda.stream(self.stream):
+            for _ in range(warmup):
+                fn()
+            self.barrier()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(self.stream)
+            for _ in range(steps):
+                fn()
+            e1.record(self.stream)
+            self.barrier()
+        return self.max_over_ranks(e0.elapsed_time(e1))
+
+    def graph_of(self, fn):
+        with torch.cuda.stream(self.stream):
+            fn()                                     # outside capture: sets function attributes, sizes caches
+            self.stream.synchronize()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=self.stream):
+                fn()
+        torch.cuda.synchronize()
+        return g
+
+
+OPS = {"bwta": "OP_BWTA", "xor": "OP_XOR", "attn": "OP_ATTN"}
+
+
+class Pool:
+    """`layers` independent problems [rows, K] x [N, K] with distinct packed planes, activations and scales, on one GPU.
+    rows = this rank's share of M (all of M when unsharded)."""
+
+    def __init__(self, cx: Ctx, M, K, N, op_name, layers, seed, rows=None, row0=0, keep_host=(0,)):
+        B, dev = cx.B, cx.dev
+        self.cx, self.M, self.K, self.N, self.op_name, self.layers = cx, M, K, N, op_name, layers
+        self.rows = M if rows is None else rows
+        self.row0 = row0
+        self.op = getattr(B, OPS[op_name])
+        self.act_mode = B.ACT_MODE_OF_OP[self.op]
+        self.plane_b = B.plane_bytes(self.rows, K)
+        g = torch.Generator(device=dev)
+        g.manual_seed(seed)                                      # same seed on every rank: one logical layer, replicated inputs
+        self.planes = torch.empty(layers * self.plane_b, dtype=torch.uint8, device=dev)
+        self.host = {}                                           # layer -> (w int8 [rows, K], x int8 [N, K]) kept for the oracle check
+        for i in range(layers):
+            w = torch.randint(0, 2, (M, K), generator=g, device=dev, dtype=torch.int8) * 2 - 1
+            w = w[row0:row0 + self.rows]
+            B.check(B.lib.bgemm_pack_weights(None, w.data_ptr(), B.DT_I8, self.rows, K, K, B.WBIT_NEGATIVE,
+                                             self.planes.data_ptr() + i * self.plane_b, None, None, 1, 0), "pack")
+            torch.cuda.synchronize()
+            if i in keep_host or i - layers in keep_host:
+                self.host[i] = [w.cpu(), None]
+            del w
+        self.alphas_full = (0.01 + 0.09 * torch.rand(layers, M, generator=g, device=dev)).to(torch.float16)
+        self.alphas = self.alphas_full[:, row0:row0 + self.rows].contiguous()
+        if op_name == "bwta":
+            u = torch.rand(layers, N, K, generator=g, device=dev)
+            self.x8 = torch.where(u < 0.35, -1, torch.where(u < 0.70, 1, 0)).to(torch.int8)
+            del u
+        else:
+            self.x8 = (torch.randint(0, 2, (layers, N, K), generator=g, device=dev, dtype=torch.int8) * 2 - 1)
+        for i in self.host:
+            self.host[i][1] = self.x8[i].cpu()
+        self.acts = torch.empty((layers, N, B.act_ld(K)), dtype=torch.int8, device=dev)
+        self.colsum = torch.empty((layers, N), dtype=torch.int32, device=dev)
+        self.act_row = N * B.act_ld(K)
+
+    # ---- launches on cx.stream ------------------------------------------------------------------------------------
+    def prepare_all(self, src=None):
+        B = self.cx.B
+        src = self.x8 if src is None else src
+        B.check(B.lib.bgemm_prepare_acts(self.cx.stream.cuda_stream, src.data_ptr(), B.dtype_code(src), self.N, self.K, self.K, self.act_mode, 0,
+                                         self.acts.data_ptr(), self.colsum.data_ptr(), self.layers, self.N * self.K), "prepare")
+
+    def gemm_layer(self, i, out, out_kind, layout, n0=0, n1=None, stream=None):
+        """One call for layer i, activation rows [n0, n1). `out` is the destination tensor of exactly that problem."""
+        B = self.cx.B
+        n1 = self.N if n1 is None else n1
+        a_off = i * self.act_row + n0 * B.act_ld(self.K)
+        B.check(B.lib.bgemm_gemm((stream or self.cx.stream).cuda_stream, self.planes.data_ptr() + i * self.plane_b, self.rows, self.K,
+                                 self.acts.data_ptr() + a_off, self.colsum.data_ptr() + 4 * (i * self.N + n0), n1 - n0, self.op, out.data_ptr(),
+                                 out_kind, layout, self.alphas.data_ptr() + 2 * i * self.rows, 0, None, 0, 1), "gemm")
+
+    def gemm_batched(self, outs, out_kind, layout):
+        B = self.cx.B
+        B.check(B.lib.bgemm_gemm(self.cx.stream.cuda_stream, self.planes.data_ptr(), self.rows, self.K, self.acts.data_ptr(), self.colsum.data_ptr(),
+                                 self.N, self.op, outs.data_ptr(), out_kind, layout, self.alphas.data_ptr(), 0, None, 0, self.layers), "gemm")
+
+    # ---- oracle ---------------------------------------------------------------------------------------------------
+    def expect(self, i, out_kind, layout):
+        """What layer i must produce, from the CPU oracle (dense fp32 matmul on the mapped int8 operands)."""
+        import oracle as O
+
+        w, x = self.host[i]
+        op = {"bwta": O.OP_BWTA, "xor": O.OP_XOR}[self.op_name]
+        acc = O.ref_acc(w.to(torch.float16), x.to(torch.float16), op)
+        want = O.ref_out(acc, out_kind, self.alphas[i].cpu())
+        return want.t() if layout == self.cx.B.LAYOUT_MN else want
+
+    def bytes_alg(self):
+        """Compulsory bytes of one layer's GEMM call: plane + int8 activations + column sums + scales + fp16 output."""
+        return self.plane_b + self.N * self.cx.B.act_ld(self.K) + 4 * self.N + 2 * self.rows + 2 * self.N * self.rows
+
+    def ops(self):
+        return 2.0 * self.rows * self.N * self.K
+
+
+def int8_peak(peaks, window_ms, clocks):
+    """2 x the bf16 GEMM peak: the burst figure when the timed window is short or ran at full clock, else sustained."""
+    burst = window_ms < 1000.0 or (clocks and clocks.get("sm_mhz") and clocks.get("sm_max_mhz") and clocks["sm_mhz"] >= 0.97 * clocks["sm_max_mhz"])
+    if burst:
+        return 2.0 * peaks["bf16_tflops"], f"2 x burst bf16 GEMM peak ({peaks['source']}: {peaks['bf16_tflops']} TF/s; window {window_ms:.0f} ms)"
+    return 2.0 * peaks["bf16_tflops_sustained"], f"2 x sustained bf16 GEMM peak ({peaks['source']}: {peaks['bf16_tflops_sustained']} TF/s; window {window_ms:.0f} ms below full clock)"
+
+
+def bound_and_frac(ops, bytes_alg, us, peaks, i8_peak):
+    t = us * 1e-6
+    tops, gbs = ops / t / 1e12, bytes_alg / t / 1e9
+    t_tensor, t_hbm = ops / (i8_peak * 1e12), bytes_alg / (peaks["hbm_gbs"] * 1e9)
+    if t_tensor >= t_hbm:
+        return {"bound": "tensor", "tops": tops, "gbs": gbs, "frac": tops / i8_peak}
+    return {"bound": "hbm", "tops": tops, "gbs": gbs, "frac": gbs / peaks["hbm_gbs"]}
+
+
+def check_equal(got, want, what):
+    ok = bool(torch.equal(got.cpu(), want))
+    if not ok:
+        sys.stderr.write(f"VERIFY FAILED: {what}: {int((got.cpu() != want).sum())} of {want.numel()} elements differ\n")
+    return ok
+
+
+# ---- headline: the row-sharded LLM projection ---------------------------------------------------------------------------
+def run_head(cx: Ctx, args, sampler):
+    from sharded import row_shards
+
+    B = cx.B
+    M, K, N = HEAD["M"], HEAD["K"], HEAD["N"]
+    s, e = row_shards(M, cx.world)[cx.rank]
+    rows = e - s
+    shard_plane = B.plane_bytes(rows, K)
+    layers = args.layers or max(4, -(-int(1.5 * L2_BYTES) // shard_plane))
+    pool = Pool(cx, M, K, N, "bwta", layers, seed=1005, rows=rows, row0=s, keep_host=(0, -1))
+    outs = torch.empty((layers, rows, N), dtype=torch.float16, device=cx.dev)           # [rows_r, N] slabs: they concatenate along M
+
+    def gemms():
+        for i in range(layers):
+            pool.gemm_layer(i, outs[i], B.OUT_F16_SCALED, B.LAYOUT_MN)
+
+    def step():
+        pool.prepare_all()
+        gemms()
+
+    # ---- verify what will be timed: first and last layer of the pool against the oracle ----
+    with torch.cuda.stream(cx.stream):
+        c0 = B.launch_count()
+        step()
+        launches_per_step = B.launch_count() - c0
+    cx.stream.synchronize()
+    verified = all(check_equal(outs[i], pool.expect(i, B.OUT_F16_SCALED, B.LAYOUT_MN), f"sharded layer {i} rank {cx.rank}") for i in sorted(pool.host))
+    g_step, g_gemm = cx.graph_of(step), cx.graph_of(gemms)
+
+    if cx.rank == 0:
         sampler.begin()
-    ms_full = timed(g_full, args.steps, args.warmup)
-    ms_gemm = timed(g_gemm, args.steps, args.warmup)
-    if rank == 0:
+    ms_step = cx.timed(g_step.replay, args.steps, args.warmup)
+    ms_gemm = cx.timed(g_gemm.replay, args.steps, args.warmup)
+    if cx.rank == 0:
         sampler.end()
-    clocks = sampler.stop() if rank == 0 else None
-    ms_layers = timed(g_layers, max(3, args.steps // 5), 3)
+    clocks = sampler.stop() if cx.rank == 0 else None
+
+    ops_layer = 2.0 * M * N * K                                    # the whole logical layer
+    value = ops_layer * layers * args.steps / (ms_step * 1e-3) / 1e12
+    launch_us = ms_gemm * 1e3 / (args.steps * layers)             # one GEMM launch = this rank's shard of one layer
+    i8_peak, peak_source = int8_peak(cx.peaks, ms_step + ms_gemm, clocks)
+    bf = bound_and_frac(pool.ops(), pool.bytes_alg(), launch_us, cx.peaks, i8_peak)
+    roofline = {"bound": bf["bound"], "achieved": bf["tops"] if bf["bound"] == "tensor" else bf["gbs"],
+                "peak": i8_peak if bf["bound"] == "tensor" else cx.peaks["hbm_gbs"], "unit": "TFLOP/s" if bf["bound"] == "tensor" else "GB/s",
+                "frac": bf["frac"], "traffic": NCU_TRAFFIC["head"] if cx.world == 1 else None, "peak_source": peak_source,
+                "frac_vs_i8_microbench": bf["tops"] / I8_MICROBENCH_TOPS, "i8_microbench_tops": I8_MICROBENCH_TOPS,
+                "kernel": "gemm_kernel<128> (tcgen05.mma kind::i8, A operand unpacked into tensor memory), one launch per layer shard",
+                "launch_us": launch_us, "ops_per_launch": pool.ops(), "bytes_alg_per_launch": pool.bytes_alg(),
+                "kernel_tops": bf["tops"], "kernel_gbs": bf["gbs"], "ops": "integer multiply-adds x 2"}
+
+    # ---- with the all-gather of the slabs (multi-GPU only) ----
+    gather = None
+    if cx.world > 1:
+        gather = run_gather(cx, args, pool, outs, layers, rows, ops_layer)
+
+    # ---- end to end through the extension with host buffers ----
+    e2e = None if args.no_e2e else run_head_e2e(cx, args, pool, layers, rows, ops_layer)
+
     status = B.lib.bgemm_device_status(1)
     assert status == 0, f"a bounded wait inside a kernel ran out (device status {status}): results invalid"
+    return dict(value=value, ms_per_step=ms_step / args.steps, roofline=roofline, clocks=clocks, verified=verified, gather=gather, e2e=e2e,
+                launches_per_step=int(launches_per_step), layers=layers, rows=rows, plane_mib=layers * shard_plane / 2**20,
+                gemm_only={"value": ops_layer * layers * args.steps / (ms_gemm * 1e-3) / 1e12, "ms_per_step": ms_gemm / args.steps})
 
-    ops_layer = 2.0 * M * N * K
-    value = ops_layer * layers * world * args.steps / (ms_full * 1e-3) / 1e12
-    launch_us = ms_gemm * 1e3 / args.steps                                   # one batched GEMM launch
-    gemm_tops = ops_layer * layers / (launch_us * 1e-6) / 1e12
-    bytes_layer = plane_b + N * B.act_ld(K) + 4 * N + 2 * M + 2 * N * M      # plane + int8 acts + colsum + alpha + fp16 out
-    gemm_gbs = bytes_layer * layers / (launch_us * 1e-6) / 1e9
-    int8_peak = 2.0 * peaks["bf16_tflops_sustained"]
-    t_tensor, t_hbm = ops_layer / (int8_peak * 1e12), bytes_layer / (peaks["hbm_gbs"] * 1e9)
-    if t_tensor >= t_hbm:
-        roofline = {"bound": "tensor", "achieved": gemm_tops, "peak": int8_peak, "unit": "TFLOP/s", "frac": gemm_tops / int8_peak,
-                    "traffic": (NCU_DRAM_BYTES_PER_LAYER[args.workload] * layers if args.workload in NCU_DRAM_BYTES_PER_LAYER else None),
-                    "peak_source": f"2 x sustained bf16 GEMM peak ({peaks['source']}; the int8 pipe runs at twice the bf16 rate); burst "
-                                   f"2 x {peaks['bf16_tflops']}; tcgen05 kind::i8 issue-rate microbenchmark on this pool: 3873",
-                    "ops": "integer multiply-adds x 2"}
-    else:
-        roofline = {"bound": "hbm", "achieved": gemm_gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": gemm_gbs / peaks["hbm_gbs"],
-                    "traffic": (NCU_DRAM_BYTES_PER_LAYER[args.workload] * layers if args.workload in NCU_DRAM_BYTES_PER_LAYER else None), "peak_source": peaks["source"]}
-    roofline.update({"kernel": "gemm_skinny_kernel (CUDA cores, weight streaming) for N <= 4; gemm_persist_kernel for pools with one tile across N, else gemm_kernel (tcgen05 kind::i8, A operand unpacked into tensor memory)", "launch_us": launch_us,
-                     "layers_per_launch": layers, "bytes_alg_per_launch": bytes_layer * layers, "ops_per_launch": ops_layer * layers,
-                     "kernel_gbs": gemm_gbs, "kernel_tops": gemm_tops})
-    lsteps = max(3, args.steps // 5)
-    per_layer = {"us_per_layer": ms_layers * 1e3 / (lsteps * layers),
-                 "tops": ops_layer * layers * lsteps / (ms_layers * 1e-3) / 1e12,
-                 "what": "same pool, one GEMM launch per layer in a CUDA graph (latency-bound regime)",
-                 "split_k": split_k or B.lib.bgemm_gemm_auto_split_k(M, N, K, 1)}
 
-    # ---- end to end through the extension with host activations -------------------------------------------------
-    e2e = None
-    if not args.no_e2e:
-        # The pool goes through the `lowbit_kernel` calls in groups on three streams, so that the host -> device
-        # copies of a group's activations and the device -> host copies of its outputs overlap other groups' GEMMs.
-        groups = max(1, min(8, layers // 8))
-        bounds = [layers * j // groups for j in range(groups + 1)]
-        h2d_s, d2h_s = torch.cuda.Stream(device=dev), torch.cuda.Stream(device=dev)
-        x_stage = torch.empty((layers, N, K), dtype=torch.float16, device=dev)
-        out_host = torch.empty((layers, N, M), dtype=torch.float16).pin_memory()
-        h2d_bytes = layers * N * K * 2
-        d2h_bytes = layers * N * M * 2
-        plane_groups = [planes[bounds[j] * plane_b: bounds[j + 1] * plane_b] for j in range(groups)]
-        alpha_groups = [alphas[bounds[j]: bounds[j + 1]].contiguous() for j in range(groups)]
+def run_gather(cx: Ctx, args, pool: Pool, outs, layers, rows, ops_layer):
+    """The step plus, per layer, the all-gather of the [rows_r, N] slabs into the full [M, N] result on every rank."""
+    B, dist = cx.B, cx.dist
+    M, N = pool.M, pool.N
+    even = rows * cx.world == M
+    if not even:
+        return {"skipped": "uneven shards"}
+    full = torch.empty((layers, M, N), dtype=torch.float16, device=cx.dev)
+    steps = max(3, min(args.steps, 10))
 
-        def e2e_step():
-            keep = []
-            for j in range(groups):
-                lo, hi = bounds[j], bounds[j + 1]
-                with torch.cuda.stream(h2d_s):
-                    x_stage[lo:hi].copy_(xs_host[lo:hi], non_blocking=True)
-                    ev = torch.cuda.Event(); ev.record(h2d_s)
-                with torch.cuda.stream(stream):
-                    stream.wait_event(ev)
-                    a, c = lowbit_kernel.prepare_acts(x_stage[lo:hi], act_mode, False)
-                    y = lowbit_kernel.gemm_prepared(plane_groups[j], M, K, a, c, op, B.OUT_F16_SCALED, B.LAYOUT_NM, alpha_groups[j], split_k)
-                    ev2 = torch.cuda.Event(); ev2.record(stream)
-                with torch.cuda.stream(d2h_s):
-                    d2h_s.wait_event(ev2)
-                    out_host[lo:hi].copy_(y, non_blocking=True)
-                    y.record_stream(d2h_s)
-                keep.append((a, c, y))
-            return keep
+    def step_plain():
+        pool.prepare_all()
+        for i in range(layers):
+            pool.gemm_layer(i, outs[i], B.OUT_F16_SCALED, B.LAYOUT_MN)
+            dist.all_gather_into_tensor(full[i], outs[i])
 
-        e2e_steps = max(3, min(args.steps, 20))
-        for _ in range(3):
-            e2e_step()
-        barrier()
-        t0 = time.perf_counter()
-        for _ in range(e2e_steps):
-            e2e_step()
-        d2h_s.synchronize(); stream.synchronize(); h2d_s.synchronize()
-        wall_ms = (time.perf_counter() - t0) * 1e3
-        barrier()
-        if world > 1:
-            t = torch.tensor([wall_ms], device=dev)
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            wall_ms = float(t.item())
-        e2e = {"value": ops_layer * layers * world * e2e_steps / (wall_ms * 1e-3) / 1e12, "unit": UNIT, "h2d_bytes_per_step": h2d_bytes,
-               "d2h_bytes_per_step": d2h_bytes, "steps": e2e_steps, "ms_per_step": wall_ms / e2e_steps,
-               "api": f"lowbit_kernel.prepare_acts + gemm_prepared (batched, {groups} groups on 3 streams): fp16 activations from pinned host "
-                      "memory, fp16 outputs copied back to pinned host memory, weights resident (prepacked)"}
+    # overlapped: activation rows in chunks; chunk c's [N_c, rows] block (output layout [N, M_r]) is gathered on a second
+    # stream while the GEMM of chunk c + 1 runs. The gathered buffer is blocked [world][N_c][rows] per chunk.
+    chunks = 4
+    nb = [N * c // chunks for c in range(chunks + 1)]
+    outs_nm = torch.empty((layers, N, rows), dtype=torch.float16, device=cx.dev)
+    full_blk = [torch.empty((layers, cx.world, nb[c + 1] - nb[c], rows), dtype=torch.float16, device=cx.dev) for c in range(chunks)]
+    comm = torch.cuda.Stream(device=cx.dev)
+
+    def step_overlap():
+        pool.prepare_all()
+        for i in range(layers):
+            for c in range(chunks):
+                pool.gemm_layer(i, outs_nm[i, nb[c]:nb[c + 1]], B.OUT_F16_SCALED, B.LAYOUT_NM, nb[c], nb[c + 1])
+                ev = torch.cuda.Event()
+                ev.record(cx.stream)
+                with torch.cuda.stream(comm):
+                    comm.wait_event(ev)
+                    dist.all_gather_into_tensor(full_blk[c][i], outs_nm[i, nb[c]:nb[c + 1]])
+        cx.stream.wait_stream(comm)
+
+    with torch.cuda.stream(cx.stream):
+        step_plain()
+        step_overlap()
+    torch.cuda.synchronize()
+    ok = True
+    if cx.rank == 0:                      # one gathered layer against the oracle (all rows), outside the timed region
+        import oracle as O
+
+        g = torch.Generator(device=cx.dev)
+        g.manual_seed(1005)
+        w0 = (torch.randint(0, 2, (M, pool.K), generator=g, device=cx.dev, dtype=torch.int8) * 2 - 1).cpu()
+        acc = O.ref_acc(w0.to(torch.float16), pool.host[0][1].to(torch.float16), O.OP_BWTA)
+        want = O.ref_out(acc, O.OUT_F16_SCALED, pool.alphas_full[0].cpu())                  # [N, M]
+        ok = check_equal(full[0], want.t(), "gathered layer 0 (plain all-gather)")
+        blk = torch.cat([full_blk[c][0] for c in range(chunks)], dim=1)                     # [world, N, rows]
+        ok = check_equal(blk.permute(1, 0, 2).reshape(N, M), want, "gathered layer 0 (chunked, overlapped)") and ok
+    ms_plain = cx.timed(step_plain, steps, 2)
+    ms_over = cx.timed(step_overlap, steps, 2)
+    per = lambda ms: {"value": ops_layer * layers * steps / (ms * 1e-3) / 1e12, "ms_per_step": ms / steps, "us_per_layer": ms * 1e3 / (steps * layers)}
+    return {"verified": ok, "bytes_received_per_gpu_per_layer": 2 * N * (M - rows),
+            "nccl_all_gather_after_gemm": per(ms_plain), "nccl_all_gather_overlapped_4_chunks": per(ms_over), "steps": steps,
+            "what": "eager launches (no CUDA graph): GEMM per layer, then torch.distributed.all_gather_into_tensor of the fp16 slabs"}
+
+
+def run_head_e2e(cx: Ctx, args, pool: Pool, layers, rows, ops_layer):
+    """The step through the `lowbit_kernel` calls with host buffers: per layer, int8 ternary activations from pinned host
+    memory -> prepare -> GEMM -> this rank's fp16 slab back to pinned host memory. Three streams keep both copy
+    directions and the kernels busy."""
+    import lowbit_kernel
+
+    B = cx.B
+    N, K = pool.N, pool.K
+    x_host = pool.x8.cpu().pin_memory()
+    out_host = torch.empty((layers, rows, N), dtype=torch.float16).pin_memory()
+    x_stage = torch.empty((layers, N, K), dtype=torch.int8, device=cx.dev)
+    h2d_s, d2h_s = torch.cuda.Stream(device=cx.dev), torch.cuda.Stream(device=cx.dev)
+    planes = [pool.planes[i * pool.plane_b:(i + 1) * pool.plane_b] for i in range(layers)]
+
+    def e2e_step():
+        keep = []
+        for i in range(layers):
+            with torch.cuda.stream(h2d_s):
+                x_stage[i].copy_(x_host[i], non_blocking=True)
+                ev = torch.cuda.Event()
+                ev.record(h2d_s)
+            with torch.cuda.stream(cx.stream):
+                cx.stream.wait_event(ev)
+                a, c = lowbit_kernel.prepare_acts(x_stage[i], pool.act_mode, False)
+                y = lowbit_kernel.gemm_prepared(planes[i], rows, K, a, c, pool.op, B.OUT_F16_SCALED, B.LAYOUT_MN, pool.alphas[i], 0)
+                ev2 = torch.cuda.Event()
+                ev2.record(cx.stream)
+            with torch.cuda.stream(d2h_s):
+                d2h_s.wait_event(ev2)
+                out_host[i].copy_(y, non_blocking=True)
+                y.record_stream(d2h_s)
+            keep.append((a, c, y))
+        return keep
+
+    steps = max(3, min(args.steps, 10))
+    for _ in range(2):
+        e2e_step()
+    cx.barrier()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        e2e_step()
+    d2h_s.synchronize(); cx.stream.synchronize(); h2d_s.synchronize()
+    wall_ms = cx.max_over_ranks((time.perf_counter() - t0) * 1e3)
+    cx.barrier()
+    ok = True
+    if 0 in pool.host:
+        ok = bool(torch.equal(out_host[0], pool.expect(0, B.OUT_F16_SCALED, B.LAYOUT_MN)))
+    return {"value": ops_layer * layers * steps / (wall_ms * 1e-3) / 1e12, "unit": UNIT, "h2d_bytes_per_step": layers * N * K,
+            "d2h_bytes_per_step": layers * rows * N * 2, "steps": steps, "ms_per_step": wall_ms / steps, "verified": ok, "activations": "int8 (ternary values) from pinned host memory",
+            "api": "lowbit_kernel.prepare_acts + gemm_prepared per layer on 3 streams: int8 activations host -> device, fp16 [rows_r, N] slab device -> host, weights resident (prepacked)"}
+
+
+# ---- the 4096 x 4096 x 128 pool of the earlier rounds (one replica per rank) ---------------------------------------------
+def run_c2_pool(cx: Ctx, args):
+    B = cx.B
+    M, K, N = C2["M"], C2["K"], C2["N"]
+    layers = max(8, -(-int(1.5 * L2_BYTES) // B.plane_bytes(M, K)))
+    pool = Pool(cx, M, K, N, "bwta", layers, seed=1002 + cx.rank, keep_host=(0, -1))
+    xs16 = pool.x8.to(torch.float16)
+    outs = torch.empty((layers, N, M), dtype=torch.float16, device=cx.dev)
+
+    def full_step():
+        pool.prepare_all(xs16)
+        pool.gemm_batched(outs, B.OUT_F16_SCALED, B.LAYOUT_NM)
+
+    def gemm_all():
+        pool.gemm_batched(outs, B.OUT_F16_SCALED, B.LAYOUT_NM)
+
+    def per_call():
+        for i in range(layers):
+            pool.gemm_layer(i, outs[i], B.OUT_F16_SCALED, B.LAYOUT_NM)
+
+    with torch.cuda.stream(cx.stream):
+        full_step()
+    cx.stream.synchronize()
+    verified = all(check_equal(outs[i], pool.expect(i, B.OUT_F16_SCALED, B.LAYOUT_NM), f"c2 pool layer {i} (batched launch)") for i in sorted(pool.host))
+    outs.zero_()
+    with torch.cuda.stream(cx.stream):
+        per_call()
+    cx.stream.synchronize()
+    verified = all(check_equal(outs[i], pool.expect(i, B.OUT_F16_SCALED, B.LAYOUT_NM), f"c2 pool layer {i} (one call per layer)") for i in sorted(pool.host)) and verified
+    g_full, g_gemm, g_call = cx.graph_of(full_step), cx.graph_of(gemm_all), cx.graph_of(per_call)
+    steps = max(10, args.steps)
+    ms_full = cx.timed(g_full.replay, steps, args.warmup)
+    ms_gemm = cx.timed(g_gemm.replay, steps, args.warmup)
+    ms_call = cx.timed(g_call.replay, max(3, steps // 5), 3)
+    ops = pool.ops()
+    i8_peak, src = int8_peak(cx.peaks, ms_full + ms_gemm, None)
+    launch_us = ms_gemm * 1e3 / steps
+    call_us = ms_call * 1e3 / (max(3, steps // 5) * layers)
+    tops = ops * layers / (launch_us * 1e-6) / 1e12
+    call_tops = ops / (call_us * 1e-6) / 1e12
+    return {"verified": verified, "layers_per_step": layers, "value": ops * layers * cx.world * steps / (ms_full * 1e-3) / 1e12,
+            "ms_per_step": ms_full / steps, "what": "one batched prepare_acts launch (fp16 in) + one batched GEMM launch over the pool; one replica per rank",
+            "batched_launch": {"launch_us": launch_us, "kernel_tops": tops, "frac": tops / i8_peak, "frac_vs_i8_microbench": tops / I8_MICROBENCH_TOPS,
+                               "peak": i8_peak, "peak_source": src, "traffic": NCU_TRAFFIC["c2_pool_per_layer"] * layers,
+                               "bytes_alg_per_launch": pool.bytes_alg() * layers, "kernel": "gemm_persist_kernel<128>"},
+            "per_call": {"us": call_us, "tops": call_tops, "frac": call_tops / i8_peak, "gbs": pool.bytes_alg() / (call_us * 1e-6) / 1e9,
+                         "split_k": B.lib.bgemm_gemm_auto_split_k(M, N, K, 1),
+                         "what": "config 2 as written: ONE bgemm_gemm call per 4096x4096x128 layer, CUDA graph cycling over the pool"}}
+
+
+# ---- every other configuration, one call per layer (N = 1 only) ---------------------------------------------------------------
+def sweep_entry(cx: Ctx, name, pool: Pool, out_kind, layout, steps=20, kernel=""):
+    B = cx.B
+    shape = (pool.N, pool.rows) if layout == B.LAYOUT_NM else (pool.rows, pool.N)
+    outs = torch.empty((pool.layers,) + shape, dtype=torch.int32 if out_kind == B.OUT_I32 else torch.float16, device=cx.dev)
+
+    def calls():
+        for i in range(pool.layers):
+            pool.gemm_layer(i, outs[i], out_kind, layout)
+
+    with torch.cuda.stream(cx.stream):
+        pool.prepare_all()
+        calls()
+    cx.stream.synchronize()
+    ok = all(check_equal(outs[i], pool.expect(i, out_kind, layout), f"sweep {name} layer {i}") for i in sorted(pool.host))
+    g = cx.graph_of(calls)
+    ms = cx.timed(g.replay, steps, 3)
+    us = ms * 1e3 / (steps * pool.layers)
+    i8_peak, _ = int8_peak(cx.peaks, ms, None)
+    bf = bound_and_frac(pool.ops(), pool.bytes_alg(), us, cx.peaks, i8_peak)
+    return {"name": name, "M": pool.rows, "K": pool.K, "N": pool.N, "op": pool.op_name, "us": us, "tops": bf["tops"], "gbs": bf["gbs"],
+            "bytes_alg": pool.bytes_alg(), "bound": bf["bound"], "frac": bf["frac"], "verified": ok, "layers_in_pool": pool.layers, "kernel": kernel}
+
+
+def run_sweep(cx: Ctx):
+    import bgemm_linear as L
+    import lowbit_kernel
+    import oracle as O
+
+    B = cx.B
+    out = []
+    # C1: {-1,+1} x {-1,+1}, fp16 out
+    layers = max(8, -(-int(1.5 * L2_BYTES) // B.plane_bytes(4096, 4096)))
+    out.append(sweep_entry(cx, "c1", Pool(cx, 4096, 4096, 64, "xor", layers, 1001), B.OUT_F16, B.LAYOUT_NM, kernel="gemm_kernel<64>, K split in a cluster"))
+    torch.cuda.empty_cache()
+    # C5 at every N (the planes are the same pool; activations differ)
+    layers5 = max(4, -(-int(1.5 * L2_BYTES) // B.plane_bytes(28672, 8192)))
+    for n in (1, 4, 16, 128, 4096):
+        kern = "gemm_skinny_kernel (CUDA cores)" if n <= 4 else "gemm_kernel (tcgen05)"
+        out.append(sweep_entry(cx, f"c5n{n}", Pool(cx, 28672, 8192, n, "bwta", layers5, 1005), B.OUT_F16_SCALED, B.LAYOUT_NM,
+                               steps=20 if n <= 128 else 5, kernel=kern))
+        torch.cuda.empty_cache()
+
+    # C3: 384 heads x (A[512,512] {0,1}, V[512,64] +-1), int32 out; 3 distinct sets so that a pass exceeds L2
+    H, S, d, sets = 384, 512, 64, 3
+    g = torch.Generator(device=cx.dev)
+    g.manual_seed(1003)
+    attn = torch.randint(0, 2, (sets, H, S, S), generator=g, device=cx.dev, dtype=torch.int8).to(torch.float16) * 2 - 1      # "1" = sign bit clear
+    v = (torch.randint(0, 2, (sets, H, S, d), generator=g, device=cx.dev, dtype=torch.int8) * 2 - 1).to(torch.float16)
+    planes = [B.pack_weights(attn[i], B.WBIT_NONNEGATIVE)[0] for i in range(sets)]
+    prepared = [B.prepare_acts(v[i], B.ACT_SIGN, transpose=True) for i in range(sets)]
+    outs3 = torch.empty((sets, H, S, d), dtype=torch.int32, device=cx.dev)
+
+    def c3_prepared():
+        with torch.cuda.stream(cx.stream):
+            for i in range(sets):
+                B.gemm(planes[i], S, S, prepared[i][0], prepared[i][1], B.OP_ATTN, B.OUT_I32, B.LAYOUT_MN, out=outs3[i])
+
+    def c3_from_fp16():
+        with torch.cuda.stream(cx.stream):
+            for i in range(sets):
+                lowbit_kernel.bgemm_attn_matmul_batched(attn[i], v[i], True)
+
+    c3_prepared()
+    cx.stream.synchronize()
+    want3 = O.ref_attn_heads(((attn[0, :8].cpu() + 1) / 2), v[0, :8].cpu())
+    ok3 = check_equal(outs3[0, :8], want3, "sweep c3 heads 0-7")
+    g3 = cx.graph_of(c3_prepared)
+    us3 = cx.timed(g3.replay, 20, 3) * 1e3 / (20 * sets)
+    for _ in range(2):
+        c3_from_fp16()
+    us3f = cx.timed(c3_from_fp16, 10, 2) * 1e3 / (10 * sets)
+    b_bits, b_f16 = H * (S * S // 8 + S * d + 4 * d + 4 * S * d), H * (2 * S * S + 2 * S * d + 4 * S * d)
+    ops3 = 2.0 * H * S * S * d
+    out.append({"name": "c3_prepared", "heads": H, "S": S, "d": d, "us": us3, "tops": ops3 / us3 / 1e6, "gbs": b_bits / us3 / 1e3, "bytes_alg": b_bits,
+                "bound": "hbm", "frac": b_bits / us3 / 1e3 / cx.peaks["hbm_gbs"], "verified": ok3, "kernel": "gemm_persist_kernel<64>, one batched launch"})
+    out.append({"name": "c3_from_fp16", "heads": H, "S": S, "d": d, "us": us3f, "tops": ops3 / us3f / 1e6, "gbs": b_f16 / us3f / 1e3, "bytes_alg": b_f16,
+                "bound": "hbm", "frac": b_f16 / us3f / 1e3 / cx.peaks["hbm_gbs"], "verified": ok3,
+                "kernel": "pack_weights + prepare_acts_t + gemm_persist_kernel<64> (lowbit_kernel.bgemm_attn_matmul_batched, eager)"})
+    del attn, v, planes, prepared, outs3
+    torch.cuda.empty_cache()
+
+    # C4: MLP 1024 -> 4096 -> 4096 -> 10 at batch 256: a pool of independent MLPs (distinct weights) so that a pass exceeds L2
+    cfg = O.config4()
+    want4, _ = O.ref_mlp(cfg["ws"], cfg["x"])
+    n_mlp = 48
+    mlps = []
+    g.manual_seed(1004)
+    for i in range(n_mlp):
+        ws = cfg["ws"] if i == 0 else [(0.02 * torch.randn(w.shape, generator=g, device=cx.dev)).to(torch.float16) for w in cfg["ws"]]
+        mlps.append(L.BinaryMLP([w.to(cx.dev) for w in ws]))
+    for layer, w in zip(mlps[0].layers, cfg["ws"]):
+        layer.alpha.copy_(torch.from_numpy(O.c_rowmeanabs_f16(w).copy()).to(cx.dev))
+    x4 = cfg["x"].to(cx.dev)
+
+    def c4_all():
+        with torch.cuda.stream(cx.stream):
+            return [m(x4) for m in mlps]
+
+    ys = c4_all()
+    cx.stream.synchronize()
+    ok4 = check_equal(ys[0], want4, "sweep c4 logits")
+    us4e = cx.timed(c4_all, 5, 2) * 1e3 / (5 * n_mlp)
+    g4 = cx.graph_of(c4_all)
+    us4g = cx.timed(g4.replay, 10, 3) * 1e3 / (10 * n_mlp)
+    ops4 = 2.0 * 256 * (1024 * 4096 + 4096 * 4096 + 4096 * 10)
+    b4 = sum(B.plane_bytes(w.shape[0], w.shape[1]) + 2 * w.shape[0] for w in cfg["ws"]) + 256 * 1024 * 2 + 256 * 10 * 2 + 2 * 256 * 4096
+    for nm, us in (("c4_graph", us4g), ("c4_eager", us4e)):
+        out.append({"name": nm, "dims": "1024-4096-4096-10", "batch": 256, "us": us, "tops": ops4 / us / 1e6, "gbs": b4 / us / 1e3, "bytes_alg": b4,
+                    "bound": "latency", "frac": None, "verified": ok4, "mlps_in_pool": n_mlp,
+                    "kernel": "prepare_acts + 3 x gemm_kernel (fused next-layer activations), 4 launches per MLP"})
+    return out
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--layers", type=int, default=0, help="layers in the headline pool (0 = enough that the packed planes exceed L2 on every GPU)")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-sweep", action="store_true")
+    ap.add_argument("--no-c2-pool", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+
+    if args.impl == "reference":
+        run_reference_arm(args)
+        return
+
+    cx = Ctx()
+    sampler = ClockSampler(cx.local_rank)      # started early: NVML start-up takes longer than a short timed region
+    if cx.rank == 0:
+        sampler.start()
+    head = run_head(cx, args, sampler)
+    torch.cuda.empty_cache()
+    c2 = None if args.no_c2_pool else run_c2_pool(cx, args)
+    torch.cuda.empty_cache()
+    sweep = None
+    if cx.world == 1 and not args.no_sweep:
+        sweep = run_sweep(cx)
+    status = cx.B.lib.bgemm_device_status(1)
+    assert status == 0, f"a bounded wait inside a kernel ran out (device status {status}): results invalid"
 
     cpu = None
-    if rank == 0 and not args.no_cpu_baseline:
-        v, n, dt = time_cpu_baseline(M, K, N, op_name)
+    if cx.rank == 0 and not args.no_cpu_baseline:
+        v, n, dt = time_cpu(HEAD["M"], HEAD["K"], HEAD["N"], HEAD["op"], warm_s=1.0, budget_s=12.0, min_layers=2)
         cpu = {"value": v, "unit": UNIT, "cores": torch.get_num_threads(), "kind": "port",
                "sample": f"{n} layer(s) of the same shape in {dt:.1f} s: torch fp32 matmul on mapped CPU tensors + scale + fp16 cast"}
 
-    if rank == 0:
+    verified = bool(head["verified"]) and (c2 is None or c2["verified"]) and (sweep is None or all(e["verified"] for e in sweep)) \
+        and (head["gather"] is None or head["gather"].get("verified", True)) and (head["e2e"] is None or head["e2e"]["verified"])
+    if cx.world > 1:
+        t = torch.tensor([1 if verified else 0], device=cx.dev)
+        cx.dist.all_reduce(t, op=cx.dist.ReduceOp.MIN)
+        verified = bool(t.item())
+    if cx.rank == 0:
+        if head["roofline"] is not None and c2 is not None:
+            head["roofline"]["per_call"] = c2["per_call"]
         line = {
-            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
-            "ms_per_step": ms_full / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-            "dtype": "u8 x s8 -> s32 (fp16 scaled out)", "data": "synthetic",
-            "config": {"workload": desc, "M_per_gpu": M, "K": K, "N": N, "layers_per_step": layers,
-                       "l2": f"weight pool {layers * plane_b / 2**20:.0f} MiB per GPU > 126 MB L2, every layer has its own plane",
-                       "split_k": split_k or B.lib.bgemm_gemm_auto_split_k(M, N, K, layers), "sharding": f"rows x{world}, no collective",
-                       "timed": "CUDA graph of one batched prepare_acts launch + one batched gemm launch over the pool"},
-            "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "clocks": clocks, "per_layer_launch": per_layer,
-            "gpu_launches": int(launches_per_step) * args.steps,
+            "metric": METRIC, "value": head["value"], "unit": UNIT, "n_gpus": cx.world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": head["ms_per_step"], "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": "u8 x s8 -> s32 (fp16 scaled out)", "data": "synthetic", "verified": verified,
+            "config": {"workload": HEAD["desc"], "M": HEAD["M"], "K": HEAD["K"], "N": HEAD["N"], "rows_per_gpu": head["rows"],
+                       "layers_per_step": head["layers"],
+                       "l2": f"packed planes {head['plane_mib']:.0f} MiB per GPU > 126 MB L2, every layer has its own plane and activations",
+                       "sharding": f"output rows split over {cx.world} GPU(s), activations replicated, no collective in `value`",
+                       "timed": "CUDA graph: one batched prepare_acts launch (int8 ternary in) + one bgemm_gemm launch per layer"},
+            "roofline": head["roofline"], "gemm_only": head["gemm_only"], "gather": head["gather"], "cpu_baseline": cpu, "e2e": head["e2e"],
+            "clocks": head["clocks"], "c2_pool": c2, "extra": {"sweep": sweep},
+            "gpu_launches": head["launches_per_step"] * args.steps,
         }
         print(json.dumps(line), flush=True)
-    if world > 1:
-        dist.destroy_process_group()
+    if cx.world > 1:
+        cx.dist.destroy_process_group()
+    if not verified:
+        sys.exit(3)
 
 
 if __name__ == "__main__":
