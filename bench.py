@@ -298,13 +298,14 @@ class Pool:
         B = self.cx.B
         n1 = self.N if n1 is None else n1
         a_off = i * self.act_row + n0 * B.act_ld(self.K)
-        B.check(B.lib.bgemm_gemm((stream or self.cx.stream).cuda_stream, self.planes.data_ptr() + i * self.plane_b, self.rows, self.K,
+        # weights were prepacked and synchronised at set-up: the static-weights promise holds
+        B.check(B.lib.bgemm_gemm_static_weights((stream or self.cx.stream).cuda_stream, self.planes.data_ptr() + i * self.plane_b, self.rows, self.K,
                                  self.acts.data_ptr() + a_off, self.colsum.data_ptr() + 4 * (i * self.N + n0), n1 - n0, self.op, out.data_ptr(),
                                  out_kind, layout, self.alphas.data_ptr() + 2 * i * self.rows, 0, None, 0, 1), "gemm")
 
     def gemm_batched(self, outs, out_kind, layout):
         B = self.cx.B
-        B.check(B.lib.bgemm_gemm(self.cx.stream.cuda_stream, self.planes.data_ptr(), self.rows, self.K, self.acts.data_ptr(), self.colsum.data_ptr(),
+        B.check(B.lib.bgemm_gemm_static_weights(self.cx.stream.cuda_stream, self.planes.data_ptr(), self.rows, self.K, self.acts.data_ptr(), self.colsum.data_ptr(),
                                  self.N, self.op, outs.data_ptr(), out_kind, layout, self.alphas.data_ptr(), 0, None, 0, self.layers), "gemm")
 
     # ---- oracle ---------------------------------------------------------------------------------------------------
@@ -500,7 +501,7 @@ def run_head_e2e(cx: Ctx, args, pool: Pool, layers, rows, ops_layer):
             with torch.cuda.stream(cx.stream):
                 cx.stream.wait_event(ev)
                 a, c = lowbit_kernel.prepare_acts(x_stage[i], pool.act_mode, False)
-                y = lowbit_kernel.gemm_prepared(planes[i], rows, K, a, c, pool.op, B.OUT_F16_SCALED, B.LAYOUT_MN, pool.alphas[i], 0)
+                y = lowbit_kernel.gemm_prepared(planes[i], rows, K, a, c, pool.op, B.OUT_F16_SCALED, B.LAYOUT_MN, pool.alphas[i], 0, True)
                 ev2 = torch.cuda.Event()
                 ev2.record(cx.stream)
             with torch.cuda.stream(d2h_s):
@@ -615,8 +616,8 @@ def run_sweep(cx: Ctx):
     torch.cuda.empty_cache()
     # C5 at every N (the planes are the same pool; activations differ)
     layers5 = max(4, -(-int(1.5 * L2_BYTES) // B.plane_bytes(28672, 8192)))
-    for n in (1, 4, 16, 128, 4096):
-        kern = "gemm_skinny_kernel (CUDA cores)" if n <= 4 else "gemm_kernel (tcgen05)"
+    for n in (1, 2, 4, 8, 16, 128, 4096):
+        kern = "gemm_stream_kernel (mma.sync int8 from registers)" if n <= 16 else "gemm_kernel (tcgen05)"
         out.append(sweep_entry(cx, f"c5n{n}", Pool(cx, 28672, 8192, n, "bwta", layers5, 1005), B.OUT_F16_SCALED, B.LAYOUT_NM,
                                steps=20 if n <= 128 else 5, kernel=kern))
         torch.cuda.empty_cache()

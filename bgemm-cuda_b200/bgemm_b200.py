@@ -47,6 +47,7 @@ lib.bgemm_pack_weights.argtypes = [_vp, _vp, _int, _i64, _i64, _i64, _int, _vp, 
 lib.bgemm_pack_weights_host.argtypes = [_vp, _int, _i64, _i64, _i64, _int, _vp, _vp, _vp]
 lib.bgemm_prepare_acts.argtypes = [_vp, _vp, _int, _i64, _i64, _i64, _int, _int, _vp, _vp, _i64, _i64]
 lib.bgemm_gemm.argtypes = [_vp, _vp, _i64, _i64, _vp, _vp, _i64, _int, _vp, _int, _int, _vp, _int, _vp, _sz, _i64]
+lib.bgemm_gemm_static_weights.argtypes = lib.bgemm_gemm.argtypes
 lib.bgemm_gemm_to_acts.argtypes = [_vp, _vp, _i64, _i64, _vp, _vp, _i64, _int, _vp, _int, _vp, _vp, _int, _vp, _sz, _i64]
 lib.bgemm_gemm_workspace_bytes.restype = _sz
 lib.bgemm_gemm_workspace_bytes.argtypes = [_i64, _i64, _i64, _int, _i64]
@@ -165,8 +166,10 @@ def workspace(device: torch.device, nbytes: int) -> torch.Tensor:
 
 def gemm(plane: torch.Tensor, M: int, K: int, acts: torch.Tensor, colsum: torch.Tensor, op: int, out_kind: int = OUT_I32,
          out_layout: int = LAYOUT_NM, alpha: torch.Tensor | None = None, split_k: int = 0, out: torch.Tensor | None = None,
-         ws: torch.Tensor | None = None):
-    """GEMM on prepared operands. acts: int8 [N, ld] or [B, N, ld]; returns [N, M] / [M, N] (with leading B if batched)."""
+         ws: torch.Tensor | None = None, static_weights: bool = False):
+    """GEMM on prepared operands. acts: int8 [N, ld] or [B, N, ld]; returns [N, M] / [M, N] (with leading B if batched).
+    static_weights=True calls bgemm_gemm_static_weights: the caller promises that `plane` was complete before the
+    previous kernel on the current stream was launched."""
     _require_cuda(plane, acts, colsum, alpha)
     batched = acts.dim() == 3
     B = acts.shape[0] if batched else 1
@@ -181,8 +184,9 @@ def gemm(plane: torch.Tensor, M: int, K: int, acts: torch.Tensor, colsum: torch.
     if need and ws is None:
         ws = workspace(acts.device, need)
     with torch.cuda.device(acts.device):
-        check(lib.bgemm_gemm(_stream(), plane.data_ptr(), M, K, acts.data_ptr(), colsum.data_ptr(), N, op, out.data_ptr(), out_kind,
-                             out_layout, _ptr(alpha), split_k, _ptr(ws) if need else None, ws.numel() if need else 0, B), "bgemm_gemm")
+        fn = lib.bgemm_gemm_static_weights if static_weights else lib.bgemm_gemm
+        check(fn(_stream(), plane.data_ptr(), M, K, acts.data_ptr(), colsum.data_ptr(), N, op, out.data_ptr(), out_kind,
+                 out_layout, _ptr(alpha), split_k, _ptr(ws) if need else None, ws.numel() if need else 0, B), "bgemm_gemm")
     return out
 
 

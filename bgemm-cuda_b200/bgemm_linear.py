@@ -359,6 +359,9 @@ class BinaryLinear(nn.Module):
         assert weight.is_cuda and weight.dim() == 2
         self.out_features, self.in_features = weight.shape
         self.register_buffer("packed", lowbit_kernel.binary_weight_prepacking_bundle_cuda(weight, 0))
+        # The weights never change after this point: once the prepack has finished, forward calls may promise the
+        # kernels "static weights" (they then fetch weights while the previous kernel of the stream still runs).
+        torch.cuda.current_stream(weight.device).synchronize()
         self.ternary = ternary
         self._views = None
         if alpha is not None:
@@ -391,7 +394,7 @@ class BinaryLinear(nn.Module):
         lead = x.shape[:-1]
         out = lowbit_kernel.bgemm_linear_forward_packed(
             x.reshape(-1, self.in_features), self.plane, self.out_features, self.in_features, self.alpha, 0,
-            BWTA if self.ternary else XOR_POP, _OUT_F16_SCALED)
+            BWTA if self.ternary else XOR_POP, _OUT_F16_SCALED, True)
         return out.reshape(*lead, self.out_features)
 
     @property
@@ -411,7 +414,7 @@ class BinaryLinear(nn.Module):
         activations inside the GEMM epilogue (no fp16 round trip) and (acts, colsum) is returned; else fp16 [N, out]."""
         if next_layer is None:
             return lowbit_kernel.gemm_prepared(self.plane, self.out_features, self.in_features, acts, colsum, self.op, _OUT_F16_SCALED, 0,
-                                               self.alpha, 0)
+                                               self.alpha, 0, True)
         assert next_layer.in_features == self.out_features
         return lowbit_kernel.gemm_prepared_to_acts(self.plane, self.out_features, self.in_features, acts, colsum, self.op,
                                                    next_layer.act_mode, self.alpha, 0)

@@ -242,9 +242,9 @@ size_t bgemm_gemm_workspace_bytes(int64_t M, int64_t N, int64_t K, int split_k, 
     return counter_bytes(tiles) + (size_t)tiles * (size_t)s * (size_t)NT * 128 * 4;
 }
 
-int bgemm_gemm(void* stream, const void* plane, int64_t M, int64_t K, const int8_t* acts, const int32_t* colsum, int64_t N, int op,
-               void* out, int out_kind, int out_layout, const void* alpha, int split_k, void* workspace, size_t workspace_bytes,
-               int64_t batch) {
+static int gemm_entry(void* stream, const void* plane, int64_t M, int64_t K, const int8_t* acts, const int32_t* colsum, int64_t N, int op,
+                      void* out, int out_kind, int out_layout, const void* alpha, int split_k, void* workspace, size_t workspace_bytes,
+                      int64_t batch, int weights_static) {
     if (!plane || !acts || !colsum || !out) return BGEMM_ERR_NULL;
     if (op < BGEMM_OP_AND || op > BGEMM_OP_W1A8 || out_kind < BGEMM_OUT_I32 || out_kind > BGEMM_OUT_F16_SCALED ||
         out_layout < BGEMM_LAYOUT_NM || out_layout > BGEMM_LAYOUT_MN)
@@ -278,6 +278,7 @@ int bgemm_gemm(void* stream, const void* plane, int64_t M, int64_t K, const int8
     p.split_k = s;
     p.epi = (op == BGEMM_OP_XOR || op == BGEMM_OP_BWTA || op == BGEMM_OP_W1A8) ? 1 : 0;
     p.acts_general = op == BGEMM_OP_W1A8 ? 1 : 0;
+    p.weights_static = weights_static;
     p.out_kind = out_kind;
     p.out_layout = out_layout;
     p.plane_batch_bytes = (long long)bgemm_plane_bytes(M, K);
@@ -292,6 +293,18 @@ int bgemm_gemm(void* stream, const void* plane, int64_t M, int64_t K, const int8
         p.ws_partial = reinterpret_cast<int32_t*>(static_cast<char*>(workspace) + counter_bytes(tiles));
     }
     return launch_gemm((cudaStream_t)stream, p, acts, bgemm_act_ld(K), batch);
+}
+
+int bgemm_gemm(void* stream, const void* plane, int64_t M, int64_t K, const int8_t* acts, const int32_t* colsum, int64_t N, int op,
+               void* out, int out_kind, int out_layout, const void* alpha, int split_k, void* workspace, size_t workspace_bytes,
+               int64_t batch) {
+    return gemm_entry(stream, plane, M, K, acts, colsum, N, op, out, out_kind, out_layout, alpha, split_k, workspace, workspace_bytes, batch, 0);
+}
+
+int bgemm_gemm_static_weights(void* stream, const void* plane, int64_t M, int64_t K, const int8_t* acts, const int32_t* colsum, int64_t N,
+                              int op, void* out, int out_kind, int out_layout, const void* alpha, int split_k, void* workspace,
+                              size_t workspace_bytes, int64_t batch) {
+    return gemm_entry(stream, plane, M, K, acts, colsum, N, op, out, out_kind, out_layout, alpha, split_k, workspace, workspace_bytes, batch, 1);
 }
 
 int bgemm_gemm_to_acts(void* stream, const void* plane, int64_t M, int64_t K, const int8_t* acts, const int32_t* colsum, int64_t N, int op,

@@ -134,7 +134,7 @@ constexpr int kSkinnyPiece = 8 * 1024;             // columns staged per pass an
 // time and owns the contiguous range of groups [groups * b / gridDim.x, groups * (b + 1) / gridDim.x).
 template <int NN, int D, int W>
 __global__ void __launch_bounds__(32 * W) gemm_skinny_kernel(const GemmParams p, const int8_t* __restrict__ acts, long long act_ld,
-                                                                     int groups, int ks) {
+                                                                     int groups, int ks, int weights_static) {
     constexpr int T = 32 * W;                    // threads of the CTA
     constexpr bool STAGE = NN <= 2;              // whole int8 activations stay in shared memory (they feed the dp4a path)
     grid_launch_dependents();
@@ -157,7 +157,6 @@ __global__ void __launch_bounds__(32 * W) gemm_skinny_kernel(const GemmParams p,
     const int g_begin = (int)(((long long)groups * blockIdx.x) / gridDim.x);
     const int g_end = (int)(((long long)groups * (blockIdx.x + 1)) / gridDim.x);
     if (tid < 8) s_pn[tid] = 0;
-    grid_dependency_wait();
     const int8_t* src = acts + (size_t)batch * p.N * act_ld;
     const uint8_t* plane = p.plane + (size_t)batch * p.plane_batch_bytes;
 
@@ -181,6 +180,20 @@ __global__ void __launch_bounds__(32 * W) gemm_skinny_kernel(const GemmParams p,
         }
         cp_async_commit();
     };
+    int gc = g_begin + team, kc = kb0;           // unit being computed
+    int gl = gc, kl = kc;                        // next unit to load
+    const uint8_t* wl = unit_ptr(gl, kl);        // where unit (gl, kl) lives
+    auto next_load = [&]() {                     // (gl, kl, wl) -> the following unit
+        wl += 4096;
+        if (++kl >= kb1) { kl = kb0; gl += gs; wl = unit_ptr(gl, kl); }
+    };
+    // With the caller's promise that the plane was complete before the previous kernel of the stream was launched
+    // (bgemm_gemm_static_weights) the ring is filled ahead of the dependency wait, i.e. while that kernel still runs.
+    if (weights_static) {
+#pragma unroll 1
+        for (int d = 0; d < D; d++) { issue(d, gl < g_end, wl); next_load(); }
+    }
+    grid_dependency_wait();
     // The (small) activation loads go first: issued behind two thirds of the weight traffic they would come back last
     // and hold up the whole CTA.
     auto load_x = [&](int i, int base, int chunks) {
@@ -194,15 +207,10 @@ __global__ void __launch_bounds__(32 * W) gemm_skinny_kernel(const GemmParams p,
         const int i = tid + r * T;
         xv[r] = i < NN * (piece / 16) ? load_x(i, 0, piece / 16) : make_uint4(0u, 0u, 0u, 0u);
     }
-    int gc = g_begin + team, kc = kb0;           // unit being computed
-    int gl = gc, kl = kc;                        // next unit to load
-    const uint8_t* wl = unit_ptr(gl, kl);        // where unit (gl, kl) lives
-    auto next_load = [&]() {                     // (gl, kl, wl) -> the following unit
-        wl += 4096;
-        if (++kl >= kb1) { kl = kb0; gl += gs; wl = unit_ptr(gl, kl); }
-    };
+    if (!weights_static) {
 #pragma unroll 1
-    for (int d = 0; d < D; d++) { issue(d, gl < g_end, wl); next_load(); }
+        for (int d = 0; d < D; d++) { issue(d, gl < g_end, wl); next_load(); }
+    }
 
     // ---- activations: int8 -> shared memory piece by piece (coalesced), checked for values outside {-1, 0, +1}, and
     //      turned into bit planes in the weight plane's bit order. Rows beyond N and columns beyond K become zero.
@@ -392,7 +400,7 @@ static int launch_skinny_variant(cudaStream_t stream, const GemmParams& p, const
         cfg.attrs = attr;
         cfg.numAttrs = 1;
     }
-    const cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_skinny_kernel<NN, D, W>, p, acts, act_ld, (int)groups, ks);
+    const cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_skinny_kernel<NN, D, W>, p, acts, act_ld, (int)groups, ks, p.weights_static);
     count_launch();
     return (int)(e != cudaSuccess ? e : cudaGetLastError());
 }

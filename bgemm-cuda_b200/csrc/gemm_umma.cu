@@ -515,8 +515,14 @@ int gemm_tile_n(long long N) {
 }
 
 int launch_gemm(cudaStream_t stream, GemmParams p, const int8_t* acts, long long act_ld, long long batch) {
-    // A handful of activation rows: pure weight streaming, served by the CUDA-core kernel (no tensor-memory set-up,
-    // no 16-column tile, no cluster reduction).
+    // Up to 16 activation rows: pure weight streaming (no tensor-memory set-up, no 128-row tile, no cluster reduction).
+    // A single row of ternary activations goes to the CUDA-core popcount kernel (28672 x 8192: 10.2 us against 11.6),
+    // everything else to the register-fed mma.sync kernel (N = 2 / 4 / 8 / 16: 11.7 / 11.8 / 12.1 / 17.5 us against
+    // 12.3 / 15.3 / 19.8 / 19.9 for the kernels behind it), which falls back to the former where it does not apply.
+    // BGEMM_STREAM_MIN_N / BGEMM_STREAM_MAX_N / BGEMM_SKINNY_MAX_N move the limits.
+    const bool single_ternary_row = p.N == 1 && p.epi && !p.acts_general && stream_min_n() <= 1;
+    if (single_ternary_row && skinny_supported(p, batch, true)) return launch_gemm_skinny(stream, p, acts, act_ld, batch);
+    if (stream_supported(p, batch)) return launch_gemm_stream(stream, p, acts, act_ld, batch, p.weights_static != 0);
     if (skinny_supported(p, batch, !p.acts_general)) return launch_gemm_skinny(stream, p, acts, act_ld, batch);
     EncodeTiledFn encode = get_encode_fn();
     if (!encode) return BGEMM_ERR_DRIVER;

@@ -34,6 +34,8 @@ struct GemmParams {
     long long out_ld;
     int act_mode;
     int acts_general;             // 1: the caller declared general int8 activations (op W1A8); 0: at most ternary expected
+    int weights_static;           // 1: the caller promised that the plane was complete before the previous kernel of the stream was
+                                  // launched (bgemm_gemm_static_weights): weight-streaming kernels may fetch it before the dependency wait
     // Test hooks (bgemm_debug_set_wait_test): budget of every bounded wait in SM clocks (0 = the default) and the
     // K block (CTA-relative stream position) whose weight tile the producer withholds (-1 = none).
     long long wait_budget;
@@ -58,6 +60,11 @@ int launch_gemm(cudaStream_t stream, GemmParams p, const int8_t* acts, long long
 bool persistent_supported(int NT);
 bool persistent_kblocks_ok(int NT, int kblocks);   // K-block counts per tile the issuers' hand-over protocol covers
 int launch_gemm_persistent(cudaStream_t stream, const void* tensor_map, const GemmParams& p, int NT, long long total_tiles, int ctas);
+
+// Weight-streaming kernel for N <= 16 on mma.sync int8 (gemm_stream.cu).
+bool stream_supported(const GemmParams& p, long long batch);
+int stream_min_n();               // smallest N the kernel takes (1 unless BGEMM_STREAM_MIN_N says otherwise)
+int launch_gemm_stream(cudaStream_t stream, const GemmParams& p, const int8_t* acts, long long act_ld, long long batch, bool weights_static);
 
 // Weight-streaming CUDA-core kernel for N <= 8 (gemm_skinny.cu).
 bool skinny_supported(const GemmParams& p, long long batch, bool ternary_acts_expected);

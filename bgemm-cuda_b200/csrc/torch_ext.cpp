@@ -199,8 +199,10 @@ std::vector<torch::Tensor> prepare_acts(torch::Tensor x, int64_t act_mode, bool 
 }
 
 // GEMM on prepared operands (see bgemm_gemm). out_kind: 0 int32, 1 fp16, 2 fp16 scaled by alpha[m].
+// static_weights: the caller promises that `plane` was complete before the previous kernel of the current stream was launched
+// (see bgemm_gemm_static_weights).
 torch::Tensor gemm_prepared(torch::Tensor plane, int64_t M, int64_t K, torch::Tensor acts, torch::Tensor colsum, int64_t op,
-                            int64_t out_kind, int64_t out_layout, c10::optional<torch::Tensor> alpha, int64_t splitK) {
+                            int64_t out_kind, int64_t out_layout, c10::optional<torch::Tensor> alpha, int64_t splitK, bool static_weights) {
     TORCH_CHECK(plane.is_cuda() && acts.is_cuda() && colsum.is_cuda(), "gemm_prepared: CUDA tensors required");
     TORCH_CHECK(acts.is_contiguous() && colsum.is_contiguous() && plane.is_contiguous(), "gemm_prepared: contiguous tensors required");
     TORCH_CHECK(acts.scalar_type() == at::kChar && colsum.scalar_type() == at::kInt, "gemm_prepared: acts int8 / colsum int32 required");
@@ -222,8 +224,10 @@ torch::Tensor gemm_prepared(torch::Tensor plane, int64_t M, int64_t K, torch::Te
     const size_t need = bgemm_gemm_workspace_bytes(M, N, K, (int)splitK, B);
     torch::Tensor ws;
     if (need) ws = workspace(acts.device(), need, true);
-    check(bgemm_gemm(stream_of(acts), plane.data_ptr(), M, K, acts.data_ptr<int8_t>(), colsum.data_ptr<int>(), N, (int)op, out.data_ptr(),
-                     (int)out_kind, (int)out_layout, alpha_ptr, (int)splitK, need ? ws.data_ptr() : nullptr, need ? (size_t)ws.numel() : 0, B),
+    check((static_weights ? bgemm_gemm_static_weights : bgemm_gemm)(stream_of(acts), plane.data_ptr(), M, K, acts.data_ptr<int8_t>(),
+                                                                     colsum.data_ptr<int>(), N, (int)op, out.data_ptr(), (int)out_kind, (int)out_layout,
+                                                                     alpha_ptr, (int)splitK, need ? ws.data_ptr() : nullptr,
+                                                                     need ? (size_t)ws.numel() : 0, B),
           "bgemm_gemm");
     return out;
 }
@@ -264,15 +268,15 @@ std::vector<torch::Tensor> gemm_prepared_to_acts(torch::Tensor plane, int64_t M,
 // x [N, K] unpacked x prepacked weights -> [N, M]. INSTR as in the reference; out_kind 1 = fp16, 0 = int32,
 // 2 = fp16 scaled by alpha (required then).
 torch::Tensor bgemm_linear_forward_packed(torch::Tensor x, torch::Tensor plane, int64_t M, int64_t K, c10::optional<torch::Tensor> alpha,
-                                          int64_t splitK, int64_t INSTR, int64_t out_kind) {
+                                          int64_t splitK, int64_t INSTR, int64_t out_kind, bool static_weights) {
     TORCH_CHECK(x.dim() == 2 && x.size(1) == K, "bgemm_linear_forward_packed: x must be [N, K]");
     auto prep = prepare_acts(x, act_mode_of((int)INSTR), false);
-    return gemm_prepared(plane, M, K, prep[0], prep[1], INSTR, out_kind, BGEMM_LAYOUT_NM, alpha, splitK);
+    return gemm_prepared(plane, M, K, prep[0], prep[1], INSTR, out_kind, BGEMM_LAYOUT_NM, alpha, splitK, static_weights);
 }
 
 // Binary weight x ternary activation with the per-channel scale fused: fp16 [N, M] = sign(x) . sign(w)^T * alpha.
 torch::Tensor bwta_linear_forward_cuda(torch::Tensor x, torch::Tensor plane, int64_t M, int64_t K, torch::Tensor alpha, int64_t splitK) {
-    return bgemm_linear_forward_packed(x, plane, M, K, alpha, splitK, BGEMM_OP_BWTA, BGEMM_OUT_F16_SCALED);
+    return bgemm_linear_forward_packed(x, plane, M, K, alpha, splitK, BGEMM_OP_BWTA, BGEMM_OUT_F16_SCALED, false);
 }
 
 // Batched {0,1} x {-1,+1} attention product: attn [B, Sq, Sk] ("1" = sign bit clear, as the reference
@@ -283,7 +287,7 @@ torch::Tensor bgemm_attn_matmul_batched(torch::Tensor attn, torch::Tensor value,
     const int64_t Sq = attn.size(1), Sk = attn.size(2);
     auto plane = binary_weight_prepacking_cuda(attn, BGEMM_WBIT_NONNEGATIVE);
     auto prep = prepare_acts(value, BGEMM_ACT_SIGN, true);
-    return gemm_prepared(plane, Sq, Sk, prep[0], prep[1], BGEMM_OP_ATTN, exact ? BGEMM_OUT_I32 : BGEMM_OUT_F16, BGEMM_LAYOUT_MN, c10::nullopt, 0);
+    return gemm_prepared(plane, Sq, Sk, prep[0], prep[1], BGEMM_OP_ATTN, exact ? BGEMM_OUT_I32 : BGEMM_OUT_F16, BGEMM_LAYOUT_MN, c10::nullopt, 0, false);
 }
 
 torch::Tensor fp6_not_provided(py::args, py::kwargs) {
@@ -308,12 +312,13 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
           py::arg("transpose") = false);
     m.def("gemm_prepared", &gemm_prepared, "GEMM on prepared operands.", py::arg("plane"), py::arg("M"), py::arg("K"), py::arg("acts"),
           py::arg("colsum"), py::arg("op"), py::arg("out_kind") = 0, py::arg("out_layout") = 0, py::arg("alpha") = py::none(),
-          py::arg("splitK") = 0);
+          py::arg("splitK") = 0, py::arg("static_weights") = false);
     m.def("gemm_prepared_to_acts", &gemm_prepared_to_acts, "GEMM whose result becomes the next layer's prepared activations.", py::arg("plane"),
           py::arg("M"), py::arg("K"), py::arg("acts"), py::arg("colsum"), py::arg("op"), py::arg("next_act_mode"), py::arg("alpha") = py::none(),
           py::arg("splitK") = 0);
     m.def("bgemm_linear_forward_packed", &bgemm_linear_forward_packed, "x x prepacked weights.", py::arg("x"), py::arg("plane"), py::arg("M"),
-          py::arg("K"), py::arg("alpha") = py::none(), py::arg("splitK") = 0, py::arg("INSTR") = 1, py::arg("out_kind") = 1);
+          py::arg("K"), py::arg("alpha") = py::none(), py::arg("splitK") = 0, py::arg("INSTR") = 1, py::arg("out_kind") = 1,
+          py::arg("static_weights") = false);
     m.def("bwta_linear_forward_cuda", &bwta_linear_forward_cuda, "Binary weight x ternary activation, scaled.", py::arg("x"), py::arg("plane"),
           py::arg("M"), py::arg("K"), py::arg("alpha"), py::arg("splitK") = 0);
     m.def("bgemm_attn_matmul_batched", &bgemm_attn_matmul_batched, "Batched {0,1} x {-1,+1} matmul.", py::arg("attn"), py::arg("value"),

@@ -164,8 +164,9 @@ int bgemm_prepare_acts(void* stream, const void* src, int src_dtype, int64_t N, 
  *   acts      int8 [N, bgemm_act_ld(K)] and colsum int32 [N] (bgemm_prepare_acts with the mode of `op`)
  *   out       BGEMM_LAYOUT_NM: [N, M]; BGEMM_LAYOUT_MN: [M, N]; element type per out_kind
  *   alpha     fp16 [M], required for BGEMM_OUT_F16_SCALED, else may be NULL
- *   N <= 4    (N <= 2 for ops AND / ATTN / W1A8) is served by a weight-streaming kernel on the CUDA cores, for which
- *             split_k and workspace have no meaning (they are validated and ignored); results are the same bits.
+ *   N <= 16   is served by a weight-streaming kernel (register-fed mma.sync int8; any op, any int8 activations, K <= 65536
+ *             and activations that fit in shared memory beside the weight ring), for which split_k and workspace have no
+ *             meaning (they are validated and ignored); results are the same bits.
  *   split_k   >= 1 forces that many K partitions, 0 lets the library choose (at most 8). Up to 8 partitions
  *             are reduced on chip (thread-block cluster + distributed shared memory) and need no workspace.
  *   workspace needed only when split_k > 8: bgemm_gemm_workspace_bytes() bytes, 256-byte aligned.
@@ -180,6 +181,20 @@ int bgemm_gemm(void* stream, const void* plane, int64_t M, int64_t K,
                int op, void* out, int out_kind, int out_layout, const void* alpha,
                int split_k, void* workspace, size_t workspace_bytes, int64_t batch);
 size_t bgemm_gemm_workspace_bytes(int64_t M, int64_t N, int64_t K, int split_k, int64_t batch);
+
+/* bgemm_gemm with one promise added by the caller: `plane` was complete in device memory BEFORE the kernel that precedes
+ * this call on `stream` was launched -- the normal case for inference, where weights are prepacked when the model is
+ * loaded (synchronise once after packing). The library launches its kernels so that a kernel may start while its
+ * predecessor on the stream is still finishing and waits, inside the kernel, before it touches anything the predecessor
+ * may have produced; with this promise the weight-streaming kernels (N <= 16) fetch the first weights ahead of that
+ * wait, which hides launch and memory latency behind the previous kernel's tail in back-to-back decode loops.
+ * Activations, column sums, scales and the output carry no such promise and are touched after the wait. Without the
+ * promise (plane written by the preceding kernels of the stream) use bgemm_gemm. Same arguments, same results.
+ * The reference has no counterpart (one stream-0 launch per call, fp6_linear.cu:593).                              */
+int bgemm_gemm_static_weights(void* stream, const void* plane, int64_t M, int64_t K,
+                              const int8_t* acts, const int32_t* colsum, int64_t N,
+                              int op, void* out, int out_kind, int out_layout, const void* alpha,
+                              int split_k, void* workspace, size_t workspace_bytes, int64_t batch);
 
 /* The same GEMM with a fused activation producer: the result is not stored, it becomes the NEXT layer's prepared
  * activations. next_acts int8 [N, bgemm_act_ld(M)] (this GEMM's M is the next layer's K) receives
