@@ -453,9 +453,42 @@ def run_gather(cx: Ctx, args, pool: Pool, outs, layers, rows, ops_layer):
                     dist.all_gather_into_tensor(full_blk[c][i], outs_nm[i, nb[c]:nb[c + 1]])
         cx.stream.wait_stream(comm)
 
+    # fused: every rank's GEMM epilogue stores its [N, rows_r] slab straight into every rank's full [N, M] result through
+    # peer-mapped (symmetric) memory -- ordinary global stores over NVLink, no TMA, no multicast -- and a cross-rank
+    # barrier on the stream follows. One symmetric buffer per layer of the pool.
+    fused, fused_err = None, None
+    try:
+        import torch.distributed._symmetric_memory as symm
+
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+        full_sym = symm.empty((layers, N, M), dtype=torch.float16, device=cx.dev)
+        hdl = symm.rendezvous(full_sym, cx.dist.group.WORLD)
+        order = [cx.rank] + [q for q in range(cx.world) if q != cx.rank]
+        row0 = pool.row0
+        ptrs = [[int(hdl.buffer_ptrs[q]) + 2 * (i * N * M + row0) for q in order] for i in range(layers)]
+
+        def step_fused():
+            pool.prepare_all()
+            hdl.barrier(channel=0)                  # nobody still reads the previous step's results
+            for i in range(layers):
+                a_off = i * pool.act_row
+                arr = (__import__("ctypes").c_void_p * len(ptrs[i]))(*ptrs[i])
+                B.check(B.lib.bgemm_gemm_multi_out(cx.stream.cuda_stream, pool.planes.data_ptr() + i * pool.plane_b, rows, pool.K,
+                                                   pool.acts.data_ptr() + a_off, pool.colsum.data_ptr() + 4 * i * N, N, pool.op, arr, len(ptrs[i]), M,
+                                                   B.OUT_F16_SCALED, B.LAYOUT_NM, pool.alphas.data_ptr() + 2 * i * rows, 0, None, 0, 1), "gemm_multi_out")
+            hdl.barrier(channel=1)                  # every slab has landed on every rank
+        fused = step_fused
+    except Exception as exc:                        # symmetric memory unavailable on this box: report, keep the NCCL numbers
+        fused_err = repr(exc)[:300]
+
     with torch.cuda.stream(cx.stream):
         step_plain()
         step_overlap()
+        if fused:
+            try:
+                fused()
+            except Exception as exc:
+                fused, fused_err = None, repr(exc)[:300]
     torch.cuda.synchronize()
     ok = True
     if cx.rank == 0:                      # one gathered layer against the oracle (all rows), outside the timed region
@@ -469,11 +502,15 @@ def run_gather(cx: Ctx, args, pool: Pool, outs, layers, rows, ops_layer):
         ok = check_equal(full[0], want.t(), "gathered layer 0 (plain all-gather)")
         blk = torch.cat([full_blk[c][0] for c in range(chunks)], dim=1)                     # [world, N, rows]
         ok = check_equal(blk.permute(1, 0, 2).reshape(N, M), want, "gathered layer 0 (chunked, overlapped)") and ok
+        if fused:
+            ok = check_equal(full_sym[0], want, "gathered layer 0 (fused into the GEMM epilogue)") and ok
     ms_plain = cx.timed(step_plain, steps, 2)
     ms_over = cx.timed(step_overlap, steps, 2)
+    ms_fused = cx.timed(fused, steps, 2) if fused else None
     per = lambda ms: {"value": ops_layer * layers * steps / (ms * 1e-3) / 1e12, "ms_per_step": ms / steps, "us_per_layer": ms * 1e3 / (steps * layers)}
     return {"verified": ok, "bytes_received_per_gpu_per_layer": 2 * N * (M - rows),
-            "nccl_all_gather_after_gemm": per(ms_plain), "nccl_all_gather_overlapped_4_chunks": per(ms_over), "steps": steps,
+            "nccl_all_gather_after_gemm": per(ms_plain), "nccl_all_gather_overlapped_4_chunks": per(ms_over),
+            "fused_peer_stores_in_epilogue": (per(ms_fused) if ms_fused else {"unavailable": fused_err}), "steps": steps,
             "what": "eager launches (no CUDA graph): GEMM per layer, then torch.distributed.all_gather_into_tensor of the fp16 slabs"}
 
 

@@ -48,6 +48,7 @@ lib.bgemm_pack_weights_host.argtypes = [_vp, _int, _i64, _i64, _i64, _int, _vp, 
 lib.bgemm_prepare_acts.argtypes = [_vp, _vp, _int, _i64, _i64, _i64, _int, _int, _vp, _vp, _i64, _i64]
 lib.bgemm_gemm.argtypes = [_vp, _vp, _i64, _i64, _vp, _vp, _i64, _int, _vp, _int, _int, _vp, _int, _vp, _sz, _i64]
 lib.bgemm_gemm_static_weights.argtypes = lib.bgemm_gemm.argtypes
+lib.bgemm_gemm_multi_out.argtypes = [_vp, _vp, _i64, _i64, _vp, _vp, _i64, _int, _vp, _int, _i64, _int, _int, _vp, _int, _vp, _sz, _int]
 lib.bgemm_gemm_to_acts.argtypes = [_vp, _vp, _i64, _i64, _vp, _vp, _i64, _int, _vp, _int, _vp, _vp, _int, _vp, _sz, _i64]
 lib.bgemm_gemm_workspace_bytes.restype = _sz
 lib.bgemm_gemm_workspace_bytes.argtypes = [_i64, _i64, _i64, _int, _i64]
@@ -188,6 +189,24 @@ def gemm(plane: torch.Tensor, M: int, K: int, acts: torch.Tensor, colsum: torch.
         check(fn(_stream(), plane.data_ptr(), M, K, acts.data_ptr(), colsum.data_ptr(), N, op, out.data_ptr(), out_kind,
                  out_layout, _ptr(alpha), split_k, _ptr(ws) if need else None, ws.numel() if need else 0, B), "bgemm_gemm")
     return out
+
+
+def gemm_multi_out(plane: torch.Tensor, M: int, K: int, acts: torch.Tensor, colsum: torch.Tensor, op: int, out_ptrs, out_ld: int,
+                   out_kind: int = OUT_F16, out_layout: int = LAYOUT_NM, alpha: torch.Tensor | None = None, split_k: int = 0,
+                   static_weights: bool = False, ws: torch.Tensor | None = None) -> None:
+    """GEMM whose result is stored once at every address in `out_ptrs` (ints: device pointers, local or peer-mapped),
+    inside matrices of row pitch `out_ld` elements: a row shard writing its slab into every rank's full result."""
+    _require_cuda(plane, acts, colsum, alpha)
+    assert acts.dim() == 2 and acts.shape[-1] == act_ld(K) and acts.is_contiguous() and colsum.is_contiguous()
+    N = acts.shape[0]
+    ptrs = (ctypes.c_void_p * len(out_ptrs))(*[int(p) for p in out_ptrs])
+    need = lib.bgemm_gemm_workspace_bytes(M, N, K, split_k, 1)
+    if need and ws is None:
+        ws = workspace(acts.device, need)
+    with torch.cuda.device(acts.device):
+        check(lib.bgemm_gemm_multi_out(_stream(), plane.data_ptr(), M, K, acts.data_ptr(), colsum.data_ptr(), N, op, ptrs, len(out_ptrs), out_ld,
+                                       out_kind, out_layout, _ptr(alpha), split_k, _ptr(ws) if need else None, ws.numel() if need else 0,
+                                       1 if static_weights else 0), "bgemm_gemm_multi_out")
 
 
 def gemm_to_acts(plane: torch.Tensor, M: int, K: int, acts: torch.Tensor, colsum: torch.Tensor, op: int, next_act_mode: int,

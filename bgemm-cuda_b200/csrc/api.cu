@@ -244,8 +244,11 @@ size_t bgemm_gemm_workspace_bytes(int64_t M, int64_t N, int64_t K, int split_k, 
 
 static int gemm_entry(void* stream, const void* plane, int64_t M, int64_t K, const int8_t* acts, const int32_t* colsum, int64_t N, int op,
                       void* out, int out_kind, int out_layout, const void* alpha, int split_k, void* workspace, size_t workspace_bytes,
-                      int64_t batch, int weights_static) {
+                      int64_t batch, int weights_static, void* const* more_outs = nullptr, int n_more = 0, int64_t out_ld = 0) {
     if (!plane || !acts || !colsum || !out) return BGEMM_ERR_NULL;
+    if (n_more < 0 || n_more > 7 || (n_more > 0 && !more_outs)) return BGEMM_ERR_SHAPE;
+    for (int i = 0; i < n_more; i++)
+        if (!more_outs[i]) return BGEMM_ERR_NULL;
     if (op < BGEMM_OP_AND || op > BGEMM_OP_W1A8 || out_kind < BGEMM_OUT_I32 || out_kind > BGEMM_OUT_F16_SCALED ||
         out_layout < BGEMM_LAYOUT_NM || out_layout > BGEMM_LAYOUT_MN)
         return BGEMM_ERR_ENUM;
@@ -255,6 +258,11 @@ static int gemm_entry(void* stream, const void* plane, int64_t M, int64_t K, con
         return BGEMM_ERR_SHAPE;
     if (!aligned(plane, 16) || !aligned(acts, 16) || !aligned(colsum, 4) || !aligned(out, out_kind == BGEMM_OUT_I32 ? 4 : 2))
         return BGEMM_ERR_ALIGN;
+    for (int i = 0; i < n_more; i++)
+        if (!aligned(more_outs[i], out_kind == BGEMM_OUT_I32 ? 4 : 2)) return BGEMM_ERR_ALIGN;
+    const int64_t ld_default = out_layout == BGEMM_LAYOUT_NM ? M : N;
+    if (out_ld == 0) out_ld = ld_default;
+    if (out_ld < ld_default || out_ld > (int64_t)1 << 40 || (out_ld != ld_default && batch != 1)) return BGEMM_ERR_SHAPE;
     // Tiles of 16 and 32 columns keep bit j of a weight byte at value 2^j and shift the sums down afterwards: with
     // general int8 activations accumulator 7 holds up to 128 * 128 * K, which leaves int32 beyond K = 65536.
     if (op == BGEMM_OP_W1A8 && N <= 32 && K > kMaxKGeneralNarrow) return BGEMM_ERR_UNSUPPORTED;
@@ -279,6 +287,9 @@ static int gemm_entry(void* stream, const void* plane, int64_t M, int64_t K, con
     p.epi = (op == BGEMM_OP_XOR || op == BGEMM_OP_BWTA || op == BGEMM_OP_W1A8) ? 1 : 0;
     p.acts_general = op == BGEMM_OP_W1A8 ? 1 : 0;
     p.weights_static = weights_static;
+    p.ldo = out_ld;
+    p.n_out_more = n_more;
+    for (int i = 0; i < n_more; i++) p.out_more[i] = more_outs[i];
     p.out_kind = out_kind;
     p.out_layout = out_layout;
     p.plane_batch_bytes = (long long)bgemm_plane_bytes(M, K);
@@ -305,6 +316,14 @@ int bgemm_gemm_static_weights(void* stream, const void* plane, int64_t M, int64_
                               int op, void* out, int out_kind, int out_layout, const void* alpha, int split_k, void* workspace,
                               size_t workspace_bytes, int64_t batch) {
     return gemm_entry(stream, plane, M, K, acts, colsum, N, op, out, out_kind, out_layout, alpha, split_k, workspace, workspace_bytes, batch, 1);
+}
+
+int bgemm_gemm_multi_out(void* stream, const void* plane, int64_t M, int64_t K, const int8_t* acts, const int32_t* colsum, int64_t N, int op,
+                         void* const* outs_host, int n_outs, int64_t out_ld, int out_kind, int out_layout, const void* alpha, int split_k,
+                         void* workspace, size_t workspace_bytes, int weights_static) {
+    if (!outs_host || n_outs < 1 || n_outs > 8) return outs_host ? BGEMM_ERR_SHAPE : BGEMM_ERR_NULL;
+    return gemm_entry(stream, plane, M, K, acts, colsum, N, op, outs_host[0], out_kind, out_layout, alpha, split_k, workspace, workspace_bytes, 1,
+                      weights_static ? 1 : 0, outs_host + 1, n_outs - 1, out_ld);
 }
 
 int bgemm_gemm_to_acts(void* stream, const void* plane, int64_t M, int64_t K, const int8_t* acts, const int32_t* colsum, int64_t N, int op,
@@ -352,6 +371,7 @@ int bgemm_gemm_to_acts(void* stream, const void* plane, int64_t M, int64_t K, co
     p.epi = (op == BGEMM_OP_XOR || op == BGEMM_OP_BWTA) ? 1 : 0;
     p.out_kind = kOutActs;
     p.out_layout = BGEMM_LAYOUT_NM;
+    p.ldo = M;
     p.plane_batch_bytes = (long long)bgemm_plane_bytes(M, K);
     p.cluster = (s > 1 && s <= kMaxClusterSplit) ? 1 : 0;
     p.colsum_next = next_colsum;

@@ -418,6 +418,8 @@ static int skinny_max_n() {
 
 bool skinny_supported(const GemmParams& p, long long batch, bool ternary_acts_expected) {
     if (p.N > skinny_max_n() || p.out_kind == kOutActs || batch > 65535) return false;
+    // this kernel writes one result with the default pitch only
+    if (p.n_out_more > 0 || p.ldo != (p.out_layout == BGEMM_LAYOUT_NM ? p.M : p.N)) return false;
     // N = 3..8 pays only on the popc path: ops of the form colsum - 2 D whose activations are ternary by contract
     if (p.N > 2 && !(p.epi && ternary_acts_expected)) return false;
     const int NN = p.N <= 1 ? 1 : (p.N <= 2 ? 2 : (p.N <= 4 ? 4 : 8));

@@ -228,9 +228,13 @@ __global__ void __launch_bounds__(32 * W, W <= 8 ? 2 : 1) gemm_stream_kernel(con
                     sums[i] = 0;
                     if (n < p.N && m < p.M) {
                         const int val = p.epi ? colsum_s[n] - 2 * d : d;
-                        const size_t idx = (size_t)batch * p.M * p.N + (p.out_layout == BGEMM_LAYOUT_NM ? (size_t)n * p.M + m : (size_t)m * p.N + n);
-                        if (p.out_kind == BGEMM_OUT_I32) reinterpret_cast<int*>(p.out)[idx] = val;
-                        else reinterpret_cast<__half*>(p.out)[idx] = __float2half_rn((float)val * scale_s[gl * 32 + row]);
+                        const size_t idx = (size_t)batch * p.M * p.N + (p.out_layout == BGEMM_LAYOUT_NM ? (size_t)n * p.ldo + m : (size_t)m * p.ldo + n);
+                        const __half hv = __float2half_rn((float)val * scale_s[gl * 32 + row]);
+                        for (int dst = 0; dst <= p.n_out_more; dst++) {       // further destinations: peer-mapped copies of the result
+                            void* o = dst == 0 ? p.out : p.out_more[dst - 1];
+                            if (p.out_kind == BGEMM_OUT_I32) reinterpret_cast<int*>(o)[idx] = val;
+                            else reinterpret_cast<__half*>(o)[idx] = hv;
+                        }
                     }
                 }
             }

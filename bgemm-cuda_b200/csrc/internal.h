@@ -34,6 +34,12 @@ struct GemmParams {
     long long out_ld;
     int act_mode;
     int acts_general;             // 1: the caller declared general int8 activations (op W1A8); 0: at most ternary expected
+    // Output addressing: the row pitch of the result matrix in elements ([N, M] layout: M unless the slab is written into
+    // a wider matrix; [M, N] layout: N) and up to 7 further destinations that receive the same result (peer-mapped
+    // buffers of other GPUs: the all-gather of a row-sharded layer fused into the epilogue). Batches need the default pitch.
+    long long ldo;
+    void* out_more[7];
+    int n_out_more;
     int weights_static;           // 1: the caller promised that the plane was complete before the previous kernel of the stream was
                                   // launched (bgemm_gemm_static_weights): weight-streaming kernels may fetch it before the dependency wait
     // Test hooks (bgemm_debug_set_wait_test): budget of every bounded wait in SM clocks (0 = the default) and the

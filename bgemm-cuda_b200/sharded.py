@@ -110,5 +110,66 @@ def make_gpu_shard(weight_rows: torch.Tensor, op: int, alpha_rows: Optional[torc
     return compute
 
 
+class FusedGatherRows:
+    """Row-sharded layer whose all-gather is fused into the GEMM epilogue (GPUs of one node, NVLink / NVSwitch).
+
+    Every rank owns a full [N_max, M] fp16 result buffer in symmetric memory (torch.distributed._symmetric_memory:
+    device memory that every rank of the group maps, used here for allocation and address exchange only). Rank r's
+    GEMM stores its [N, rows_r] slab at column start_r of EVERY rank's buffer (bgemm_gemm_multi_out: ordinary 16-byte
+    global stores from the epilogue, remote ones over NVLink, no TMA, no multicast), a cross-rank barrier on the stream
+    follows, and `forward` returns this rank's buffer, which now holds the whole [N, M] result. The transfer overlaps the
+    tensor-core work tile by tile instead of following it as a separate collective.
+
+    Successive calls reuse the buffer: the caller must be done with the previous result before the next forward
+    (the leading barrier of `forward` makes sure no peer overwrites a result another rank is still reading only
+    together with that rule).
+    """
+
+    def __init__(self, weight_rows_of: Callable[[int, int], torch.Tensor], M: int, K: int, n_max: int, op: int,
+                 alpha: Optional[torch.Tensor], group: Optional[dist.ProcessGroup] = None):
+        import os
+
+        import bgemm_b200 as B
+        import torch.distributed._symmetric_memory as symm
+
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")      # plain peer mappings only
+        self.B, self.M, self.K, self.op, self.n_max = B, M, K, op, n_max
+        self.group = group if group is not None else dist.group.WORLD
+        self.world_size, self.rank = dist.get_world_size(self.group), dist.get_rank(self.group)
+        self.shards = row_shards(M, self.world_size)
+        self.start, self.end = self.shards[self.rank]
+        w = weight_rows_of(self.start, self.end)                             # this rank's rows [rows_r, K]
+        dev = w.device
+        self.plane, _, _ = B.pack_weights(w, B.WBIT_OF_OP[op])
+        self.alpha = None if alpha is None else alpha[self.start:self.end].to(torch.float16).contiguous()
+        self.full = symm.empty((n_max, M), dtype=torch.float16, device=dev)
+        self.handle = symm.rendezvous(self.full, self.group)
+        # destination q = rank q's buffer + this rank's first column; the local one first
+        order = [self.rank] + [q for q in range(self.world_size) if q != self.rank]
+        self.out_ptrs = [int(self.handle.buffer_ptrs[q]) + 2 * self.start for q in order]
+        torch.cuda.current_stream(dev).synchronize()                         # weights are static from here on
+
+    @property
+    def rows_local(self) -> int:
+        return self.end - self.start
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        B = self.B
+        N = x.shape[0]
+        assert N <= self.n_max
+        acts, colsum = B.prepare_acts(x, B.ACT_MODE_OF_OP[self.op])
+        return self.forward_prepared(acts, colsum)
+
+    def forward_prepared(self, acts: torch.Tensor, colsum: torch.Tensor) -> torch.Tensor:
+        B = self.B
+        N = acts.shape[0]
+        self.handle.barrier(channel=0)            # every rank is done reading the previous result
+        if self.rows_local > 0:
+            B.gemm_multi_out(self.plane, self.rows_local, self.K, acts, colsum, self.op, self.out_ptrs, self.M,
+                             B.OUT_F16_SCALED if self.alpha is not None else B.OUT_F16, B.LAYOUT_NM, self.alpha, 0, static_weights=True)
+        self.handle.barrier(channel=1)            # every rank's slab has landed everywhere
+        return self.full[:N]
+
+
 def shard_sizes(shards: Sequence[tuple[int, int]]) -> list[int]:
     return [e - s for s, e in shards]

@@ -196,6 +196,21 @@ int bgemm_gemm_static_weights(void* stream, const void* plane, int64_t M, int64_
                               int op, void* out, int out_kind, int out_layout, const void* alpha,
                               int split_k, void* workspace, size_t workspace_bytes, int64_t batch);
 
+/* The GEMM with its result stored `n_outs` (1..8) times, once at every address of the HOST array `outs_host` (device
+ * pointers; the array itself is read during the call only), inside a matrix of row pitch `out_ld` elements
+ * ([N, M] layout: out_ld >= M, 0 = M; [M, N] layout: out_ld >= N, 0 = N). This is the all-gather of a row-sharded layer
+ * fused into the GEMM epilogue: rank r computes rows [start_r, end_r) of a layer with M_total rows and passes, for every
+ * rank q, the peer-mapped address of q's full [N, M_total] result plus start_r elements, with out_ld = M_total; every
+ * 16-byte piece of the slab then leaves the SM once per destination as an ordinary global store (remote ones travel
+ * over NVLink) while the tensor cores work on the next tile. No TMA and no multicast is involved. The caller makes
+ * the stores visible to the other ranks' later kernels the usual way (a cross-rank barrier after the launch).
+ * One problem per call (no batch). `weights_static` != 0 adds the promise of bgemm_gemm_static_weights.
+ * The reference has no multi-GPU path; this entry point has no counterpart there.                                  */
+int bgemm_gemm_multi_out(void* stream, const void* plane, int64_t M, int64_t K,
+                         const int8_t* acts, const int32_t* colsum, int64_t N, int op,
+                         void* const* outs_host, int n_outs, int64_t out_ld, int out_kind, int out_layout,
+                         const void* alpha, int split_k, void* workspace, size_t workspace_bytes, int weights_static);
+
 /* The same GEMM with a fused activation producer: the result is not stored, it becomes the NEXT layer's prepared
  * activations. next_acts int8 [N, bgemm_act_ld(M)] (this GEMM's M is the next layer's K) receives
  * act(fp16 result) under next_act_mode (BGEMM_ACT_*), where the fp16 result is rne(acc) or, with alpha != NULL,

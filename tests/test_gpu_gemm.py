@@ -420,6 +420,39 @@ def test_seeded_random_shapes(B):
     assert B.lib.bgemm_device_status(1) == 0
 
 
+@pytest.mark.parametrize("M,K,N,layout,kind", [(384, 1024, 200, 0, O.OUT_F16_SCALED), (300, 2048, 130, 1, O.OUT_I32), (512, 4096, 9, 0, O.OUT_F16_SCALED),
+                                                (256, 512, 64, 0, O.OUT_I32), (1000, 768, 1, 0, O.OUT_F16_SCALED), (128, 8192, 40, 1, O.OUT_F16)])
+def test_multi_destination_epilogue_with_pitch(B, M, K, N, layout, kind):
+    """bgemm_gemm_multi_out: the slab of a row shard written into three wider matrices at a column (row) offset -- the
+    fused all-gather of the row-sharded layer, here with all destinations on this GPU. Everything outside the slab
+    must stay untouched."""
+    g = O._gen(M + K + N)
+    w, x = O.rand_pm1((M, K), g), O.rand_ternary((N, K), g)
+    alpha = (0.01 + 0.09 * torch.rand(M, generator=g)).to(torch.float16)
+    want = O.ref_out(O.ref_acc(w, x, O.OP_BWTA), kind, alpha)                    # [N, M]
+    plane, _, _ = B.pack_weights(w.cuda(), B.WBIT_NEGATIVE)
+    acts, colsum = B.prepare_acts(x.cuda(), B.ACT_TERNARY)
+    dt = torch.int32 if kind == O.OUT_I32 else torch.float16
+    esz = 4 if kind == O.OUT_I32 else 2
+    if layout == 0:       # [N, M_total], this shard's columns start at `off`
+        total, off = M + 640, 256
+        bufs = [torch.full((N, total), -7, dtype=dt, device="cuda") for _ in range(3)]
+        ptrs = [b.data_ptr() + esz * off for b in bufs]
+        ref = torch.full((N, total), -7, dtype=dt)
+        ref[:, off:off + M] = want
+    else:                 # [M_total, N] with a wider row pitch, this shard's rows start at `off`
+        pitch, off = N + 24, 16
+        bufs = [torch.full((M + 32, pitch), -7, dtype=dt, device="cuda") for _ in range(3)]
+        ptrs = [b.data_ptr() + esz * off * pitch for b in bufs]
+        total = pitch
+        ref = torch.full((M + 32, pitch), -7, dtype=dt)
+        ref[off:off + M, :N] = want.t()
+    B.gemm_multi_out(plane, M, K, acts, colsum, B.OP_BWTA, ptrs, total, kind, layout, alpha.cuda() if kind == O.OUT_F16_SCALED else None)
+    for b in bufs:
+        assert torch.equal(b.cpu(), ref)
+    assert B.lib.bgemm_device_status(1) == 0
+
+
 def test_argument_errors(B):
     x = torch.zeros(4, 256, dtype=torch.float16, device="cuda")
     assert B.lib.bgemm_pack_weights(None, None, 0, 4, 256, 256, 0, x.data_ptr(), None, None, 1, 0) == -1
