@@ -28,6 +28,7 @@ captured in a CUDA graph. Strong scaling: the work per step is fixed, value = 2*
 from __future__ import annotations
 
 import argparse
+import ctypes
 import json
 import os
 import statistics
@@ -465,16 +466,15 @@ def run_gather(cx: Ctx, args, pool: Pool, outs, layers, rows, ops_layer):
         hdl = symm.rendezvous(full_sym, cx.dist.group.WORLD)
         order = [cx.rank] + [q for q in range(cx.world) if q != cx.rank]
         row0 = pool.row0
-        ptrs = [[int(hdl.buffer_ptrs[q]) + 2 * (i * N * M + row0) for q in order] for i in range(layers)]
+        ptrs = [(ctypes.c_void_p * cx.world)(*[int(hdl.buffer_ptrs[q]) + 2 * (i * N * M + row0) for q in order]) for i in range(layers)]
 
         def step_fused():
             pool.prepare_all()
             hdl.barrier(channel=0)                  # nobody still reads the previous step's results
             for i in range(layers):
                 a_off = i * pool.act_row
-                arr = (__import__("ctypes").c_void_p * len(ptrs[i]))(*ptrs[i])
                 B.check(B.lib.bgemm_gemm_multi_out(cx.stream.cuda_stream, pool.planes.data_ptr() + i * pool.plane_b, rows, pool.K,
-                                                   pool.acts.data_ptr() + a_off, pool.colsum.data_ptr() + 4 * i * N, N, pool.op, arr, len(ptrs[i]), M,
+                                                   pool.acts.data_ptr() + a_off, pool.colsum.data_ptr() + 4 * i * N, N, pool.op, ptrs[i], cx.world, M,
                                                    B.OUT_F16_SCALED, B.LAYOUT_NM, pool.alphas.data_ptr() + 2 * i * rows, 0, None, 0, 1), "gemm_multi_out")
             hdl.barrier(channel=1)                  # every slab has landed on every rank
         fused = step_fused

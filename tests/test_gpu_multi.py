@@ -35,7 +35,7 @@ def _worker(rank, world, port, M, K, Ns, result_dir):
         import bgemm_b200 as B
         from sharded import FusedGatherRows, ShardedRows, make_gpu_shard, row_shards
 
-        cfg = O.config5(M=M, K=K, N=max(Ns), seed=1005)                # same seed on every rank: replicated inputs
+        cfg = O.config5(M=M, K=K, N=max(Ns) + len(Ns), seed=1005)      # same seed on every rank: replicated inputs
         w, alpha = cfg["w"], cfg["alpha"]
         s, e = row_shards(M, world)[rank]
         plain = ShardedRows(M, make_gpu_shard(w[s:e].to(dev), B.OP_BWTA, alpha[s:e].to(dev), B.OUT_F16_SCALED))
