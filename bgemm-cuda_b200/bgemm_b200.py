@@ -26,7 +26,7 @@ DT_F16, DT_BF16, DT_F32, DT_I8 = 0, 1, 2, 3
 OP_AND, OP_XOR, OP_ATTN, OP_BWTA, OP_W1A8 = 0, 1, 2, 3, 4
 WBIT_NEGATIVE, WBIT_NONNEGATIVE, WBIT_NONZERO, WBIT_NEGATIVE_NZ = 0, 1, 2, 3
 ACT_SIGN, ACT_TERNARY, ACT_NEG01, ACT_INT8 = 0, 1, 2, 3
-OUT_I32, OUT_F16, OUT_F16_SCALED = 0, 1, 2
+OUT_I32, OUT_F16, OUT_F16_SCALED, OUT_F32 = 0, 1, 2, 3
 LAYOUT_NM, LAYOUT_MN = 0, 1
 ACT_MODE_OF_OP = {OP_AND: ACT_NEG01, OP_XOR: ACT_SIGN, OP_ATTN: ACT_SIGN, OP_BWTA: ACT_TERNARY, OP_W1A8: ACT_INT8}
 WBIT_OF_OP = {OP_AND: WBIT_NEGATIVE, OP_XOR: WBIT_NEGATIVE, OP_ATTN: WBIT_NONNEGATIVE, OP_BWTA: WBIT_NEGATIVE, OP_W1A8: WBIT_NEGATIVE}
@@ -49,6 +49,7 @@ lib.bgemm_prepare_acts.argtypes = [_vp, _vp, _int, _i64, _i64, _i64, _int, _int,
 lib.bgemm_gemm.argtypes = [_vp, _vp, _i64, _i64, _vp, _vp, _i64, _int, _vp, _int, _int, _vp, _int, _vp, _sz, _i64]
 lib.bgemm_gemm_static_weights.argtypes = lib.bgemm_gemm.argtypes
 lib.bgemm_gemm_multi_out.argtypes = [_vp, _vp, _i64, _i64, _vp, _vp, _i64, _int, _vp, _int, _i64, _int, _int, _vp, _int, _vp, _sz, _int]
+lib.bgemm_w1a16_gemm.argtypes = [_vp, _vp, _i64, _i64, _vp, _i64, _i64, _vp, _int, _int, _vp, _int]
 lib.bgemm_gemm_to_acts.argtypes = [_vp, _vp, _i64, _i64, _vp, _vp, _i64, _int, _vp, _int, _vp, _vp, _int, _vp, _sz, _i64]
 lib.bgemm_gemm_workspace_bytes.restype = _sz
 lib.bgemm_gemm_workspace_bytes.argtypes = [_i64, _i64, _i64, _int, _i64]
@@ -207,6 +208,21 @@ def gemm_multi_out(plane: torch.Tensor, M: int, K: int, acts: torch.Tensor, cols
         check(lib.bgemm_gemm_multi_out(_stream(), plane.data_ptr(), M, K, acts.data_ptr(), colsum.data_ptr(), N, op, ptrs, len(out_ptrs), out_ld,
                                        out_kind, out_layout, _ptr(alpha), split_k, _ptr(ws) if need else None, ws.numel() if need else 0,
                                        1 if static_weights else 0), "bgemm_gemm_multi_out")
+
+
+def w1a16_gemm(plane: torch.Tensor, M: int, K: int, x: torch.Tensor, out_kind: int = OUT_F32, out_layout: int = LAYOUT_NM,
+               alpha: torch.Tensor | None = None, static_weights: bool = False, out: torch.Tensor | None = None) -> torch.Tensor:
+    """Binary weight x fp16 activation: x fp16 [N, K] (unprepared) -> [N, M] / [M, N], fp32 or fp16, fp32 accumulation."""
+    _require_cuda(plane, x, alpha)
+    assert x.dim() == 2 and x.dtype == torch.float16 and x.shape[1] == K and x.stride(1) == 1
+    N = x.shape[0]
+    shape = (N, M) if out_layout == LAYOUT_NM else (M, N)
+    if out is None:
+        out = torch.empty(shape, dtype=torch.float32 if out_kind == OUT_F32 else torch.float16, device=x.device)
+    with torch.cuda.device(x.device):
+        check(lib.bgemm_w1a16_gemm(_stream(), plane.data_ptr(), M, K, x.data_ptr(), x.stride(0), N, out.data_ptr(), out_kind, out_layout,
+                                   _ptr(alpha), 1 if static_weights else 0), "bgemm_w1a16_gemm")
+    return out
 
 
 def gemm_to_acts(plane: torch.Tensor, M: int, K: int, acts: torch.Tensor, colsum: torch.Tensor, op: int, next_act_mode: int,

@@ -326,6 +326,39 @@ int bgemm_gemm_multi_out(void* stream, const void* plane, int64_t M, int64_t K, 
                       weights_static ? 1 : 0, outs_host + 1, n_outs - 1, out_ld);
 }
 
+int bgemm_w1a16_gemm(void* stream, const void* plane, int64_t M, int64_t K, const void* x_f16, int64_t x_ld, int64_t N, void* out, int out_kind,
+                     int out_layout, const void* alpha, int weights_static) {
+    if (!plane || !x_f16 || !out) return BGEMM_ERR_NULL;
+    if ((out_kind != BGEMM_OUT_F32 && out_kind != BGEMM_OUT_F16) || out_layout < BGEMM_LAYOUT_NM || out_layout > BGEMM_LAYOUT_MN) return BGEMM_ERR_ENUM;
+    if (M < 1 || N < 1 || K < 1 || M > kMaxDim || N > kMaxDim || K > kMaxDim || x_ld < K) return BGEMM_ERR_SHAPE;
+    if (!aligned(plane, 16) || !aligned(x_f16, 2) || !aligned(out, out_kind == BGEMM_OUT_F32 ? 4 : 2)) return BGEMM_ERR_ALIGN;
+    const int kblocks = (int)((K + 255) / 256);
+    const int rows = w1a16_rows_per_launch(kblocks);
+    if (rows < 1) return BGEMM_ERR_UNSUPPORTED;
+    const size_t esz = out_kind == BGEMM_OUT_F32 ? 4 : 2;
+    for (int64_t n0 = 0; n0 < N; n0 += rows) {
+        GemmParams p{};
+        p.plane = static_cast<const uint8_t*>(plane);
+        // rows n0.. of an [N, M] result start n0 * M elements in; columns n0.. of an [M, N] result start n0 elements in
+        p.out = static_cast<char*>(out) + esz * (size_t)(out_layout == BGEMM_LAYOUT_NM ? n0 * M : n0);
+        p.alpha = static_cast<const __half*>(alpha);
+        p.status = device_status_word();
+        apply_test_hooks(p);
+        p.M = (int)M; p.N = (int)(N - n0 < rows ? N - n0 : rows); p.K = (int)K;
+        p.kblocks = kblocks;
+        p.mtiles = (int)((M + 127) / 128);
+        p.split_k = 1;
+        p.out_kind = out_kind;
+        p.out_layout = out_layout;
+        p.ldo = out_layout == BGEMM_LAYOUT_NM ? M : N;
+        p.plane_batch_bytes = (long long)bgemm_plane_bytes(M, K);
+        p.weights_static = weights_static ? 1 : 0;
+        const int rc = launch_gemm_w1a16((cudaStream_t)stream, p, static_cast<const __half*>(x_f16) + (size_t)n0 * x_ld, x_ld);
+        if (rc) return rc;
+    }
+    return BGEMM_OK;
+}
+
 int bgemm_gemm_to_acts(void* stream, const void* plane, int64_t M, int64_t K, const int8_t* acts, const int32_t* colsum, int64_t N, int op,
                        const void* alpha, int next_act_mode, int8_t* next_acts, int32_t* next_colsum, int split_k, void* workspace,
                        size_t workspace_bytes, int64_t batch) {

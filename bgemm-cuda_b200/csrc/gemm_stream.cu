@@ -55,22 +55,39 @@ __device__ __forceinline__ void mma_u8s8(int (&d)[4], uint32_t a0, uint32_t a1, 
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
+// D (16 x 8, f32) += A (16 x 16, f16, row) * B (16 x 8, f16, col)
+__device__ __forceinline__ void mma_f16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+// Two weight bits of a packed word -> a pair of fp16 values -1.0 / +1.0 (bit set = negative). `shift` moves the bit of the
+// low half to bit 15; its partner sits 16 bits higher and lands on bit 31. One shift and one three-input logic operation.
+__device__ __forceinline__ uint32_t pm1_pair(uint32_t w, int shift) { return ((w << shift) & 0x80008000u) | 0x3C003C00u; }
+
 struct StreamArgs {
     const int8_t* acts;
     long long act_ld;
+    const __half* x16;       // fp16 activations [N, K] (binary weight x fp16 activation variant), row pitch x_ld elements
+    long long x_ld;
     int groups;              // 32-row groups of one problem (4 per row tile)
     int weights_static;      // fill the ring before the dependency wait
 };
 
 // Shared memory: [x rows: N x (Kpad + 16)] [ring: W x D x 1 KB] [sums: kGroupsPerPass x NPAD x 32 int] [row scales] [column sums] [mbarrier, flags]
-template <int NTILES, int W, int D>
+// F16: the activations are fp16 values (not prepared int8 rows) and the sums are fp32: weight bits become fp16 -1 / +1
+// pairs and meet the activations in mma.m16n8k16 (one column tile, N <= 8).
+template <int NTILES, int W, int D, bool F16 = false>
 __global__ void __launch_bounds__(32 * W, W <= 8 ? 2 : 1) gemm_stream_kernel(const GemmParams p, const StreamArgs a) {
+    static_assert(!F16 || NTILES == 1, "the fp16-activation variant has one column tile");
     constexpr int NPAD = 8 * NTILES;
-    constexpr bool POW2 = NTILES == 1;
+    constexpr bool POW2 = NTILES == 1 && !F16;
     constexpr int T = 32 * W;
     grid_launch_dependents();
     extern __shared__ __align__(128) uint8_t stream_smem[];
-    const int kpad = p.kblocks * 256, pitch = kpad + 16;
+    // activation rows in shared memory: int8 rows of pitch Kpad + 16 (ldmatrix rows of 16 bytes fall on distinct banks),
+    // fp16 rows of pitch 2 Kpad + 32 (the 8-byte loads of a half-warp fall on distinct banks)
+    const int kpad = p.kblocks * 256, pitch = F16 ? 2 * kpad + 32 : kpad + 16;
     uint8_t* xs = stream_smem;
     uint8_t* ring = xs + (((size_t)p.N * pitch + 127) & ~(size_t)127);
     int* sums = reinterpret_cast<int*>(ring + (size_t)W * D * 1024);
@@ -149,7 +166,29 @@ __global__ void __launch_bounds__(32 * W, W <= 8 ? 2 : 1) gemm_stream_kernel(con
 #pragma unroll 1
         for (int d = 0; d < D; d++) issue(ring_addr + d * 1024, cl);
     }
-    if (tid == 0) {                      // activations: one bulk copy per row into the padded rows of xs
+    if (F16) {
+        // fp16 activations: every group of four columns (e0, e1, e2, e3) is stored as (e0, e2, e1, e3), the order in which
+        // the weight bits of a packed word pair up (bits 16 apart); columns from K on are zero.
+        const bool vec = (reinterpret_cast<uintptr_t>(a.x16) & 15) == 0 && (a.x_ld & 7) == 0;
+        const int chunks = kpad / 8;
+        for (int i = tid; i < p.N * chunks; i += T) {
+            const int n = i / chunks, k0 = (i - n * chunks) * 8;
+            const __half* src = a.x16 + (size_t)n * a.x_ld + k0;
+            uint4 v;
+            if (vec && k0 + 8 <= p.K) {
+                v = *reinterpret_cast<const uint4*>(src);
+            } else {
+                __align__(16) __half e[8];
+#pragma unroll
+                for (int q = 0; q < 8; q++) e[q] = k0 + q < p.K ? src[q] : __ushort_as_half(0);
+                v = *reinterpret_cast<const uint4*>(e);
+            }
+            uint4 o;
+            o.x = __byte_perm(v.x, v.y, 0x5410); o.y = __byte_perm(v.x, v.y, 0x7632);
+            o.z = __byte_perm(v.z, v.w, 0x5410); o.w = __byte_perm(v.z, v.w, 0x7632);
+            *reinterpret_cast<uint4*>(xs + (size_t)n * pitch + (size_t)k0 * 2) = o;
+        }
+    } else if (tid == 0) {               // activations: one bulk copy per row into the padded rows of xs
         mbar_arrive_expect_tx(smem_u32(bar), (uint32_t)p.N * (uint32_t)kpad);
         const int8_t* src = a.acts + (size_t)batch * p.N * a.act_ld;
         for (int n = 0; n < p.N; n++) bulk_g2s(smem_u32(xs + (size_t)n * pitch), src + (size_t)n * a.act_ld, (uint32_t)kpad, smem_u32(bar));
@@ -158,13 +197,19 @@ __global__ void __launch_bounds__(32 * W, W <= 8 ? 2 : 1) gemm_stream_kernel(con
     auto stage_epilogue = [&](int pass_g0) {
         for (int i = tid; i < kGroupsPerPass * 32; i += T) {
             const int m = pass_g0 * 32 + i;
-            scale_s[i] = (p.out_kind == BGEMM_OUT_F16_SCALED && m < p.M) ? __half2float(p.alpha[(size_t)batch * p.M + m]) : 1.f;
+            const bool scaled = F16 ? p.alpha != nullptr : p.out_kind == BGEMM_OUT_F16_SCALED;
+            scale_s[i] = (scaled && m < p.M) ? __half2float(p.alpha[(size_t)batch * p.M + m]) : 1.f;
         }
         if (tid < 16) colsum_s[tid] = (p.epi && tid < p.N) ? __ldg(p.colsum + (size_t)batch * p.N + tid) : 0;
     };
     stage_epilogue(g_begin);
-    bool ok = mbar_wait(smem_u32(bar), 0, abort_flag, p.status, 31);
-    ok = __all_sync(0xffffffffu, ok);
+    bool ok = true;
+    if (F16) {
+        __syncthreads();                 // the activation rows are in place
+    } else {
+        ok = mbar_wait(smem_u32(bar), 0, abort_flag, p.status, 31);
+        ok = __all_sync(0xffffffffu, ok);
+    }
 
     // B-operand addressing: lane l supplies row (l % 8) of matrix (l / 8); matrix m of a load = 16 bytes at k offset 16 m
     uint32_t xrow[NTILES];
@@ -174,9 +219,24 @@ __global__ void __launch_bounds__(32 * W, W <= 8 ? 2 : 1) gemm_stream_kernel(con
         if (n >= p.N) n = p.N - 1;                       // columns beyond N: any valid row, their results are dropped
         xrow[t] = smem_u32(xs + (size_t)n * pitch) + 16 * (lane >> 3);
     }
+    // fp16 variant: lane (g, tig) reads, for column g, the permuted four-column group of packed word tig (or 4 + tig)
+    uint32_t xrow16 = 0;
+    if (F16) {
+        int n = lane >> 2;
+        if (n >= p.N) n = p.N - 1;
+        xrow16 = smem_u32(xs + (size_t)n * pitch) + 8 * (lane & 3);
+    }
 
     int acc[2][POW2 ? 8 : 1][NTILES][4];
+    float facc[2][4];                    // fp16 variant
     auto zero_acc = [&]() {
+        if (F16) {
+#pragma unroll
+            for (int f = 0; f < 2; f++)
+#pragma unroll
+                for (int i = 0; i < 4; i++) facc[f][i] = 0.f;
+            return;
+        }
 #pragma unroll
         for (int f = 0; f < 2; f++)
 #pragma unroll
@@ -189,6 +249,17 @@ __global__ void __launch_bounds__(32 * W, W <= 8 ? 2 : 1) gemm_stream_kernel(con
     // add the warp's sums of group `gl` (pass-local) into the CTA's shared sums [gl][n][row]
     auto flush = [&](int gl) {
         const int g = lane >> 2, tig = lane & 3;
+        if (F16) {
+#pragma unroll
+            for (int f = 0; f < 2; f++)
+#pragma unroll
+                for (int i = 0; i < 4; i++) {
+                    const int n = 2 * tig + (i & 1), row = 16 * f + g + 8 * (i >> 1);
+                    atomicAdd(reinterpret_cast<float*>(sums) + (gl * NPAD + n) * 32 + row, facc[f][i]);
+                }
+            zero_acc();
+            return;
+        }
 #pragma unroll
         for (int f = 0; f < 2; f++)
 #pragma unroll
@@ -226,6 +297,15 @@ __global__ void __launch_bounds__(32 * W, W <= 8 ? 2 : 1) gemm_stream_kernel(con
                     const int m = (cur_pass + gl) * 32 + row;
                     const int d = sums[i];
                     sums[i] = 0;
+                    if (F16) {
+                        if (n < p.N && m < p.M) {
+                            const float val = __int_as_float(d) * scale_s[gl * 32 + row];
+                            const size_t idx = p.out_layout == BGEMM_LAYOUT_NM ? (size_t)n * p.ldo + m : (size_t)m * p.ldo + n;
+                            if (p.out_kind == BGEMM_OUT_F32) reinterpret_cast<float*>(p.out)[idx] = val;
+                            else reinterpret_cast<__half*>(p.out)[idx] = __float2half_rn(val);
+                        }
+                        continue;
+                    }
                     if (n < p.N && m < p.M) {
                         const int val = p.epi ? colsum_s[n] - 2 * d : d;
                         const size_t idx = (size_t)batch * p.M * p.N + (p.out_layout == BGEMM_LAYOUT_NM ? (size_t)n * p.ldo + m : (size_t)m * p.ldo + n);
@@ -257,6 +337,23 @@ __global__ void __launch_bounds__(32 * W, W <= 8 ? 2 : 1) gemm_stream_kernel(con
         issue(slot_addr, cl);            // the slot's words are on their way to registers: its next unit may leave
         slot_addr += 1024;
         if (++slot == D) { slot = 0; slot_addr = ring_addr; }
+        if (F16) {
+            const uint32_t xo16 = xrow16 + xo * 2;
+#pragma unroll
+            for (int j = 0; j < 8; j++) {
+#pragma unroll
+                for (int h = 0; h < 2; h++) {            // packed words tig (h = 0) and 4 + tig (h = 1): 16 columns per step
+                    uint32_t b0, b1;
+                    asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(b0), "=r"(b1) : "r"(xo16 + (32 * j + 16 * h) * 2));
+#pragma unroll
+                    for (int f = 0; f < 2; f++) {
+                        const uint32_t w0 = h ? hi[2 * f] : lo[2 * f], w1 = h ? hi[2 * f + 1] : lo[2 * f + 1];
+                        // columns (0, 2) of the word's group: bits j and 16 + j; columns (1, 3): bits 8 + j and 24 + j
+                        mma_f16(facc[f], pm1_pair(w0, 15 - j), pm1_pair(w1, 15 - j), pm1_pair(w0, 7 - j), pm1_pair(w1, 7 - j), b0, b1);
+                    }
+                }
+            }
+        } else
 #pragma unroll
         for (int jp = 0; jp < 4; jp++) {                 // two slices (32 columns each) per B load
             uint32_t b[NTILES][4];
@@ -327,6 +424,43 @@ int launch_stream_variant(cudaStream_t stream, const GemmParams& p, const Stream
     return (int)(e != cudaSuccess ? e : cudaGetLastError());
 }
 
+size_t stream16_smem_bytes(int N, int kblocks, int W, int D) {
+    const size_t x = ((size_t)N * ((size_t)kblocks * 512 + 32) + 127) & ~(size_t)127;
+    return x + (size_t)W * D * 1024 + (size_t)kGroupsPerPass * 8 * 32 * sizeof(float) + (size_t)kGroupsPerPass * 32 * sizeof(float) + 64 + 64;
+}
+
+template <int W, int D>
+int launch_stream16_variant(cudaStream_t stream, const GemmParams& p, const StreamArgs& a) {
+    const size_t smem = stream16_smem_bytes(p.N, p.kblocks, W, D);
+    static bool configured[64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 0 || dev >= 64) return BGEMM_ERR_DRIVER;
+    if (!configured[dev]) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_stream_kernel<1, W, D, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kStreamMaxSmem);
+        if (e != cudaSuccess) return (int)e;
+        configured[dev] = true;
+    }
+    const int per_sm = (W <= 8 && smem <= 110 * 1024) ? 2 : 1;
+    long long ctas = (long long)sm_count() * per_sm;
+    if (ctas > a.groups) ctas = a.groups;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)ctas, 1, 1);
+    cfg.blockDim = dim3(32u * W, 1, 1);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    if (programmatic_launch_enabled()) {
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+    }
+    const cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_stream_kernel<1, W, D, true>, p, a);
+    count_launch();
+    return (int)(e != cudaSuccess ? e : cudaGetLastError());
+}
+
 // Largest N served here (tuning override: BGEMM_STREAM_MAX_N, 0 switches the kernel off).
 int stream_max_n() {
     static const int v = [] {
@@ -370,8 +504,29 @@ bool stream_supported(const GemmParams& p, long long batch) {
     return stream_variant(p.N, p.kblocks) != 0;
 }
 
+// Activation rows one launch of the fp16-activation variant can hold in shared memory (0: K is too large even for one).
+int w1a16_rows_per_launch(int kblocks) {
+    for (int n = 8; n >= 1; n--)
+        if (stream16_smem_bytes(n, kblocks, 16, 4) <= (size_t)kStreamMaxSmem) return n;
+    return 0;
+}
+
+// One launch: `p.N` <= w1a16_rows_per_launch activation rows starting at x16.
+int launch_gemm_w1a16(cudaStream_t stream, const GemmParams& p, const __half* x16, long long x_ld) {
+    StreamArgs a{};
+    a.x16 = x16;
+    a.x_ld = x_ld;
+    a.groups = p.mtiles * 4;
+    a.weights_static = p.weights_static;
+    if (stream16_smem_bytes(p.N, p.kblocks, 8, 8) <= 110 * 1024) return launch_stream16_variant<8, 8>(stream, p, a);
+    if (stream16_smem_bytes(p.N, p.kblocks, 8, 4) <= 110 * 1024) return launch_stream16_variant<8, 4>(stream, p, a);
+    if (stream16_smem_bytes(p.N, p.kblocks, 16, 8) <= (size_t)kStreamMaxSmem) return launch_stream16_variant<16, 8>(stream, p, a);
+    if (stream16_smem_bytes(p.N, p.kblocks, 16, 4) <= (size_t)kStreamMaxSmem) return launch_stream16_variant<16, 4>(stream, p, a);
+    return BGEMM_ERR_UNSUPPORTED;
+}
+
 int launch_gemm_stream(cudaStream_t stream, const GemmParams& p, const int8_t* acts, long long act_ld, long long batch, bool weights_static) {
-    StreamArgs a;
+    StreamArgs a{};
     a.acts = acts;
     a.act_ld = act_ld;
     a.groups = p.mtiles * 4;

@@ -69,6 +69,8 @@ int launch_gemm_persistent(cudaStream_t stream, const void* tensor_map, const Ge
 
 // Weight-streaming kernel for N <= 16 on mma.sync int8 (gemm_stream.cu).
 bool stream_supported(const GemmParams& p, long long batch);
+int w1a16_rows_per_launch(int kblocks);
+int launch_gemm_w1a16(cudaStream_t stream, const GemmParams& p, const __half* x16, long long x_ld);
 int stream_min_n();               // smallest N the kernel takes (1 unless BGEMM_STREAM_MIN_N says otherwise)
 int launch_gemm_stream(cudaStream_t stream, const GemmParams& p, const int8_t* acts, long long act_ld, long long batch, bool weights_static);
 

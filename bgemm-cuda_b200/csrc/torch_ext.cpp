@@ -290,6 +290,30 @@ torch::Tensor bgemm_attn_matmul_batched(torch::Tensor attn, torch::Tensor value,
     return gemm_prepared(plane, Sq, Sk, prep[0], prep[1], BGEMM_OP_ATTN, exact ? BGEMM_OUT_I32 : BGEMM_OUT_F16, BGEMM_LAYOUT_MN, c10::nullopt, 0, false);
 }
 
+// Binary weight x fp16 activation ("W1A16"): x fp16 [N, K] (as it is, no activation pass) x prepacked plane -> [N, M],
+// fp32 accumulation; fp32 result when out_f32, else fp16. alpha (optional): per-output-channel scale.
+torch::Tensor w1a16_linear_forward(torch::Tensor x, torch::Tensor plane, int64_t M, int64_t K, c10::optional<torch::Tensor> alpha, bool out_f32,
+                                   bool static_weights) {
+    TORCH_CHECK(x.is_cuda() && plane.is_cuda() && x.dim() == 2 && x.size(1) == K, "w1a16_linear_forward: x must be a CUDA tensor [N, K]");
+    TORCH_CHECK((size_t)plane.numel() >= bgemm_plane_bytes(M, K), "w1a16_linear_forward: plane too small for M, K");
+    c10::cuda::CUDAGuard guard(x.device());
+    auto xh = x.to(at::kHalf);
+    if (xh.stride(1) != 1) xh = xh.contiguous();
+    const int64_t N = xh.size(0);
+    auto out = torch::empty({N, M}, torch::TensorOptions().dtype(out_f32 ? at::kFloat : at::kHalf).device(x.device()));
+    const void* alpha_ptr = nullptr;
+    torch::Tensor a;
+    if (alpha.has_value()) {
+        a = alpha->to(at::kHalf).contiguous();
+        TORCH_CHECK(a.is_cuda() && a.numel() == M, "w1a16_linear_forward: alpha must hold M values on the GPU");
+        alpha_ptr = a.data_ptr();
+    }
+    check(bgemm_w1a16_gemm(stream_of(x), plane.data_ptr(), M, K, xh.data_ptr(), xh.stride(0), N, out.data_ptr(), out_f32 ? BGEMM_OUT_F32 : BGEMM_OUT_F16,
+                           BGEMM_LAYOUT_NM, alpha_ptr, static_weights ? 1 : 0),
+          "bgemm_w1a16_gemm");
+    return out;
+}
+
 torch::Tensor fp6_not_provided(py::args, py::kwargs) {
     throw py::type_error("the FP6 entry points of the reference (linear_forward_cuda, weight_dequant_cpu) are not part of this library");
 }
@@ -323,6 +347,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
           py::arg("M"), py::arg("K"), py::arg("alpha"), py::arg("splitK") = 0);
     m.def("bgemm_attn_matmul_batched", &bgemm_attn_matmul_batched, "Batched {0,1} x {-1,+1} matmul.", py::arg("attn"), py::arg("value"),
           py::arg("exact") = false);
+    m.def("w1a16_linear_forward", &w1a16_linear_forward, "Binary weight x fp16 activation, fp32 accumulation.", py::arg("x"), py::arg("plane"),
+          py::arg("M"), py::arg("K"), py::arg("alpha") = py::none(), py::arg("out_f32") = false, py::arg("static_weights") = false);
     m.def("linear_forward_cuda", &fp6_not_provided, "FP6 GEMM of the reference: not provided.");
     m.def("weight_dequant_cpu", &fp6_not_provided, "FP6 dequant of the reference: not provided.");
     m.def("plane_bytes", [](int64_t M, int64_t K) { return (int64_t)bgemm_plane_bytes(M, K); });

@@ -79,6 +79,7 @@ extern "C" {
 #define BGEMM_OUT_I32         0   /* int32 accumulators, untouched                                     */
 #define BGEMM_OUT_F16         1   /* fp16 = round-to-nearest-even(acc)   (kernel_matmul.cuh:540)       */
 #define BGEMM_OUT_F16_SCALED  2   /* fp16 = rne(float(acc) * float(alpha[m])), alpha = per-row scale   */
+#define BGEMM_OUT_F32         3   /* fp32 sums (bgemm_w1a16_gemm only)                                  */
 
 /* ---- result matrix orientation ------------------------------------------------------------------ */
 #define BGEMM_LAYOUT_NM  0   /* C is [N, M], M contiguous: the reference's linear output (kernel_matmul.cuh:534-546) */
@@ -210,6 +211,19 @@ int bgemm_gemm_multi_out(void* stream, const void* plane, int64_t M, int64_t K,
                          const int8_t* acts, const int32_t* colsum, int64_t N, int op,
                          void* const* outs_host, int n_outs, int64_t out_ld, int out_kind, int out_layout,
                          const void* alpha, int split_k, void* workspace, size_t workspace_bytes, int weights_static);
+
+/* Binary weight x fp16 activation ("W1A16", listed as to-do in the reference's README.md:29; no counterpart in its code):
+ *   C[n, m] = sum_k sgn(w[m, k]) * x[n, k]   (* alpha[m] when alpha != NULL),   sgn by the sign bit as everywhere else,
+ * with fp32 accumulation on the tensor cores (mma.sync m16n8k16: the weight bits are expanded to fp16 -1 / +1 in
+ * registers). `plane` is the ordinary tiled weight plane (BGEMM_WBIT_NEGATIVE); `x_f16` is the UNPREPARED activation
+ * matrix [N, K], fp16, row pitch x_ld elements. out_kind: BGEMM_OUT_F32 (fp32) or BGEMM_OUT_F16 (fp16 = rne(sum, scaled
+ * when alpha is given)); out_layout as in bgemm_gemm. It is a weight-streaming kernel built for decode shapes: eight
+ * activation rows per pass over the weights (fewer for very large K), so the time grows with ceil(N / 8); sums of fp32
+ * partial sums are order-dependent in their last bits (compare within 1e-3 relative, not bit for bit).
+ * BGEMM_ERR_UNSUPPORTED when one activation row does not fit in shared memory beside the weight ring (K beyond ~75000).
+ * `weights_static` != 0 adds the promise of bgemm_gemm_static_weights.                                                  */
+int bgemm_w1a16_gemm(void* stream, const void* plane, int64_t M, int64_t K, const void* x_f16, int64_t x_ld, int64_t N,
+                     void* out, int out_kind, int out_layout, const void* alpha, int weights_static);
 
 /* The same GEMM with a fused activation producer: the result is not stored, it becomes the NEXT layer's prepared
  * activations. next_acts int8 [N, bgemm_act_ld(M)] (this GEMM's M is the next layer's K) receives

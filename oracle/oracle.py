@@ -208,6 +208,14 @@ def ref_acc(w: torch.Tensor, x: torch.Tensor, op: int) -> torch.Tensor:
     return acc.to(torch.int32)
 
 
+def ref_w1a16(w: torch.Tensor, x: torch.Tensor, alpha: torch.Tensor | None = None) -> torch.Tensor:
+    """fp32 [N, M] = fp16(x) @ sgn(w).T (* alpha[m]) in fp32 on the CPU: binary weight x fp16 activation, the variant the
+    reference lists as to-do (README.md:29), defined like its dense layers (tests/python/bgemm_linear.py:270-272) with
+    sgn read from the sign bit."""
+    acc = x.cpu().to(torch.float16).float() @ map_weight(w.cpu(), OP_XOR).transpose(-1, -2)
+    return acc if alpha is None else acc * alpha.cpu().to(torch.float16).float()
+
+
 def ref_out(acc: torch.Tensor, out_kind: int, alpha: torch.Tensor | None = None) -> torch.Tensor:
     """Store conversion of an [..., N, M] int32 accumulator."""
     if out_kind == OUT_I32:
