@@ -5,11 +5,11 @@
 // for a 128-row tile, tensor-memory set-up and an unpack -> tensor memory -> UMMA round trip per K block that cost
 // several times the streaming time; here a warp owns a 32-row group of weights for a range of K blocks, fetches the
 // group's 1 KB of a K block with 16-byte asynchronous copies into a private ring in shared memory (several K blocks
-// in flight per warp, no barrier involved), turns bit j of every byte into the u8 value 2^j with ONE logic operation
-// per four weights (A fragments: two 16-row fragments per warp), and multiplies by the int8 activations (B fragments,
-// ldmatrix from shared memory) into accumulator set j; the end adds acc_j >> j. With two column tiles (N = 9..16)
-// the bit is shifted down instead and one accumulator set serves all j. Results are int32-exact for any int8
-// activations (|x| <= 128, K <= 65536 keeps accumulator 7 inside int32) and bit-identical to the tensor-memory kernels'.
+// in flight per warp, no barrier involved), turns bit j of every byte into the u8 value 2^j (even j) or 2^(j-1) (odd j,
+// from the word shifted right by one) with ONE logic operation per four weights (A fragments: two 16-row fragments per
+// warp), and multiplies by the int8 activations (B fragments, ldmatrix from shared memory) into accumulator set j / 2;
+// the end adds acc_s >> 2s. Results are int32-exact for any int8 activations (|x| <= 128; K <= 65536 is the limit this
+// library keeps for narrow tiles) and bit-identical to the tensor-memory kernels'.
 //
 // Work split: a CTA owns a contiguous range of 32-row groups; its warps cut the (group, K block) units of the range
 // into equal contiguous pieces, add their partial sums into shared memory when they leave a group, and after one
@@ -81,7 +81,10 @@ template <int NTILES, int W, int D, bool F16 = false>
 __global__ void __launch_bounds__(32 * W, W <= 8 ? 2 : 1) gemm_stream_kernel(const GemmParams p, const StreamArgs a) {
     static_assert(!F16 || NTILES == 1, "the fp16-activation variant has one column tile");
     constexpr int NPAD = 8 * NTILES;
-    constexpr bool POW2 = NTILES == 1 && !F16;
+    // Bit slice j of a packed byte is isolated where it stands (value 2^j) for even j, and one position lower in the
+    // word shifted right by one (value 2^(j-1)) for odd j: slices 2s and 2s + 1 then share the scale 4^s and one
+    // accumulator set, four sets in all; the end adds acc_s >> 2s (exact: set s holds 4^s times its share of the sum).
+    constexpr int SETS = F16 ? 1 : 4;
     constexpr int T = 32 * W;
     grid_launch_dependents();
     extern __shared__ __align__(128) uint8_t stream_smem[];
@@ -227,7 +230,7 @@ __global__ void __launch_bounds__(32 * W, W <= 8 ? 2 : 1) gemm_stream_kernel(con
         xrow16 = smem_u32(xs + (size_t)n * pitch) + 8 * (lane & 3);
     }
 
-    int acc[2][POW2 ? 8 : 1][NTILES][4];
+    int acc[2][SETS][NTILES][4];
     float facc[2][4];                    // fp16 variant
     auto zero_acc = [&]() {
         if (F16) {
@@ -240,7 +243,7 @@ __global__ void __launch_bounds__(32 * W, W <= 8 ? 2 : 1) gemm_stream_kernel(con
 #pragma unroll
         for (int f = 0; f < 2; f++)
 #pragma unroll
-            for (int j = 0; j < (POW2 ? 8 : 1); j++)
+            for (int j = 0; j < SETS; j++)
 #pragma unroll
                 for (int t = 0; t < NTILES; t++)
 #pragma unroll
@@ -267,12 +270,8 @@ __global__ void __launch_bounds__(32 * W, W <= 8 ? 2 : 1) gemm_stream_kernel(con
 #pragma unroll
                 for (int i = 0; i < 4; i++) {
                     int v = 0;
-                    if (POW2) {
 #pragma unroll
-                        for (int j = 0; j < 8; j++) v += acc[f][j][t][i] >> j;      // accumulator j holds 2^j x its share: exact
-                    } else {
-                        v = acc[f][0][t][i];
-                    }
+                    for (int j = 0; j < SETS; j++) v += acc[f][j][t][i] >> (2 * j);      // set j holds 4^j x its share: exact
                     const int n = 8 * t + 2 * tig + (i & 1), row = 16 * f + g + 8 * (i >> 1);
                     atomicAdd(&sums[(gl * NPAD + n) * 32 + row], v);
                 }
@@ -334,6 +333,9 @@ __global__ void __launch_bounds__(32 * W, W <= 8 ? 2 : 1) gemm_stream_kernel(con
         uint32_t lo[4], hi[4];
         ldsm_x4(slot_addr, lo);          // word (lane % 4) of rows lane / 4 + {0, 8, 16, 24}
         ldsm_x4(slot_addr + 512, hi);    // word 4 + (lane % 4) of the same rows
+        uint32_t lo1[4], hi1[4];         // the same words one bit lower, for the odd slices
+#pragma unroll
+        for (int i = 0; i < 4; i++) { lo1[i] = lo[i] >> 1; hi1[i] = hi[i] >> 1; }
         issue(slot_addr, cl);            // the slot's words are on their way to registers: its next unit may leave
         slot_addr += 1024;
         if (++slot == D) { slot = 0; slot_addr = ring_addr; }
@@ -361,19 +363,14 @@ __global__ void __launch_bounds__(32 * W, W <= 8 ? 2 : 1) gemm_stream_kernel(con
             for (int t = 0; t < NTILES; t++) ldsm_x4(xrow[t] + xo + jp * 64, b[t]);
 #pragma unroll
             for (int h = 0; h < 2; h++) {
-                const int j = 2 * jp + h;
 #pragma unroll
                 for (int f = 0; f < 2; f++) {
-                    uint32_t a0, a1, a2, a3;
-                    if (POW2) {
-                        const uint32_t m = 0x01010101u << j;
-                        a0 = lo[2 * f] & m; a1 = lo[2 * f + 1] & m; a2 = hi[2 * f] & m; a3 = hi[2 * f + 1] & m;
-                    } else {
-                        a0 = (lo[2 * f] >> j) & 0x01010101u; a1 = (lo[2 * f + 1] >> j) & 0x01010101u;
-                        a2 = (hi[2 * f] >> j) & 0x01010101u; a3 = (hi[2 * f + 1] >> j) & 0x01010101u;
-                    }
+                    // j = 2 jp + h: even slices from the words as they are, odd ones from the shifted words, both at bit 2 jp
+                    const uint32_t m = 0x01010101u << (2 * jp);
+                    const uint32_t a0 = (h ? lo1[2 * f] : lo[2 * f]) & m, a1 = (h ? lo1[2 * f + 1] : lo[2 * f + 1]) & m;
+                    const uint32_t a2 = (h ? hi1[2 * f] : hi[2 * f]) & m, a3 = (h ? hi1[2 * f + 1] : hi[2 * f + 1]) & m;
 #pragma unroll
-                    for (int t = 0; t < NTILES; t++) mma_u8s8(acc[f][POW2 ? j : 0][t], a0, a1, a2, a3, b[t][2 * h], b[t][2 * h + 1]);
+                    for (int t = 0; t < NTILES; t++) mma_u8s8(acc[f][jp][t], a0, a1, a2, a3, b[t][2 * h], b[t][2 * h + 1]);
                 }
             }
         }
@@ -499,7 +496,8 @@ int stream_min_n() {       // smallest N served here (tuning override: BGEMM_STR
 
 bool stream_supported(const GemmParams& p, long long batch) {
     if (p.N > stream_max_n() || p.N < stream_min_n() || p.out_kind == kOutActs || batch > 65535) return false;
-    // accumulator 7 of the one-tile variant holds 128 x (its share of) the sum: |x| <= 128 keeps it inside int32 up to K = 65536
+    // accumulator set 3 holds 64 x (its quarter of) the sum: |x| <= 128 keeps it inside int32 far beyond this limit, which
+    // is the one the other narrow-tile kernels need
     if (p.K > 65536) return false;
     return stream_variant(p.N, p.kblocks) != 0;
 }
