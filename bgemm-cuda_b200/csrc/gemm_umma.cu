@@ -526,7 +526,14 @@ int launch_gemm(cudaStream_t stream, GemmParams p, const int8_t* acts, long long
     if (skinny_supported(p, batch, !p.acts_general)) return launch_gemm_skinny(stream, p, acts, act_ld, batch);
     EncodeTiledFn encode = get_encode_fn();
     if (!encode) return BGEMM_ERR_DRIVER;
-    const int NT = gemm_tile_n(p.N);
+    int NT = gemm_tile_n(p.N);
+    // One partial wave: with 128-wide tiles on more than one but at most two CTAs per SM, some SMs run two tiles side by
+    // side while the others run one, and the launch lasts as long as the pairs (3584 x 8192 x 1024, the 8-GPU shard of the
+    // 28672-row layer: 32.5 us); 256-wide tiles, one CTA per SM, finish sooner when they all fit at once (28.9 us).
+    if (NT == 128 && p.split_k == 1 && batch == 1 && forced_nt() < 0) {
+        const long long t128 = (long long)p.mtiles * ((p.N + 127) / 128), t256 = (long long)p.mtiles * ((p.N + 255) / 256);
+        if (t128 > sm_count() && t128 <= 2LL * sm_count() && t256 <= sm_count() && p.N % 256 == 0) NT = 256;
+    }
     p.ntiles = (int)((p.N + NT - 1) / NT);
 
     CUtensorMap tmap;

@@ -194,6 +194,22 @@ __device__ __forceinline__ uint2 act_values_x8(const uint4& w, int mode, int& su
     return o;
 }
 
+// Eight int8 source values -> eight int8 activation values, four elements per 32-bit operation (per-byte compares).
+__device__ __forceinline__ uint2 act_values_i8x8(const uint2& w, int mode, int& sum) {
+    const uint32_t in[2] = {w.x, w.y};
+    uint32_t o[2];
+#pragma unroll
+    for (int i = 0; i < 2; i++) {
+        const uint32_t neg = __vcmplts4(in[i], 0u);                 // 0xff where the byte is negative
+        if (mode == BGEMM_ACT_INT8) o[i] = in[i];
+        else if (mode == BGEMM_ACT_NEG01) o[i] = neg & 0x01010101u;
+        else if (mode == BGEMM_ACT_SIGN) o[i] = neg | 0x01010101u;  // 0xff (-1) or 0x01 (+1)
+        else o[i] = neg | (__vcmpne4(in[i], 0u) & 0x01010101u);     // torch.sign: 0xff, 0x00, 0x01
+        sum = __dp4a((int)o[i], 0x01010101, sum);
+    }
+    return make_uint2(o[0], o[1]);
+}
+
 // Activation rows (rows of all batches numbered through) -> int8 rows + column sums. The launcher picks the split:
 // many rows: a warp converts `rows_per_warp` consecutive rows, sized so that the launch is one resident wave (with
 // one short row per warp a launch of 1.3 waves ran its last third on a nearly idle GPU); few rows: `warps_per_row`
@@ -232,6 +248,7 @@ __global__ void __launch_bounds__(256, 4) prepare_acts_kernel(const T* __restric
             const T* rp = src + batch * src_batch_stride + row * ld;
             int8_t* dp = dst + gr * kld;
             const bool vec_ok = (sizeof(T) == 2) && ((reinterpret_cast<uintptr_t>(rp) & 15) == 0);
+            const bool vec8_ok = (sizeof(T) == 1) && ((reinterpret_cast<uintptr_t>(rp) & 7) == 0);
             for (long long kbase = b0 * 256 + lane * 8; kbase < b1 * 256; kbase += 256 * U) {
                 if (vec_ok && kbase + 256 * (U - 1) + 8 <= K && kbase + 256 * (U - 1) < b1 * 256) {
                     // all U blocks inside the row and the slice: loads first, then two elements per operation
@@ -240,6 +257,15 @@ __global__ void __launch_bounds__(256, 4) prepare_acts_kernel(const T* __restric
                     for (int u = 0; u < U; u++) v[u] = __ldcs(reinterpret_cast<const uint4*>(rp + kbase + 256 * u));
 #pragma unroll
                     for (int u = 0; u < U; u++) *reinterpret_cast<uint2*>(dp + kbase + 256 * u) = act_values_x8(v[u], mode, sum);
+                    continue;
+                }
+                if (vec8_ok && kbase + 256 * (U - 1) + 8 <= K && kbase + 256 * (U - 1) < b1 * 256) {
+                    // int8 sources: the same with 8-byte loads and four elements per operation
+                    uint2 v[U];
+#pragma unroll
+                    for (int u = 0; u < U; u++) v[u] = __ldcs(reinterpret_cast<const uint2*>(rp + kbase + 256 * u));
+#pragma unroll
+                    for (int u = 0; u < U; u++) *reinterpret_cast<uint2*>(dp + kbase + 256 * u) = act_values_i8x8(v[u], mode, sum);
                     continue;
                 }
 #pragma unroll 1

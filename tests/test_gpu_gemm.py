@@ -97,6 +97,21 @@ def test_prepare_acts(B, mode, N, K):
     assert np.array_equal(colsum_t.cpu().numpy(), ref_c)
 
 
+@pytest.mark.parametrize("mode", [0, 1, 2, 3])
+@pytest.mark.parametrize("N,K,pad", [(3, 4096, 0), (40, 8192, 0), (5, 2500, 0), (7, 4096, 4), (2, 300, 0), (1100, 2304, 0)])
+def test_prepare_acts_from_int8_sources(B, mode, N, K, pad):
+    """int8 activations (ternary values already stored as bytes, or general int8 for W1A8) through every mode: rows long
+    enough for the 8-byte vector path, ragged tails, rows that are not 8-byte aligned (pitch K + 4)."""
+    g = O._gen(N + K + mode)
+    full = torch.randint(-128, 128, (N, K + pad), generator=g, dtype=torch.int8)
+    full[:, ::7] = 0
+    x = full[:, :K]
+    acts, colsum = B.prepare_acts(full.cuda()[:, :K], mode)
+    ref_a, ref_c = O.np_prepare_acts(x, mode)
+    assert np.array_equal(acts.cpu().numpy(), ref_a)
+    assert np.array_equal(colsum.cpu().numpy(), ref_c)
+
+
 def test_rowmajor_msb_prepack_matches_reference_format(B):
     g = O._gen(11)
     M, K = 96, 512
