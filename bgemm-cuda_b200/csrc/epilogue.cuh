@@ -30,9 +30,8 @@ __device__ __forceinline__ void store8_rows(const TileOut& t, int n, int m0, con
     const bool full = gm + 8 <= p.M;
     if (p.out_kind == kOutActs) return;       // handled by store8_rows_as_acts
     if (p.out_kind == BGEMM_OUT_I32) {
-#pragma unroll 1
-        for (int d = 0; d <= p.n_out_more; d++) {          // every destination gets the same 32 bytes (peers: plain stores over NVLink)
-            int* o = reinterpret_cast<int*>(d == 0 ? p.out : p.out_more[d - 1]) + idx;
+        auto put = [&](void* base) {
+            int* o = reinterpret_cast<int*>(base) + idx;
             if (full && (reinterpret_cast<uintptr_t>(o) & 15) == 0) {
                 reinterpret_cast<int4*>(o)[0] = make_int4(val[0], val[1], val[2], val[3]);
                 reinterpret_cast<int4*>(o)[1] = make_int4(val[4], val[5], val[6], val[7]);
@@ -40,22 +39,28 @@ __device__ __forceinline__ void store8_rows(const TileOut& t, int n, int m0, con
 #pragma unroll
                 for (int q = 0; q < 8; q++) if (gm + q < p.M) o[q] = val[q];
             }
-        }
+        };
+        put(p.out);
+        // further destinations (peer-mapped copies of the result: plain stores over NVLink); none in the common case
+#pragma unroll 1
+        for (int d = 0; d < p.n_out_more; d++) put(p.out_more[d]);
     } else {
         __align__(16) __half h[8];
 #pragma unroll
         for (int q = 0; q < 8; q++)
             h[q] = __float2half_rn(p.out_kind == BGEMM_OUT_F16 ? (float)val[q] : (float)val[q] * t.s_alpha[m0 + q]);
-#pragma unroll 1
-        for (int d = 0; d <= p.n_out_more; d++) {
-            __half* o = reinterpret_cast<__half*>(d == 0 ? p.out : p.out_more[d - 1]) + idx;
+        auto put = [&](void* base) {
+            __half* o = reinterpret_cast<__half*>(base) + idx;
             if (full && (reinterpret_cast<uintptr_t>(o) & 15) == 0) {
                 *reinterpret_cast<uint4*>(o) = *reinterpret_cast<const uint4*>(h);
             } else {
 #pragma unroll
                 for (int q = 0; q < 8; q++) if (gm + q < p.M) o[q] = h[q];
             }
-        }
+        };
+        put(p.out);
+#pragma unroll 1
+        for (int d = 0; d < p.n_out_more; d++) put(p.out_more[d]);
     }
 }
 
@@ -97,9 +102,8 @@ __device__ __forceinline__ void store8_cols(const TileOut& t, int m, int n0, con
     const size_t idx = (size_t)t.batch * p.M * p.N + (size_t)gm * p.ldo + gn;
     const bool full = gn + 8 <= p.N;
     if (p.out_kind == BGEMM_OUT_I32) {
-#pragma unroll 1
-        for (int d = 0; d <= p.n_out_more; d++) {
-            int* o = reinterpret_cast<int*>(d == 0 ? p.out : p.out_more[d - 1]) + idx;
+        auto put = [&](void* base) {
+            int* o = reinterpret_cast<int*>(base) + idx;
             if (full && (reinterpret_cast<uintptr_t>(o) & 15) == 0) {
                 reinterpret_cast<int4*>(o)[0] = make_int4(val[0], val[1], val[2], val[3]);
                 reinterpret_cast<int4*>(o)[1] = make_int4(val[4], val[5], val[6], val[7]);
@@ -107,22 +111,27 @@ __device__ __forceinline__ void store8_cols(const TileOut& t, int m, int n0, con
 #pragma unroll
                 for (int q = 0; q < 8; q++) if (gn + q < p.N) o[q] = val[q];
             }
-        }
+        };
+        put(p.out);
+#pragma unroll 1
+        for (int d = 0; d < p.n_out_more; d++) put(p.out_more[d]);
     } else {
         const float a = t.s_alpha[m];
         __align__(16) __half h[8];
 #pragma unroll
         for (int q = 0; q < 8; q++) h[q] = __float2half_rn(p.out_kind == BGEMM_OUT_F16 ? (float)val[q] : (float)val[q] * a);
-#pragma unroll 1
-        for (int d = 0; d <= p.n_out_more; d++) {
-            __half* o = reinterpret_cast<__half*>(d == 0 ? p.out : p.out_more[d - 1]) + idx;
+        auto put = [&](void* base) {
+            __half* o = reinterpret_cast<__half*>(base) + idx;
             if (full && (reinterpret_cast<uintptr_t>(o) & 15) == 0) {
                 *reinterpret_cast<uint4*>(o) = *reinterpret_cast<const uint4*>(h);
             } else {
 #pragma unroll
                 for (int q = 0; q < 8; q++) if (gn + q < p.N) o[q] = h[q];
             }
-        }
+        };
+        put(p.out);
+#pragma unroll 1
+        for (int d = 0; d < p.n_out_more; d++) put(p.out_more[d]);
     }
 }
 
