@@ -135,6 +135,24 @@ __device__ __forceinline__ void store8_cols(const TileOut& t, int m, int n0, con
     }
 }
 
+// [M, N] results of an unpartitioned tile: the accumulator tile is staged ROW-major, [128 rows][kRowPitch(NT)] int32 (an
+// accumulator row leaves tensor memory as consecutive columns, so the staging stores are 16-byte vectors), and
+// consecutive threads take consecutive 8-column chunks of a row: both the shared-memory reads and the global stores of a
+// warp are contiguous runs (a whole 128 x NT tile row after row when NT columns are all there is).
+__host__ __device__ constexpr int row_pitch_of(int nt) { return nt + 4; }      // (pitch / 4) odd: 16-byte row accesses spread over all banks
+template <int NT>
+__device__ __forceinline__ void write_tile_rowmajor(const TileOut& t, const int* staged, int et, int nthreads) {
+    constexpr int CH = NT / 8, PITCH = row_pitch_of(NT);
+#pragma unroll 1
+    for (int u = et; u < 128 * CH; u += nthreads) {
+        const int m = u / CH, c0 = (u - m * CH) * 8;
+        const int4* g = reinterpret_cast<const int4*>(staged + m * PITCH + c0);
+        const int4 a = g[0], b = g[1];
+        const int acc[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+        store8_cols(t, m, c0, acc);
+    }
+}
+
 // Sum `parts` partial tiles (each `stride` ints apart, starting at `base`) over 8 consecutive rows at element
 // offset `off` of a [columns][128] int32 tile. GLOBAL: the tiles are slabs in global memory (L2 reads).
 template <bool GLOBAL>

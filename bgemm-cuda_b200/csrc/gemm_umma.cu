@@ -71,9 +71,11 @@ struct Cfg {
     static constexpr int NMMA = NT == 256 ? 1 : 2;
     static constexpr int NBARS = 2 * W_STAGES + 2 * B_STAGES + 2 * A_STAGES + 2;
     static constexpr int MISC_BYTES = 512 /*barriers*/ + 512 /*alpha*/ + 1024 /*colsum*/ + 512 /*flags*/;
-    // Epilogue staging aliases the activation and weight stages: one [NT][128] int32 tile, or -- K partitions in a
-    // cluster -- up to (NT + 7 * 8) columns of partial sums received from the peers.
+    // Epilogue staging aliases the activation and weight stages: one [NT][128] int32 tile (row-major with padded rows
+    // for [M, N] results), or -- K partitions in a cluster -- up to (NT + 7 * 8) columns of partial sums received from
+    // the peers.
     static constexpr int STAGE_TILE_BYTES = (NT + 56) * 128 * 4;
+    static_assert(128 * row_pitch_of(NT) * 4 <= STAGE_TILE_BYTES, "row-major staging");
     static constexpr int SMEM_USED = B_STAGES * B_STAGE_BYTES + W_STAGES * 4096 + MISC_BYTES + 1024 /*align*/;
     // Co-resident CTAs must not ask for more tensor memory than the SM has (a later tcgen05.alloc would
     // stall until an earlier CTA exits): request enough shared memory to cap residency at 512 / TMEM_COLS.
@@ -324,6 +326,8 @@ __global__ void __launch_bounds__(kGemmThreads, Cfg<NT, POW2, DEEP>::MIN_CTAS) g
     tout.p = &p; tout.s_alpha = s_alpha; tout.s_colsum = s_colsum;
     tout.batch = batch; tout.m_base = mt * 128; tout.n_base = nt * NT;
 
+    // [M, N] results without K partitions: staged row-major, stored as contiguous runs (see write_tile_rowmajor)
+    const bool rowmajor = p.split_k == 1 && p.out_layout == BGEMM_LAYOUT_MN && p.out_kind != kOutActs;
     if (p.cluster) {   // every CTA of the cluster is past its mainloop: peers' operand stages may be overwritten
         __syncwarp();
         cluster_arrive_release();
@@ -357,7 +361,11 @@ __global__ void __launch_bounds__(kGemmThreads, Cfg<NT, POW2, DEEP>::MIN_CTAS) g
 #pragma unroll
                 for (int q = 0; q < 8; q++) acc[q] = (int)t[q];
             }
-            if (p.cluster) {
+            if (rowmajor) {
+                int4* o = reinterpret_cast<int4*>(sP + r * row_pitch_of(NT) + n0);
+                o[0] = make_int4(acc[0], acc[1], acc[2], acc[3]);
+                o[1] = make_int4(acc[4], acc[5], acc[6], acc[7]);
+            } else if (p.cluster) {
                 const int dst = n0 / per;                        // the 8 columns of a chunk share their destination
                 const uint32_t remote = mapa_shared(smem_u32(sP + ((split * per + (n0 - dst * per)) * 128 + r)), (uint32_t)dst);
 #pragma unroll
@@ -374,7 +382,10 @@ __global__ void __launch_bounds__(kGemmThreads, Cfg<NT, POW2, DEEP>::MIN_CTAS) g
     if (p.split_k == 1) {
         if (epi_thread) {
             named_bar_sync(1, kUnpackThreads);
-            if (!*abort_flag) write_tile<false>(tout, sP, 1, 0, 0, NT, tid, kUnpackThreads);
+            if (!*abort_flag) {
+                if (rowmajor) write_tile_rowmajor<NT>(tout, sP, tid, kUnpackThreads);
+                else write_tile<false>(tout, sP, 1, 0, 0, NT, tid, kUnpackThreads);
+            }
         }
     } else if (p.cluster) {
         __syncwarp();
