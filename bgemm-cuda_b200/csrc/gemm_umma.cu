@@ -71,9 +71,8 @@ struct Cfg {
     static constexpr int NMMA = NT == 256 ? 1 : 2;
     static constexpr int NBARS = 2 * W_STAGES + 2 * B_STAGES + 2 * A_STAGES + 2;
     static constexpr int MISC_BYTES = 512 /*barriers*/ + 512 /*alpha*/ + 1024 /*colsum*/ + 512 /*flags*/;
-    // Epilogue staging aliases the activation and weight stages: one [NT][128] int32 tile (row-major with padded rows
-    // for [M, N] results), or -- K partitions in a cluster -- up to (NT + 7 * 8) columns of partial sums received from
-    // the peers.
+    // Epilogue staging aliases the activation and weight stages: one [NT][128] int32 tile, or -- K partitions in a
+    // cluster -- up to (NT + 7 * 8) columns of partial sums received from the peers.
     static constexpr int STAGE_TILE_BYTES = (NT + 56) * 128 * 4;
     static_assert(128 * row_pitch_of(NT) * 4 <= STAGE_TILE_BYTES, "row-major staging");
     static constexpr int SMEM_USED = B_STAGES * B_STAGE_BYTES + W_STAGES * 4096 + MISC_BYTES + 1024 /*align*/;
