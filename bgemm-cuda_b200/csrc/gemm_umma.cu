@@ -544,17 +544,21 @@ int launch_gemm(cudaStream_t stream, GemmParams p, const int8_t* acts, long long
         const long long t128 = (long long)p.mtiles * ((p.N + 127) / 128), t256 = (long long)p.mtiles * ((p.N + 255) / 256);
         if (t128 > sm_count() && t128 <= 2LL * sm_count() && t256 <= sm_count() && p.N % 256 == 0) NT = 256;
     }
+    // Wide activation matrices: 256 x 256 tiles on CTA pairs (each CTA loads boxes of 128 activation rows).
+    const bool pair = pair_supported(p, batch);
+    if (pair) NT = 256;
     p.ntiles = (int)((p.N + NT - 1) / NT);
 
     CUtensorMap tmap;
     cuuint64_t dims[3] = {(cuuint64_t)act_ld, (cuuint64_t)p.N, (cuuint64_t)batch};
     cuuint64_t strides[2] = {(cuuint64_t)act_ld, (cuuint64_t)act_ld * (cuuint64_t)p.N};
-    cuuint32_t box[3] = {128u, (cuuint32_t)NT, 1u};
+    cuuint32_t box[3] = {128u, (cuuint32_t)(pair ? 128 : NT), 1u};
     cuuint32_t estr[3] = {1u, 1u, 1u};
     CUresult r = encode(&tmap, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<int8_t*>(acts), dims, strides, box, estr,
                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return BGEMM_ERR_DRIVER;
+    if (pair) return launch_gemm_pair(stream, &tmap, p, batch);
 
     // A pool of narrow problems (one tile across N, many more tiles than SMs, no K partitioning): one persistent CTA
     // per SM walks over the tiles and overlaps every tile's epilogue with the next tile's mainloop (measured 2.46 vs

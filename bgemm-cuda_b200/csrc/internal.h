@@ -67,6 +67,11 @@ bool persistent_supported(int NT);
 bool persistent_kblocks_ok(int NT, int kblocks);   // K-block counts per tile the issuers' hand-over protocol covers
 int launch_gemm_persistent(cudaStream_t stream, const void* tensor_map, const GemmParams& p, int NT, long long total_tiles, int ctas);
 
+// Persistent kernel on CTA pairs, 256 x 256 tiles (gemm_pair.cu); `tensor_map` must have boxes of 128 activation rows
+// and p.ntiles must count 256-column tiles.
+bool pair_supported(const GemmParams& p, long long batch);
+int launch_gemm_pair(cudaStream_t stream, const void* tensor_map, const GemmParams& p, long long batch);
+
 // Weight-streaming kernel for N <= 16 on mma.sync int8 (gemm_stream.cu).
 bool stream_supported(const GemmParams& p, long long batch);
 int w1a16_rows_per_launch(int kblocks);
