@@ -276,6 +276,10 @@ class Pool:
             del w
         self.alphas_full = (0.01 + 0.09 * torch.rand(layers, M, generator=g, device=dev)).to(torch.float16)
         self.alphas = self.alphas_full[:, row0:row0 + self.rows].contiguous()
+        # optional workspace of bgemm_gemm: lets the kernel for wide activation matrices split its work into exactly equal
+        # parts per SM pair (zeroed once; every launch leaves it zero); one per pool, all GEMM calls are on one stream
+        need = max(B.lib.bgemm_gemm_balance_workspace_bytes(self.rows, N, K, 0, 1), B.lib.bgemm_gemm_balance_workspace_bytes(self.rows, N, K, 0, layers), 256)
+        self.ws = torch.zeros(need, dtype=torch.uint8, device=cx.dev)
         if op_name == "bwta":
             u = torch.rand(layers, N, K, generator=g, device=dev)
             self.x8 = torch.where(u < 0.35, -1, torch.where(u < 0.70, 1, 0)).to(torch.int8)
@@ -303,12 +307,12 @@ class Pool:
         # weights were prepacked and synchronised at set-up: the static-weights promise holds
         B.check(B.lib.bgemm_gemm_static_weights((stream or self.cx.stream).cuda_stream, self.planes.data_ptr() + i * self.plane_b, self.rows, self.K,
                                  self.acts.data_ptr() + a_off, self.colsum.data_ptr() + 4 * (i * self.N + n0), n1 - n0, self.op, out.data_ptr(),
-                                 out_kind, layout, self.alphas.data_ptr() + 2 * i * self.rows, 0, None, 0, 1), "gemm")
+                                 out_kind, layout, self.alphas.data_ptr() + 2 * i * self.rows, 0, self.ws.data_ptr(), self.ws.numel(), 1), "gemm")
 
     def gemm_batched(self, outs, out_kind, layout):
         B = self.cx.B
         B.check(B.lib.bgemm_gemm_static_weights(self.cx.stream.cuda_stream, self.planes.data_ptr(), self.rows, self.K, self.acts.data_ptr(), self.colsum.data_ptr(),
-                                 self.N, self.op, outs.data_ptr(), out_kind, layout, self.alphas.data_ptr(), 0, None, 0, self.layers), "gemm")
+                                 self.N, self.op, outs.data_ptr(), out_kind, layout, self.alphas.data_ptr(), 0, self.ws.data_ptr(), self.ws.numel(), self.layers), "gemm")
 
     # ---- oracle ---------------------------------------------------------------------------------------------------
     def expect(self, i, out_kind, layout):
@@ -476,7 +480,7 @@ def run_gather(cx: Ctx, args, pool: Pool, outs, layers, rows, ops_layer):
                 a_off = i * pool.act_row
                 B.check(B.lib.bgemm_gemm_multi_out(cx.stream.cuda_stream, pool.planes.data_ptr() + i * pool.plane_b, rows, pool.K,
                                                    pool.acts.data_ptr() + a_off, pool.colsum.data_ptr() + 4 * i * N, N, pool.op, ptrs[i], cx.world, M,
-                                                   B.OUT_F16_SCALED, B.LAYOUT_NM, pool.alphas.data_ptr() + 2 * i * rows, 0, None, 0, 1), "gemm_multi_out")
+                                                   B.OUT_F16_SCALED, B.LAYOUT_NM, pool.alphas.data_ptr() + 2 * i * rows, 0, pool.ws.data_ptr(), pool.ws.numel(), 1), "gemm_multi_out")
             hdl.barrier(channel=1)                  # every slab has landed on every rank
         fused = step_fused
     except Exception as exc:                        # symmetric memory unavailable on this box: report, keep the NCCL numbers

@@ -53,6 +53,8 @@ lib.bgemm_w1a16_gemm.argtypes = [_vp, _vp, _i64, _i64, _vp, _i64, _i64, _vp, _in
 lib.bgemm_gemm_to_acts.argtypes = [_vp, _vp, _i64, _i64, _vp, _vp, _i64, _int, _vp, _int, _vp, _vp, _int, _vp, _sz, _i64]
 lib.bgemm_gemm_workspace_bytes.restype = _sz
 lib.bgemm_gemm_workspace_bytes.argtypes = [_i64, _i64, _i64, _int, _i64]
+lib.bgemm_gemm_balance_workspace_bytes.restype = _sz
+lib.bgemm_gemm_balance_workspace_bytes.argtypes = [_i64, _i64, _i64, _int, _i64]
 lib.bgemm_gemm_auto_split_k.argtypes = [_i64, _i64, _i64, _i64]
 lib.bgemm_linear_forward.argtypes = [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _int, _int, _int, _vp, _int, _vp, _sz]
 lib.bgemm_linear_workspace_bytes.restype = _sz
@@ -166,6 +168,24 @@ def workspace(device: torch.device, nbytes: int) -> torch.Tensor:
     return ws
 
 
+_balance_workspaces: dict = {}
+
+
+def balance_workspace(device: torch.device, nbytes: int) -> torch.Tensor:
+    """The optional workspace of bgemm_gemm (exact work split for wide activation matrices), per (device, current
+    stream). Kept apart from `workspace`: its first 64 KiB are flags that must stay zero between launches, and the other
+    buffer also parks packed operands."""
+    index = device.index if device.index is not None else torch.cuda.current_device()
+    key = (device.type, index, torch.cuda.current_stream(index).cuda_stream)
+    ws = _balance_workspaces.get(key)
+    if ws is None or ws.numel() < nbytes:
+        ws = torch.zeros(nbytes, dtype=torch.uint8, device=device)
+        if key in _balance_workspaces:
+            _balance_workspaces[key].record_stream(torch.cuda.current_stream(index))
+        _balance_workspaces[key] = ws
+    return ws
+
+
 def gemm(plane: torch.Tensor, M: int, K: int, acts: torch.Tensor, colsum: torch.Tensor, op: int, out_kind: int = OUT_I32,
          out_layout: int = LAYOUT_NM, alpha: torch.Tensor | None = None, split_k: int = 0, out: torch.Tensor | None = None,
          ws: torch.Tensor | None = None, static_weights: bool = False):
@@ -185,10 +205,14 @@ def gemm(plane: torch.Tensor, M: int, K: int, acts: torch.Tensor, colsum: torch.
     need = lib.bgemm_gemm_workspace_bytes(M, N, K, split_k, B)
     if need and ws is None:
         ws = workspace(acts.device, need)
+    if not need and ws is None:
+        need = lib.bgemm_gemm_balance_workspace_bytes(M, N, K, split_k, B)      # optional: exact work split for wide N
+        if need:
+            ws = balance_workspace(acts.device, need)
     with torch.cuda.device(acts.device):
         fn = lib.bgemm_gemm_static_weights if static_weights else lib.bgemm_gemm
         check(fn(_stream(), plane.data_ptr(), M, K, acts.data_ptr(), colsum.data_ptr(), N, op, out.data_ptr(), out_kind,
-                 out_layout, _ptr(alpha), split_k, _ptr(ws) if need else None, ws.numel() if need else 0, B), "bgemm_gemm")
+                 out_layout, _ptr(alpha), split_k, _ptr(ws), ws.numel() if ws is not None else 0, B), "bgemm_gemm")
     return out
 
 
@@ -204,9 +228,13 @@ def gemm_multi_out(plane: torch.Tensor, M: int, K: int, acts: torch.Tensor, cols
     need = lib.bgemm_gemm_workspace_bytes(M, N, K, split_k, 1)
     if need and ws is None:
         ws = workspace(acts.device, need)
+    if not need and ws is None:
+        need = lib.bgemm_gemm_balance_workspace_bytes(M, N, K, split_k, 1)
+        if need:
+            ws = balance_workspace(acts.device, need)
     with torch.cuda.device(acts.device):
         check(lib.bgemm_gemm_multi_out(_stream(), plane.data_ptr(), M, K, acts.data_ptr(), colsum.data_ptr(), N, op, ptrs, len(out_ptrs), out_ld,
-                                       out_kind, out_layout, _ptr(alpha), split_k, _ptr(ws) if need else None, ws.numel() if need else 0,
+                                       out_kind, out_layout, _ptr(alpha), split_k, _ptr(ws), ws.numel() if ws is not None else 0,
                                        1 if static_weights else 0), "bgemm_gemm_multi_out")
 
 

@@ -242,6 +242,14 @@ size_t bgemm_gemm_workspace_bytes(int64_t M, int64_t N, int64_t K, int split_k, 
     return counter_bytes(tiles) + (size_t)tiles * (size_t)s * (size_t)NT * 128 * 4;
 }
 
+// Optional workspace of bgemm_gemm and its variants (see the header): with it the CTA-pair kernel cuts its work into
+// exactly equal ranges per SM pair. Layout: [64 KiB of flags, zero between launches][one partial accumulator per CTA].
+size_t bgemm_gemm_balance_workspace_bytes(int64_t M, int64_t N, int64_t K, int split_k, int64_t batch) {
+    if (M < 1 || N < 1 || K < 1 || batch < 1) return 0;
+    if (resolve_split_k(M, N, K, batch, split_k) != 1) return 0;
+    return pair_balance_workspace_bytes(M, N, K, batch);
+}
+
 static int gemm_entry(void* stream, const void* plane, int64_t M, int64_t K, const int8_t* acts, const int32_t* colsum, int64_t N, int op,
                       void* out, int out_kind, int out_layout, const void* alpha, int split_k, void* workspace, size_t workspace_bytes,
                       int64_t batch, int weights_static, void* const* more_outs = nullptr, int n_more = 0, int64_t out_ld = 0) {
@@ -302,6 +310,13 @@ static int gemm_entry(void* stream, const void* plane, int64_t M, int64_t K, con
         const long long tiles = mtiles * ((N + NT - 1) / NT) * batch;
         p.ws_counters = static_cast<unsigned int*>(workspace);
         p.ws_partial = reinterpret_cast<int32_t*>(static_cast<char*>(workspace) + counter_bytes(tiles));
+    } else if (s == 1 && workspace && aligned(workspace, 256)) {
+        // optional: room for the pair kernel's exact work split
+        const size_t want = pair_balance_workspace_bytes(M, N, K, batch);
+        if (want && workspace_bytes >= want) {
+            p.ws_counters = static_cast<unsigned int*>(workspace);
+            p.ws_partial = reinterpret_cast<int32_t*>(static_cast<char*>(workspace) + 65536);
+        }
     }
     return launch_gemm((cudaStream_t)stream, p, acts, bgemm_act_ld(K), batch);
 }

@@ -15,7 +15,12 @@ struct TileOut {
     const float* s_alpha;    // [128] per-row scale of this tile (1 when unused)
     const int* s_colsum;     // [NT] column sums of this tile (0 when unused)
     int batch, m_base, n_base;
+    bool streaming = false;  // results are written with streaming stores (first out of L2): for kernels that keep other data there
 };
+__device__ __forceinline__ void store16B(void* dst, const uint4& v, bool streaming) {
+    if (streaming) __stcs(reinterpret_cast<uint4*>(dst), v);
+    else *reinterpret_cast<uint4*>(dst) = v;
+}
 
 // 8 consecutive rows m0..m0+7 (tile-local) of column n (tile-local): the [N, M] layout.
 __device__ __forceinline__ void store8_rows(const TileOut& t, int n, int m0, const int (&acc)[8]) {
@@ -33,8 +38,8 @@ __device__ __forceinline__ void store8_rows(const TileOut& t, int n, int m0, con
         auto put = [&](void* base) {
             int* o = reinterpret_cast<int*>(base) + idx;
             if (full && (reinterpret_cast<uintptr_t>(o) & 15) == 0) {
-                reinterpret_cast<int4*>(o)[0] = make_int4(val[0], val[1], val[2], val[3]);
-                reinterpret_cast<int4*>(o)[1] = make_int4(val[4], val[5], val[6], val[7]);
+                store16B(o, make_uint4((uint32_t)val[0], (uint32_t)val[1], (uint32_t)val[2], (uint32_t)val[3]), t.streaming);
+                store16B(o + 4, make_uint4((uint32_t)val[4], (uint32_t)val[5], (uint32_t)val[6], (uint32_t)val[7]), t.streaming);
             } else {
 #pragma unroll
                 for (int q = 0; q < 8; q++) if (gm + q < p.M) o[q] = val[q];
@@ -52,7 +57,7 @@ __device__ __forceinline__ void store8_rows(const TileOut& t, int n, int m0, con
         auto put = [&](void* base) {
             __half* o = reinterpret_cast<__half*>(base) + idx;
             if (full && (reinterpret_cast<uintptr_t>(o) & 15) == 0) {
-                *reinterpret_cast<uint4*>(o) = *reinterpret_cast<const uint4*>(h);
+                store16B(o, *reinterpret_cast<const uint4*>(h), t.streaming);
             } else {
 #pragma unroll
                 for (int q = 0; q < 8; q++) if (gm + q < p.M) o[q] = h[q];
@@ -105,8 +110,8 @@ __device__ __forceinline__ void store8_cols(const TileOut& t, int m, int n0, con
         auto put = [&](void* base) {
             int* o = reinterpret_cast<int*>(base) + idx;
             if (full && (reinterpret_cast<uintptr_t>(o) & 15) == 0) {
-                reinterpret_cast<int4*>(o)[0] = make_int4(val[0], val[1], val[2], val[3]);
-                reinterpret_cast<int4*>(o)[1] = make_int4(val[4], val[5], val[6], val[7]);
+                store16B(o, make_uint4((uint32_t)val[0], (uint32_t)val[1], (uint32_t)val[2], (uint32_t)val[3]), t.streaming);
+                store16B(o + 4, make_uint4((uint32_t)val[4], (uint32_t)val[5], (uint32_t)val[6], (uint32_t)val[7]), t.streaming);
             } else {
 #pragma unroll
                 for (int q = 0; q < 8; q++) if (gn + q < p.N) o[q] = val[q];
@@ -123,7 +128,7 @@ __device__ __forceinline__ void store8_cols(const TileOut& t, int m, int n0, con
         auto put = [&](void* base) {
             __half* o = reinterpret_cast<__half*>(base) + idx;
             if (full && (reinterpret_cast<uintptr_t>(o) & 15) == 0) {
-                *reinterpret_cast<uint4*>(o) = *reinterpret_cast<const uint4*>(h);
+                store16B(o, *reinterpret_cast<const uint4*>(h), t.streaming);
             } else {
 #pragma unroll
                 for (int q = 0; q < 8; q++) if (gn + q < p.N) o[q] = h[q];

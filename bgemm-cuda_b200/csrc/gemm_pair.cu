@@ -2,25 +2,31 @@
 // a cluster -- the two SMs of a TPC -- compute one 256(M) x 256(N) tile together. Each CTA streams and unpacks ITS OWN
 // 128 weight rows into its own tensor memory and loads only HALF of the activation tile (128 of the 256 activation
 // rows) into its own shared memory; one thread of the even CTA issues a single 256 x 256 x 32 UMMA for both SMs, which
-// reads both halves. Against the 128-row kernels that halves the activation bytes an SM pulls from L2 per unit of
-// tensor work (36 KB per 1024 clocks of UMMA instead of 36 KB per 512) and halves the instructions, waits and commits
-// per unit of tensor work for the issuing threads -- the two walls those kernels run into.
+// reads both halves. Against the 128-row kernels each SM pulls half the activation bytes from L2 per unit of tensor
+// work (36 KB per 1024 clocks of UMMA instead of 36 KB per 512), the issuing thread spends one instruction per 128
+// clocks of tensor work instead of one per 64, and the tensor-memory stores of the unpacked weights -- which complete
+// only between the UMMAs of a K block, ~330 clocks per K block -- are paid once per 1024 clocks of UMMA, not per 512.
+//
+// Work split: the K blocks of all tiles form one sequence of units, and every cluster takes an equal, contiguous
+// range of it. With a workspace the ranges are cut exactly (a tile that straddles a boundary is accumulated in parts:
+// every cluster that stops inside a tile writes its partial accumulator to the workspace, the cluster that ends the
+// tile adds the parts and stores the result), so all SMs finish together whatever the number of tiles; without one
+// the ranges are rounded to whole tiles.
 //
 // Same math and operand formats as gemm_kernel (gemm_umma.cu) and gemm_persist_kernel; replaces the same reference
 // code (PACK_BGEMM_Kernel, lowbit_kernel/csrc/include/kernel_matmul.cuh:370-547).
 //
 // Tensor memory (all 512 columns, allocated by both CTAs together): one accumulator of 256 columns (each CTA holds
 // its 128 rows of the tile) and a ring of four u8 weight-operand stages of 64 columns.
-//   warps 0-7    unpack, two sets taking alternate K blocks of the CTA's whole K-block stream (as gemm_persist_kernel)
-//   warps 8-15   epilogue: warp w reads lane quadrant w % 4 of column half (w - 8) / 4 into an int16 staging tile, hands
-//                the accumulator back, then converts and stores under the next tile's mainloop
-//   warp 16      tensor-memory allocation; in the even CTA one lane issues the UMMAs of the even K blocks
-//   warp 19      in the even CTA one lane issues the UMMAs of the odd K blocks
-//   warp 17      one lane streams this CTA's packed weight tiles (cp.async.bulk)
-//   warp 18      one lane loads this CTA's half of the activation tiles (TMA, 128B swizzle); the bytes of both halves
+//   warps 0-15   unpack, four sets of four warps; set s takes the K blocks g of the CTA's stream with g % 4 == s
+//   warps 16-23  epilogue: warp w reads lane quadrant w % 4 of column half (w - 16) / 4 into an int16 staging tile, hands
+//                the accumulator back, then converts and stores under the next item's mainloop
+//   warp 24      tensor-memory allocation; in the even CTA one lane issues all UMMAs
+//   warp 25      one lane streams this CTA's packed weight tiles (cp.async.bulk)
+//   warp 26      one lane loads this CTA's half of the activation tiles (TMA, 128B swizzle); the bytes of both halves
 //                are counted on the even CTA's barrier
 // Signals across the pair: the odd CTA's unpack and epilogue warps arrive on the even CTA's barriers with plain
-// remote arrivals (no data crosses; every CTA loads what it needs itself); the issuers' commits arrive on the barrier
+// remote arrivals (no data crosses; every CTA loads what it needs itself); the issuer's commits arrive on the barrier
 // of the same name in both CTAs. Every wait is bounded as in the other kernels, and both CTAs meet in a cluster
 // barrier before either frees tensor memory or exits, so no signal is ever sent to a CTA that has left.
 #include <cuda.h>
@@ -35,9 +41,13 @@
 
 namespace bgemm {
 
-constexpr int kQThreads = 640;
+// Unpack sets of four warps; set s takes the K blocks g with g % kQSets == s, i.e. always the same operand stage. A set
+// needs ~2100 clocks per K block (its tensor-memory stores complete only between UMMAs), a K block of UMMAs 1024: two
+// sets leave the tensor pipe waiting (28672 x 8192 x 4096: 656 us), four do not (580 us).
+constexpr int kQSets = 4;
 constexpr int kQEpiThreads = 256;
-constexpr int kQWarpEpi = 8, kQWarpMma0 = 16, kQWarpW = 17, kQWarpB = 18, kQWarpMma1 = 19;
+constexpr int kQWarpEpi = 4 * kQSets, kQWarpMma = kQWarpEpi + 8, kQWarpW = kQWarpMma + 1, kQWarpB = kQWarpMma + 2;
+constexpr int kQThreads = 32 * (kQWarpB + 1);
 constexpr long long kQCopyDrainClocks = 4000000;   // ~2 ms: far beyond any TMA copy of a 32 KB tile
 
 struct QCfg {
@@ -47,25 +57,160 @@ struct QCfg {
     static constexpr int A_COL0 = NT;
     static constexpr int B_HALF_ROWS = NT / 2;              // activation rows this CTA loads
     static constexpr int B_STAGE_BYTES = B_HALF_ROWS * 256;
-    static constexpr int W_STAGES = 6;
-    static constexpr int STAGE_TILE_BYTES = 128 * NT * 2;   // this CTA's 128 x 256 accumulator as int16
-    // w_full/w_empty, full/empty, d_full, d_empty, first_done, drained
-    static constexpr int NBARS = 2 * W_STAGES + 2 * STAGES + 4;
+    static constexpr int W_STAGES = kQSets == 4 ? 4 : 6;
+    static constexpr int ROW_PITCH = 68;                    // words per row of a half in the row-major ([M, N] results) staging: 64 + 4
+    static constexpr int HALF_WORDS = 128 * ROW_PITCH;      // staging words of one column half (>= 64 x 128 of the column-major form)
+    static constexpr int STAGE_TILE_BYTES = 2 * HALF_WORDS * 4;   // this CTA's 128 x 256 accumulator as int16 pairs
+    static constexpr int PART_INTS = 128 * NT;              // a CTA's partial accumulator in the workspace
+    // w_full/w_empty, full/empty, d_full, d_empty, drained
+    static constexpr int NBARS = 2 * W_STAGES + 2 * STAGES + 3;
     static constexpr int MISC_BYTES = 512 /*barriers*/ + 512 /*alpha*/ + 1024 /*colsum*/ + 512 /*flags*/;
     static constexpr int SMEM_BYTES = STAGES * B_STAGE_BYTES + W_STAGES * 4096 + STAGE_TILE_BYTES + MISC_BYTES + 1024 /*align*/;
-    static_assert(W_STAGES % 2 == 0 && STAGES % 2 == 0, "stage -> unpack set / issuer must stay fixed");
+    static_assert(W_STAGES % kQSets == 0 && STAGES % kQSets == 0, "stage -> unpack set must stay fixed");
     static_assert(NT + STAGES * A_STAGE_COLS <= 512, "tensor memory budget");
     static_assert(NBARS * 8 <= 512, "barrier area");
     static_assert(SMEM_BYTES <= 227 * 1024, "shared memory budget");
     static_assert(SMEM_BYTES > 114 * 1024, "one CTA per SM");
 };
 
-// The issuers' signal to both CTAs of the pair: one commit whose arrival is delivered to the barrier at the same
+// The issuer's signal to both CTAs of the pair: one commit whose arrival is delivered to the barrier at the same
 // offset in each of them.
 __device__ __forceinline__ void commit_both(uint32_t bar) { umma_commit_pair_mask(bar, (uint16_t)3); }
 
+// First unit (K block of the global sequence) of cluster c. Exact split: c * units / ncl; whole-tile split: the same on
+// tiles. Both are monotonic with range(0) = 0 and range(ncl) = everything.
+__device__ __forceinline__ long long pair_range_begin(long long c, long long ncl, long long total_tiles, int nkb, int exact) {
+    return exact ? (c * total_tiles * nkb) / ncl : ((c * total_tiles) / ncl) * nkb;
+}
+
+// fp16 results of 8 adjacent columns (n0 .. n0 + 7) of row m of the [M, N] layout; same values as store8_cols.
+__device__ __forceinline__ void store_row8_f16(const TileOut& t, int m, int n0, const int (&acc)[8]) {
+    const GemmParams& p = *t.p;
+    const int gm = t.m_base + m, gn = t.n_base + n0;
+    if (gm >= p.M || gn >= p.N) return;
+    const bool full = gn + 8 <= p.N;
+    const int4 c0 = *reinterpret_cast<const int4*>(t.s_colsum + n0), c1 = *reinterpret_cast<const int4*>(t.s_colsum + n0 + 4);
+    const int cs[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+    int big = 0;
+#pragma unroll
+    for (int q = 0; q < 8; q++) big |= abs(cs[q]);
+    const bool small = big < (1 << 21);
+    const float a = t.s_alpha[m];
+    float f[8];
+#pragma unroll
+    for (int q = 0; q < 8; q++) {
+        const int val = p.epi ? cs[q] - 2 * acc[q] : acc[q];
+        f[q] = small ? __int_as_float(0x4B400000 + val) - 12582912.f : (float)val;
+        if (p.out_kind == BGEMM_OUT_F16_SCALED) f[q] *= a;
+    }
+    __align__(16) __half2 h2[4];
+#pragma unroll
+    for (int q = 0; q < 4; q++) h2[q] = __floats2half2_rn(f[2 * q], f[2 * q + 1]);
+    const size_t idx = (size_t)t.batch * p.M * p.N + (size_t)gm * p.ldo + gn;
+    auto put = [&](void* base) {
+        __half* o = reinterpret_cast<__half*>(base) + idx;
+        if (full && (reinterpret_cast<uintptr_t>(o) & 15) == 0) {
+            store16B(o, *reinterpret_cast<const uint4*>(h2), t.streaming);
+        } else {
+            const __half* hs = reinterpret_cast<const __half*>(h2);
+#pragma unroll
+            for (int q = 0; q < 8; q++) if (gn + q < p.N) o[q] = hs[q];
+        }
+    };
+    put(p.out);
+#pragma unroll 1
+    for (int d = 0; d < p.n_out_more; d++) put(p.out_more[d]);
+}
+
+// fp16 results of two adjacent columns (n, n + 1) x 8 rows (m0 .. m0 + 7) of the [N, M] layout from 8 staged int16
+// pairs: the same values as store8_rows produces (exact int -> float, one rounding in the multiply, round-to-nearest-
+// even to fp16), with conversions that stay off the slow conversion pipe -- int -> float by adding the integer to the
+// bit pattern of 1.5 * 2^23 (exact below 2^22; larger column sums take the ordinary conversion) and two floats -> half2
+// in one instruction.
+__device__ __forceinline__ void store2cols_f16(const TileOut& t, int n, int m0, const uint32_t (&wv)[8]) {
+    const GemmParams& p = *t.p;
+    const int gm = t.m_base + m0;
+    if (gm >= p.M) return;
+    const bool full = gm + 8 <= p.M;
+    float al[8];
+    if (p.out_kind == BGEMM_OUT_F16_SCALED) {
+        const float4 a0 = *reinterpret_cast<const float4*>(t.s_alpha + m0), a1 = *reinterpret_cast<const float4*>(t.s_alpha + m0 + 4);
+        al[0] = a0.x; al[1] = a0.y; al[2] = a0.z; al[3] = a0.w; al[4] = a1.x; al[5] = a1.y; al[6] = a1.z; al[7] = a1.w;
+    } else {
+#pragma unroll
+        for (int q = 0; q < 8; q++) al[q] = 1.f;
+    }
+#pragma unroll
+    for (int c = 0; c < 2; c++) {
+        const int gn = t.n_base + n + c;
+        if (gn >= p.N) break;
+        const int cs = t.s_colsum[n + c];
+        float f[8];
+        const bool small = cs > -(1 << 21) && cs < (1 << 21);
+#pragma unroll
+        for (int q = 0; q < 8; q++) {
+            const int v = c ? ((int)wv[q] >> 16) : (int)(short)(wv[q] & 0xffffu);
+            const int val = p.epi ? cs - 2 * v : v;
+            f[q] = small ? __int_as_float(0x4B400000 + val) - 12582912.f : (float)val;
+            if (p.out_kind == BGEMM_OUT_F16_SCALED) f[q] *= al[q];
+        }
+        __align__(16) __half2 h2[4];
+#pragma unroll
+        for (int q = 0; q < 4; q++) h2[q] = __floats2half2_rn(f[2 * q], f[2 * q + 1]);
+        const size_t idx = (size_t)t.batch * p.M * p.N + (size_t)gn * p.ldo + gm;
+        auto put = [&](void* base) {
+            __half* o = reinterpret_cast<__half*>(base) + idx;
+            if (full && (reinterpret_cast<uintptr_t>(o) & 15) == 0) {
+                store16B(o, *reinterpret_cast<const uint4*>(h2), t.streaming);
+            } else {
+                const __half* hs = reinterpret_cast<const __half*>(h2);
+#pragma unroll
+                for (int q = 0; q < 8; q++) if (gm + q < p.M) o[q] = hs[q];
+            }
+        };
+        put(p.out);
+#pragma unroll 1
+        for (int d = 0; d < p.n_out_more; d++) put(p.out_more[d]);
+    }
+}
+
+// The items of a cluster's range [u0, u1), in the order it works through them: a tile's K blocks that belong to one
+// cluster form one item. Parts of a tile that stop before its last K block are handed over through the workspace and
+// come FIRST (at most one per cluster: the head of the range's last tile, or a range that lies inside one tile); the
+// part that ends a tile begun by other clusters comes after the first whole tile and adds their parts, which were
+// written as those clusters' first items -- a tile's time earlier at the least; the other whole tiles follow. So
+// nobody waits for work that is scheduled late, the partial sums are read back while they are still in L2, and every
+// cluster ends on a whole tile.
+struct PairItems {
+    long long ta, tb;     // first and last tile of the range
+    int a, b;             // first K block of the range in tile ta, end K block in tile tb
+    int nkb, has_head, has_tail, n;
+    __device__ __forceinline__ PairItems(long long u0, long long u1, int nkb_) : nkb(nkb_) {
+        ta = u0 / nkb; a = (int)(u0 - ta * nkb);
+        tb = (u1 - 1) / nkb; b = (int)(u1 - tb * nkb);
+        if (u1 <= u0) { has_head = has_tail = 0; n = 0; }
+        else if (ta == tb) { has_head = 1; has_tail = 0; n = 1; }                  // one item; "head" slot whatever its kind
+        else {
+            has_head = b < nkb ? 1 : 0;
+            has_tail = a > 0 ? 1 : 0;
+            n = has_head + has_tail + (int)(tb - ta + 1 - has_head - has_tail);
+        }
+    }
+    __device__ __forceinline__ void get(int idx, long long& t, int& kb0, int& kb1) const {
+        if (ta == tb) { t = ta; kb0 = a; kb1 = b; return; }
+        if (idx < has_head) { t = tb; kb0 = 0; kb1 = b; return; }
+        idx -= has_head;
+        const int n_full = n - has_head - has_tail;
+        // one whole tile (if there is one) before the part that needs other clusters' sums: by then they are written
+        const int tail_at = n_full > 0 ? 1 : 0;
+        if (has_tail && idx == tail_at) { t = ta; kb0 = a; kb1 = nkb; return; }
+        if (has_tail && idx > tail_at) idx--;
+        t = ta + has_tail + idx; kb0 = 0; kb1 = nkb;
+    }
+};
+
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kQThreads, 1)
-gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_acts, const GemmParams p, const long long total_tiles) {
+gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_acts, const GemmParams p, const long long total_tiles, const int exact) {
     using C = QCfg;
     constexpr int NT = C::NT;
     BGEMM_TUNING_ONLY(const long long t_cta0 = clock64();)
@@ -87,18 +232,20 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_acts, const GemmParams
     const uint32_t w_empty = w_full + 8 * C::W_STAGES;
     const uint32_t full = w_empty + 8 * C::W_STAGES;     // [S] even CTA only: operand stage filled in BOTH CTAs
     const uint32_t empty = full + 8 * C::STAGES;         // [S] both CTAs: operand stage consumed (one commit)
-    const uint32_t d_full = empty + 8 * C::STAGES;       // both CTAs: accumulator complete (one commit per issuer)
+    const uint32_t d_full = empty + 8 * C::STAGES;       // both CTAs: accumulator complete (one commit)
     const uint32_t d_empty = d_full + 8;                 // even CTA only: accumulator read out by the epilogue warps of both CTAs
-    const uint32_t first_done = d_empty + 8;             // even CTA only: the K block that zeroes the accumulator has been executed
-    const uint32_t drained = first_done + 8;             // both CTAs: every UMMA of the pair has been executed
+    const uint32_t drained = d_empty + 8;                // both CTAs: every UMMA of the pair has been executed
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const uint32_t rank = cluster_ctarank();             // 0: the CTA that issues the UMMAs and owns the "filled" barriers
     const bool leader = rank == 0;
     const int nkb = p.kblocks;
     const long long cid = blockIdx.x >> 1, ncl = gridDim.x >> 1;
-    // pair tiles of this cluster: cid, cid + ncl, ... (pair tile index = (batch * (mtiles / 2) + mt / 2) * ntiles + nt)
-    const long long my_tiles = cid < total_tiles ? (total_tiles - cid + ncl - 1) / ncl : 0;
+    // units of this cluster: [u0, u1) of the sequence (tile 0: K blocks 0 .. nkb - 1, tile 1: ..., ...);
+    // tile index = (batch * (mtiles / 2) + mt / 2) * ntiles + nt
+    const long long u0 = pair_range_begin(cid, ncl, total_tiles, nkb, exact);
+    const long long u1 = pair_range_begin(cid + 1, ncl, total_tiles, nkb, exact);
+    const PairItems items(u0, u1, nkb);
     const int mpairs = p.mtiles >> 1;
     // the even CTA's barriers as seen from either CTA
     const uint32_t full_leader = mapa_shared(full, 0);
@@ -110,16 +257,14 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_acts, const GemmParams
             int count = 1;
             if (i >= C::W_STAGES && i < 2 * C::W_STAGES) count = 4;           // w_empty: unpack warps of a set
             else if (i >= f0 && i < f0 + C::STAGES) count = 9;                // full: activation producer + unpack warps of a set in both CTAs
-            else if (i == d0) count = 2;                                      // d_full: both issuers
             else if (i == d0 + 1) count = 16;                                 // d_empty: epilogue warps of both CTAs
-            else if (i == d0 + 3) count = 2;                                  // drained: both issuers
             mbar_init(w_full + 8 * i, count);
         }
         if (lane == 0) { *abort_flag = 0; set_wait_budget(abort_flag, p.wait_budget); }
         mbar_fence_init();
     } else if (warp == kQWarpB) {
         if (lane == 0) tma_prefetch_desc(&tmap_acts);
-    } else if (warp == kQWarpMma0) {
+    } else if (warp == kQWarpMma) {
         tmem_alloc_pair(smem_u32(tmem_holder), 512);
     }
     tc_fence_before();
@@ -138,11 +283,13 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_acts, const GemmParams
         if (lane == 0) {
             long long g = 0;
             bool ok = true;
-            for (long long t = cid; t < total_tiles && ok; t += ncl) {
+            for (int item = 0; item < items.n && ok; item++) {
+                long long t; int kb0, kb1;
+                items.get(item, t, kb0, kb1);
                 const long long bm = t / p.ntiles;                      // batch * mpairs + pair row
                 const int mt = 2 * (int)(bm % mpairs) + (int)rank, batch = (int)(bm / mpairs);
                 const uint8_t* src = p.plane + (size_t)batch * p.plane_batch_bytes + (size_t)mt * nkb * 4096;
-                for (int i = 0; i < nkb; i++, g++) {
+                for (int i = kb0; i < kb1; i++, g++) {
                     const int s = (int)(g % C::W_STAGES);
                     if (g >= C::W_STAGES) ok = mbar_wait_relaxed(w_empty + 8 * s, (uint32_t)((g / C::W_STAGES) - 1) & 1, abort_flag, p.status, 41);
                     if (!ok) break;
@@ -163,16 +310,18 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_acts, const GemmParams
         if (lane == 0) {
             long long g = 0;
             bool ok = true;
-            for (long long t = cid; t < total_tiles && ok; t += ncl) {
+            for (int item = 0; item < items.n && ok; item++) {
+                long long t; int kb0, kb1;
+                items.get(item, t, kb0, kb1);
                 const int nt = (int)(t % p.ntiles);
                 const int batch = (int)(t / p.ntiles / mpairs);
                 const int row0 = nt * NT + (int)rank * C::B_HALF_ROWS;
-                for (int i = 0; i < nkb; i++, g++) {
+                for (int i = kb0; i < kb1; i++, g++) {
                     const int s = (int)(g % C::STAGES);
                     if (g >= C::STAGES) ok = mbar_wait_relaxed(empty + 8 * s, (uint32_t)((g / C::STAGES) - 1) & 1, abort_flag, p.status, 42);
                     if (!ok) break;
-                    // one arrival for the pair, announcing the bytes of both halves
                     BGEMM_TRACE(4, g);
+                    // one arrival for the pair, announcing the bytes of both halves
                     if (leader) mbar_arrive_expect_tx(full + 8 * s, 2 * C::B_STAGE_BYTES);
                     const uint32_t dst = smem_u32(sB + s * C::B_STAGE_BYTES);
                     tma_load_3d_pair(dst, &tmap_acts, i * 256, row0, batch, full_leader + 8 * s);
@@ -186,34 +335,23 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_acts, const GemmParams
                 while (g > 0 && clock64() - t0 < kQCopyDrainClocks) {}
             }
         }
-    } else if (warp == kQWarpMma0 || warp == kQWarpMma1) {
-        // ---------------- UMMA issuers (even CTA): issuer `me` takes the K blocks with g % 2 == me ----------------
-        const int me = warp == kQWarpMma0 ? 0 : 1;
+    } else if (warp == kQWarpMma) {
+        // ---------------- UMMA issuer (even CTA) ----------------
+        // A 256 x 256 x 32 UMMA keeps both tensor pipes busy for 128 clocks and costs its issuer ~85, so one thread is
+        // enough; it also makes the hand-over of the single accumulator trivial: the first K block of an item
+        // (accumulate = 0) is issued once the epilogue warps of both CTAs have read the previous item out.
         if (lane == 0 && leader) {
             constexpr uint32_t idesc = umma_idesc_u8s8_m(NT, 256);
             bool ok = true;
             long long g = 0;
-            for (long long lt = 0; lt < my_tiles && ok; lt++) {
-                // The first K block of a tile overwrites the accumulator (accumulate = 0). Its issuer (the "opener",
-                // whoever owns that K block) waits until the epilogue warps of both CTAs have read the previous tile
-                // out; the other issuer waits until that K block has been executed before it adds anything. Integer
-                // accumulation commutes, so no other order is needed. Parity waits never name a phase their barrier
-                // has not reached -- the argument is the one in gemm_persist_kernel with a single accumulator buffer:
-                // d_empty phase lt - 2 was awaited by the opener of tile lt - 1, and the other issuer waited for that
-                // tile to be opened; first_done phase lt - 1 was either awaited by this thread or committed by it
-                // before it reused one of its operand stages (odd K-block counts are only launched with at least
-                // STAGES K blocks per tile).
-                const bool opener = (int)(g & 1) == me;
-                if (opener) {
-                    if (lt >= 1) ok = mbar_wait(d_empty, (uint32_t)(lt - 1) & 1, abort_flag, p.status, 45);
-                } else {
-                    ok = mbar_wait(first_done, (uint32_t)lt & 1, abort_flag, p.status, 46);
-                }
+            for (int item = 0; item < items.n && ok; item++) {
+                long long t; int kb0, kb1;
+                items.get(item, t, kb0, kb1);
+                if (item >= 1) ok = mbar_wait(d_empty, (uint32_t)(item - 1) & 1, abort_flag, p.status, 45);
                 if (!ok) break;
-                if (opener) BGEMM_TRACE(7, lt);
+                BGEMM_TRACE(7, item);
                 tc_fence_after();
-                for (int i = 0; i < nkb; i++, g++) {
-                    if ((int)(g & 1) != me) continue;
+                for (int i = kb0; i < kb1; i++, g++) {
                     const int s = (int)(g % C::STAGES);
                     ok = mbar_wait(full + 8 * s, (uint32_t)(g / C::STAGES) & 1, abort_flag, p.status, 43);
                     if (!ok) break;
@@ -224,9 +362,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_acts, const GemmParams
                     for (int j = 0; j < 8; j++) {
                         // the same descriptor is applied in both CTAs: rows 0-127 of B here, rows 128-255 in the partner
                         const uint64_t bdesc = umma_desc_sw128(bbase + (j >> 2) * (C::B_HALF_ROWS * 128) + (j & 3) * 32);
-                        umma_i8_ts_pair(tmem_d, tmem_a + s * C::A_STAGE_COLS + j * 8, bdesc, idesc, (i | j) ? 1u : 0u);
+                        umma_i8_ts_pair(tmem_d, tmem_a + s * C::A_STAGE_COLS + j * 8, bdesc, idesc, (i > kb0 || j) ? 1u : 0u);
                     }
-                    if (i == 0) umma_commit_pair(first_done);
                     commit_both(empty + 8 * s);
                     BGEMM_TRACE(1, g);
                 }
@@ -235,18 +372,14 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_acts, const GemmParams
             }
             commit_both(drained);
         }
-    } else if (warp < 8) {
-        // ---------------- unpack: set 0 = warps 0-3 takes even K blocks of the stream, set 1 = warps 4-7 odd ones ----
+    } else if (warp < 4 * kQSets) {
+        // ---------------- unpack: set s = warps 4 s .. 4 s + 3 takes the K blocks g of the stream with g % kQSets == s ----
         const int set = warp >> 2;
         const int r = (warp & 3) * 32 + lane;                 // weight row of this CTA's half tile == tensor-memory lane
         const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
-        const long long total_kb = my_tiles * nkb;
+        const long long total_kb = u1 - u0;
         bool ok = true;
-        // The tensor-memory stores of a K block take ~1000 clocks to complete while the UMMAs keep the memory busy, so
-        // their completion (tcgen05.wait::st, then the "filled" arrival) is deferred until the weights of the set's
-        // NEXT K block have been fetched from shared memory: `pend` is the stage whose stores are still in flight.
-        int pend = -1;
-        for (long long g = set; g < total_kb && ok; g += 2) {
+        for (long long g = set; g < total_kb && ok; g += kQSets) {
             const int ws = (int)(g % C::W_STAGES);
             ok = mbar_wait(w_full + 8 * ws, (uint32_t)(g / C::W_STAGES) & 1, abort_flag, p.status, 47);
             ok = __all_sync(0xffffffffu, ok);
@@ -257,17 +390,10 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_acts, const GemmParams
             __syncwarp();
             if (lane == 0) mbar_arrive(w_empty + 8 * ws);
             const uint32_t w[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
-            if (pend >= 0) {              // the previous K block of this set is complete in tensor memory
-                tmem_wait_st();
-                tc_fence_before();
-                __syncwarp();
-                if (lane == 0) mbar_arrive_cluster(full_leader + 8 * pend);
-                if ((tid & 127) == 0) BGEMM_TRACE(3, g - 2);
-            }
             const int as = (int)(g % C::STAGES);
             if (g >= C::STAGES) ok = mbar_wait_relaxed(empty + 8 * as, (uint32_t)((g / C::STAGES) - 1) & 1, abort_flag, p.status, 48);
             ok = __all_sync(0xffffffffu, ok);
-            if (!ok) { pend = -1; break; }
+            if (!ok) break;
             if ((tid & 127) == 0) BGEMM_TRACE(2, g);
             tc_fence_after();
 #pragma unroll
@@ -277,101 +403,173 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_acts, const GemmParams
                 for (int c = 0; c < 8; c++) v[c] = (w[c] >> j) & 0x01010101u;
                 tmem_st8(tmem_a + lane_base + as * C::A_STAGE_COLS + j * 8, v);
             }
-            if ((tid & 127) == 0) BGEMM_TRACE(5, g);
-            pend = as;
-        }
-        tmem_wait_st();                   // (also on the way out after a wait ran out: no store is left in flight)
-        if (pend >= 0) {
+            tmem_wait_st();
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive_cluster(full_leader + 8 * pend);
+            if (lane == 0) mbar_arrive_cluster(full_leader + 8 * as);
+            if ((tid & 127) == 0) BGEMM_TRACE(3, g);
         }
     } else if (warp >= kQWarpEpi && warp < kQWarpEpi + 8) {
         // ---------------- epilogue: this CTA's 128 rows of the tile, columns [128 h, 128 h + 128) per half h ----------------
         // The single accumulator must be handed back quickly: the warps first move it into a shared-memory staging tile
         // as int16 pairs (64 KB; |D| <= K for ternary and binary activations), release it, and only then convert and
-        // store -- under the next tile's mainloop. A half whose values do not fit 16 bits (general int8 activations)
+        // store -- under the next item's mainloop. A half whose values do not fit 16 bits (general int8 activations)
         // keeps the accumulator and converts straight from tensor memory through a small int32 tile aliased on its
         // part of the staging area.
+        // Items that cover only part of a tile's K range (see PairItems): an item that stops before the tile's last K
+        // block writes its accumulator to this CTA's slot of the workspace and raises the slot's flag; the item that
+        // ends a tile begun by other clusters waits for their flags (they took those items FIRST), adds their slots
+        // while it reads its own accumulator, and clears the flags for the next launch.
         const int h = (warp - kQWarpEpi) >> 2;
         const int et = (warp & 3) * 32 + lane;                // accumulator row == tensor-memory lane
         const int eall = h * 128 + et;
         const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
-        uint32_t* sS = reinterpret_cast<uint32_t*>(sP) + h * (64 * 128);      // [64 column pairs][128 rows] of this half
+        // staging of this half: [64 column pairs][128 rows] for [N, M] results (a column's rows are contiguous in the
+        // result), [128 rows][68] for [M, N] results (a row's columns are)
+        uint32_t* sS = reinterpret_cast<uint32_t*>(sP) + h * C::HALF_WORDS;
+        const bool rowmajor = p.out_layout == BGEMM_LAYOUT_MN;
         TileOut tout;
         tout.p = &p; tout.s_alpha = s_alpha; tout.s_colsum = s_colsum;
-        long long lt = 0;
-        for (long long t = cid; t < total_tiles; t += ncl, lt++) {
+        // with the exact split the partial sums must survive in L2 from the kernel's first item to its last: results stream out
+        tout.streaming = exact != 0;
+        const uint64_t keep = l2_policy_evict_last();
+        for (int item = 0; item < items.n; item++) {
+            long long t; int kb0, kb1;
+            items.get(item, t, kb0, kb1);
             const int nt = (int)(t % p.ntiles);
             const long long bm = t / p.ntiles;
             const int mt = 2 * (int)(bm % mpairs) + (int)rank, batch = (int)(bm / mpairs);
+            const bool writes_part = kb1 < nkb;
+            // clusters cid - 1 .. cid - nparts computed the earlier K blocks of this tile (each as its first item)
+            int nparts = 0;
+            if (kb1 == nkb && kb0 > 0)
+                while (cid - 1 - nparts >= 0 && pair_range_begin(cid - nparts, ncl, total_tiles, nkb, exact) > t * nkb) nparts++;
             tout.batch = batch; tout.m_base = mt * 128; tout.n_base = nt * NT;
-            if (h == 0) {
-                const int m = mt * 128 + et;
-                s_alpha[et] = (p.out_kind == BGEMM_OUT_F16_SCALED && m < p.M) ? __half2float(p.alpha[(size_t)batch * p.M + m]) : 1.f;
-            }
-            {
+            if (!writes_part) {
+                if (h == 0) {
+                    const int m = mt * 128 + et;
+                    s_alpha[et] = (p.out_kind == BGEMM_OUT_F16_SCALED && m < p.M) ? __half2float(p.alpha[(size_t)batch * p.M + m]) : 1.f;
+                }
                 const int n = nt * NT + eall;
                 s_colsum[eall] = (p.epi && n < p.N) ? __ldg(p.colsum + (size_t)batch * p.N + n) : 0;
             }
-            bool ok = mbar_wait_relaxed(d_full, (uint32_t)lt & 1, abort_flag, p.status, 49);
+            bool ok = mbar_wait_relaxed(d_full, (uint32_t)item & 1, abort_flag, p.status, 49);
+            if (ok && nparts > 0 && eall == 0) {
+                // bounded wait for the continuing clusters' partial sums (flags live in the zero-initialised counter area)
+                const long long t0 = clock64(), budget = wait_budget_of(abort_flag);
+                for (int q = 0; q < nparts && ok; q++) {
+                    volatile unsigned int* f = p.ws_counters + 2 * (cid - 1 - q) + rank;
+                    while (*f == 0u) {
+                        if (*abort_flag || clock64() - t0 > budget) {
+                            *abort_flag = 1;
+                            if (p.status) atomicCAS(p.status, 0, 50);
+                            ok = false;
+                            break;
+                        }
+                        __nanosleep(100);
+                    }
+                }
+                __threadfence();
+            }
             ok = __all_sync(0xffffffffu, ok);
-            // One answer for all eight warps (either everybody stores this tile or everybody leaves); the barrier also
-            // makes this tile's scales and column sums visible to all of them.
+            // One answer for all eight warps (either everybody handles this item or everybody leaves); the barrier also
+            // makes this tile's scales and column sums, and the other clusters' partial sums, visible to all of them.
             if (named_bar_or(2, kQEpiThreads, !ok)) break;
-            if (warp == kQWarpEpi && lane == 0) BGEMM_TRACE(6, lt * 4);
+            if (warp == kQWarpEpi && lane == 0) BGEMM_TRACE(6, item * 4);
             tc_fence_after();
+            // this thread's 32 accumulator values of columns h * 128 + c0 .. + 31, plus the other clusters' parts
+            auto load32 = [&](int c0, uint32_t (&v0)[16], uint32_t (&v1)[16]) {
+                tmem_ld16(tmem_d + lane_base + h * 128 + c0, v0);
+                tmem_ld16(tmem_d + lane_base + h * 128 + c0 + 16, v1);
+                tmem_wait_ld();
+                for (int q = 0; q < nparts; q++) {
+                    const int* part = p.ws_partial + (size_t)(2 * (cid - 1 - q) + rank) * C::PART_INTS + (h * 128 + c0) * 128 + et;
+#pragma unroll
+                    for (int i = 0; i < 16; i++) v0[i] += (uint32_t)ld_global_hint(part + i * 128, keep);
+#pragma unroll
+                    for (int i = 0; i < 16; i++) v1[i] += (uint32_t)ld_global_hint(part + (16 + i) * 128, keep);
+                }
+            };
+            auto release_accumulator = [&]() {
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive_cluster(d_empty_leader);
+                if (warp == kQWarpEpi && lane == 0) BGEMM_TRACE(6, item * 4 + 1);
+            };
+            if (writes_part) {
+                int* part = p.ws_partial + (size_t)(2 * cid + rank) * C::PART_INTS + (h * 128) * 128 + et;
+#pragma unroll 1
+                for (int c0 = 0; c0 < 128; c0 += 32) {
+                    uint32_t v0[16], v1[16];
+                    load32(c0, v0, v1);
+                    if (c0 + 32 >= 128) release_accumulator();
+#pragma unroll
+                    for (int i = 0; i < 16; i++) st_global_hint(part + (c0 + i) * 128, (int)v0[i], keep);
+#pragma unroll
+                    for (int i = 0; i < 16; i++) st_global_hint(part + (c0 + 16 + i) * 128, (int)v1[i], keep);
+                }
+                __threadfence();
+                named_bar_sync(7, kQEpiThreads);
+                if (eall == 0) {
+                    __threadfence();
+                    *(volatile unsigned int*)(p.ws_counters + 2 * cid + rank) = 1u;
+                }
+                continue;
+            }
             int lo16 = 0, hi16 = 0;                               // value range of this thread's part of the accumulator
 #pragma unroll 1
             for (int c0 = 0; c0 < 128; c0 += 32) {
                 uint32_t v0[16], v1[16];
-                tmem_ld16(tmem_d + lane_base + h * 128 + c0, v0);
-                tmem_ld16(tmem_d + lane_base + h * 128 + c0 + 16, v1);
-                tmem_wait_ld();
+                load32(c0, v0, v1);
 #pragma unroll
-                for (int q = 0; q < 16; q += 2) {
-                    lo16 = min(lo16, min((int)v0[q], (int)v0[q + 1])); hi16 = max(hi16, max((int)v0[q], (int)v0[q + 1]));
-                    sS[((c0 + q) >> 1) * 128 + et] = ((uint32_t)v0[q] & 0xffffu) | ((uint32_t)v0[q + 1] << 16);
+                for (int q = 0; q < 16; q++) { lo16 = min(lo16, min((int)v0[q], (int)v1[q])); hi16 = max(hi16, max((int)v0[q], (int)v1[q])); }
+                uint32_t w0[8], w1[8];
+#pragma unroll
+                for (int q = 0; q < 8; q++) {
+                    w0[q] = (v0[2 * q] & 0xffffu) | (v0[2 * q + 1] << 16);
+                    w1[q] = (v1[2 * q] & 0xffffu) | (v1[2 * q + 1] << 16);
                 }
+                if (rowmajor) {
+                    uint4* dst = reinterpret_cast<uint4*>(sS + et * C::ROW_PITCH + (c0 >> 1));
+                    dst[0] = make_uint4(w0[0], w0[1], w0[2], w0[3]); dst[1] = make_uint4(w0[4], w0[5], w0[6], w0[7]);
+                    dst[2] = make_uint4(w1[0], w1[1], w1[2], w1[3]); dst[3] = make_uint4(w1[4], w1[5], w1[6], w1[7]);
+                } else {
 #pragma unroll
-                for (int q = 0; q < 16; q += 2) {
-                    lo16 = min(lo16, min((int)v1[q], (int)v1[q + 1])); hi16 = max(hi16, max((int)v1[q], (int)v1[q + 1]));
-                    sS[((c0 + 16 + q) >> 1) * 128 + et] = ((uint32_t)v1[q] & 0xffffu) | ((uint32_t)v1[q + 1] << 16);
+                    for (int q = 0; q < 8; q++) { sS[((c0 >> 1) + q) * 128 + et] = w0[q]; sS[((c0 >> 1) + 8 + q) * 128 + et] = w1[q]; }
                 }
             }
             // One answer per half: did every value fit 16 bits? (The barrier also publishes the staging tile.)
             const bool wide = named_bar_or(3 + h, 128, lo16 < -32768 || hi16 > 32767);
             if (!wide) {
-                tc_fence_before();
-                __syncwarp();
-                if (lane == 0) mbar_arrive_cluster(d_empty_leader);
-                if (warp == kQWarpEpi && lane == 0) BGEMM_TRACE(6, lt * 4 + 1);
+                release_accumulator();
                 if (p.out_layout == BGEMM_LAYOUT_NM) {
                     // unit = (column pair, 8 rows): 16 lanes cover the 128 rows of a column, i.e. 256 contiguous bytes (fp16)
 #pragma unroll 1
-                    for (int u = et; u < 64 * 16; u += 128) {
-                        const int cp = u >> 4, m0 = (u & 15) * 8;
+                    for (int un = et; un < 64 * 16; un += 128) {
+                        const int cp = un >> 4, m0 = (un & 15) * 8;
                         const uint4 a = *reinterpret_cast<const uint4*>(sS + cp * 128 + m0);
                         const uint4 b = *reinterpret_cast<const uint4*>(sS + cp * 128 + m0 + 4);
                         const uint32_t wv[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
-                        int even[8], odd[8];
+                        if (p.out_kind != BGEMM_OUT_I32) {
+                            store2cols_f16(tout, h * 128 + 2 * cp, m0, wv);
+                        } else {
+                            int even[8], odd[8];
 #pragma unroll
-                        for (int q = 0; q < 8; q++) { even[q] = (int)(short)(wv[q] & 0xffffu); odd[q] = (int)wv[q] >> 16; }
-                        store8_rows(tout, h * 128 + 2 * cp, m0, even);
-                        store8_rows(tout, h * 128 + 2 * cp + 1, m0, odd);
+                            for (int q = 0; q < 8; q++) { even[q] = (int)(short)(wv[q] & 0xffffu); odd[q] = (int)wv[q] >> 16; }
+                            store8_rows(tout, h * 128 + 2 * cp, m0, even);
+                            store8_rows(tout, h * 128 + 2 * cp + 1, m0, odd);
+                        }
                     }
                 } else {
-                    // unit = (row, 8 columns): a lane owns a row
+                    // unit = (row, 8 columns): 16 lanes cover the 128 columns of a row, i.e. 256 contiguous bytes (fp16)
 #pragma unroll 1
-                    for (int u = et; u < 16 * 128; u += 128) {
-                        const int m = u & 127, cp0 = (u >> 7) * 4;
-                        int acc[8];
-#pragma unroll
-                        for (int q = 0; q < 4; q++) {
-                            const uint32_t wv = sS[(cp0 + q) * 128 + m];
-                            acc[2 * q] = (int)(short)(wv & 0xffffu); acc[2 * q + 1] = (int)wv >> 16;
-                        }
-                        store8_cols(tout, m, h * 128 + 2 * cp0, acc);
+                    for (int un = et; un < 128 * 16; un += 128) {
+                        const int m = un >> 4, cg = un & 15;
+                        const uint4 a = *reinterpret_cast<const uint4*>(sS + m * C::ROW_PITCH + cg * 4);
+                        const int acc[8] = {(int)(short)(a.x & 0xffffu), (int)a.x >> 16, (int)(short)(a.y & 0xffffu), (int)a.y >> 16,
+                                            (int)(short)(a.z & 0xffffu), (int)a.z >> 16, (int)(short)(a.w & 0xffffu), (int)a.w >> 16};
+                        if (p.out_kind != BGEMM_OUT_I32) store_row8_f16(tout, m, h * 128 + cg * 8, acc);
+                        else store8_cols(tout, m, h * 128 + cg * 8, acc);
                     }
                 }
             } else {
@@ -382,14 +580,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_acts, const GemmParams
                     const int n0 = h * 128 + c0;
                     uint32_t v0[16], v1[16];
                     named_bar_sync(5 + h, 128);                   // the tile is free (first round: the int16 pass is over)
-                    tmem_ld16(tmem_d + lane_base + n0, v0);
-                    tmem_ld16(tmem_d + lane_base + n0 + 16, v1);
-                    tmem_wait_ld();
-                    if (c0 + 32 >= 128) {
-                        tc_fence_before();
-                        __syncwarp();
-                        if (lane == 0) mbar_arrive_cluster(d_empty_leader);
-                    }
+                    load32(c0, v0, v1);
+                    if (c0 + 32 >= 128) release_accumulator();
 #pragma unroll
                     for (int q = 0; q < 16; q++) sPh[q * 128 + et] = (int)v0[q];
 #pragma unroll
@@ -398,8 +590,10 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_acts, const GemmParams
                     write_tile<false>(tout, sPh, 1, 0, n0, 32, et, 128);
                 }
             }
-            if (warp == kQWarpEpi && lane == 0) BGEMM_TRACE(6, lt * 4 + 2);
-            named_bar_sync(7, kQEpiThreads);                      // staging tile, scales and column sums are free for the next tile
+            if (warp == kQWarpEpi && lane == 0) BGEMM_TRACE(6, item * 4 + 2);
+            named_bar_sync(7, kQEpiThreads);                      // staging tile, scales and column sums are free for the next item
+            if (nparts > 0 && eall == 0)                          // every thread has read the parts: clear their flags for the next launch
+                for (int q = 0; q < nparts; q++) *(volatile unsigned int*)(p.ws_counters + 2 * (cid - 1 - q) + rank) = 0u;
         }
     }
     tc_fence_before();
@@ -407,7 +601,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_acts, const GemmParams
     // Both CTAs are done with each other's barriers and tensor memory before either frees it or exits.
     cluster_arrive_release();
     cluster_wait_acquire();
-    if (warp == kQWarpMma0) {
+    if (warp == kQWarpMma) {
         if (lane == 0) {   // every UMMA has been executed before the columns are freed (immediate unless a wait ran out)
             const long long t0 = clock64();
             while (!mbar_test(drained, 0) && clock64() - t0 < wait_budget_of(abort_flag)) {}
@@ -422,19 +616,30 @@ static int env_int_q(const char* name) {
     const char* e = std::getenv(name);
     return e ? std::atoi(e) : -1;
 }
+static int pair_forced() { static const int v = env_int_q("BGEMM_PAIR"); return v; }       // 0: never, 1: whenever the shape allows
 
 // Shapes the pair kernel takes: wide activation matrices (at least one full 256-column tile), an even number of
-// 128-row tiles, no K partitioning, K-block counts the issuers' hand-over protocol covers.
+// 128-row tiles, no K partitioning by the caller, no activation-producing epilogue.
 bool pair_supported(const GemmParams& p, long long batch) {
-    static const int forced = env_int_q("BGEMM_PAIR");       // 0: never, 1: whenever the shape allows
+    const int forced = pair_forced();
     if (forced == 0) return false;
-    if (p.split_k != 1 || (p.mtiles & 1) || p.N < QCfg::NT || p.out_kind == kOutActs) return false;
-    if (p.kblocks < 2 || !(p.kblocks % 2 == 0 || p.kblocks >= QCfg::STAGES)) return false;
-    if (p.test_skip_kblock >= 0 && forced != 1) return false;
+    if (p.split_k != 1 || (p.mtiles & 1) || p.N < QCfg::NT || p.out_kind == kOutActs || p.kblocks < 2) return false;
+    if (forced == 1) return true;
+    if (p.test_skip_kblock >= 0) return false;
+    // worth it when every pair of SMs gets at least one tile
     const long long tiles = (long long)(p.mtiles / 2) * ((p.N + QCfg::NT - 1) / QCfg::NT) * batch;
-    if (forced == 1) return tiles >= 1;
-    // worth it when the pairs have at least one round of tiles
     return tiles >= sm_count() / 2;
+}
+
+// Workspace with which the pair kernel cuts its work into exactly equal ranges: the 64 KiB counter area (flags; zeroed
+// once, left zero by every launch) and one partial accumulator per CTA. 0 when the shape would not use it.
+size_t pair_balance_workspace_bytes(long long M, long long N, long long K, long long batch) {
+    if (pair_forced() == 0) return 0;
+    const long long mtiles = (M + 127) / 128, kblocks = (K + 255) / 256;
+    if ((mtiles & 1) || N < QCfg::NT || kblocks < 2) return 0;
+    const long long tiles = (mtiles / 2) * ((N + QCfg::NT - 1) / QCfg::NT) * batch;
+    if (pair_forced() != 1 && tiles < sm_count() / 2) return 0;
+    return (size_t)65536 + (size_t)sm_count() * QCfg::PART_INTS * 4;
 }
 
 int launch_gemm_pair(cudaStream_t stream, const void* tensor_map, const GemmParams& p, long long batch) {
@@ -449,7 +654,16 @@ int launch_gemm_pair(cudaStream_t stream, const void* tensor_map, const GemmPara
         configured[dev] = true;
     }
     const long long total_tiles = (long long)(p.mtiles / 2) * p.ntiles * batch;
-    const long long clusters = total_tiles < sm_count() / 2 ? total_tiles : sm_count() / 2;
+    const long long units = total_tiles * p.kblocks;
+    const long long pairs = sm_count() / 2;
+    // exact ranges need the workspace and every cluster resident at once (a cluster waits for its successors' parts):
+    // one cluster per SM pair, at least four K blocks each
+    // -- and it pays when every cluster has at least a tile's worth of work and the tiles do not divide evenly anyway
+    int exact = (p.ws_partial && p.ws_counters && units >= 4 * pairs && total_tiles >= pairs && total_tiles % pairs != 0) ? 1 : 0;
+    if (pair_forced() == 1 && p.ws_partial && p.ws_counters && units >= 4 * pairs) exact = 1;      // tuning / tests: whenever possible
+    static const int no_exact = env_int_q("BGEMM_PAIR_EXACT");     // tuning override: 0 = whole tiles only
+    if (no_exact == 0) exact = 0;
+    const long long clusters = exact ? pairs : (total_tiles < pairs ? total_tiles : pairs);
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)(2 * clusters), 1, 1);
     cfg.blockDim = dim3(kQThreads, 1, 1);
@@ -462,7 +676,7 @@ int launch_gemm_pair(cudaStream_t stream, const void* tensor_map, const GemmPara
         cfg.attrs = attr;
         cfg.numAttrs = 1;
     }
-    const cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_pair_kernel, tmap, p, total_tiles);
+    const cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_pair_kernel, tmap, p, total_tiles, exact);
     count_launch();
     return (int)(e != cudaSuccess ? e : cudaGetLastError());
 }

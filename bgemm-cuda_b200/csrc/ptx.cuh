@@ -173,6 +173,23 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
         : "r"(taddr)
         : "memory");
 }
+// ---- L2 residency hints ------------------------------------------------------------------------------------------
+// Policy for data that is written early in a kernel and read back at its end (partial sums handed between CTAs): keep
+// it in L2 while the kernel streams its operands and results through.
+__device__ __forceinline__ uint64_t l2_policy_evict_last() {
+    uint64_t pol;
+    asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(pol));
+    return pol;
+}
+__device__ __forceinline__ void st_global_hint(int* addr, int v, uint64_t policy) {
+    asm volatile("st.global.L2::cache_hint.b32 [%0], %1, %2;" ::"l"(addr), "r"(v), "l"(policy) : "memory");
+}
+__device__ __forceinline__ int ld_global_hint(const int* addr, uint64_t policy) {
+    int v;
+    asm volatile("ld.global.L2::cache_hint.b32 %0, [%1], %2;" : "=r"(v) : "l"(addr), "l"(policy) : "memory");
+    return v;
+}
+
 // ---- CTA pairs (cta_group::2): one UMMA over the two SMs of a 2-CTA cluster -----------------------------------------
 // Both CTAs allocate (and free) the same tensor-memory columns together; each keeps its own 128 rows of A and D and
 // half of the B tile in its own shared memory, and one thread of the even CTA issues the instruction for both.
@@ -192,11 +209,23 @@ __device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t ncols
 __host__ __device__ constexpr uint32_t umma_idesc_u8s8_m(int n, int m) {
     return (2u << 4) | (0u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
 }
+// kind::i8 instruction descriptor with the operand signedness spelled out (0 = u8, 1 = s8), both operands K-major.
+__host__ __device__ constexpr uint32_t umma_idesc_i8(int a_signed, int b_signed, int n, int m) {
+    return (2u << 4) | ((uint32_t)a_signed << 7) | ((uint32_t)b_signed << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
 __device__ __forceinline__ void umma_i8_ts_pair(uint32_t tmem_d, uint32_t tmem_a, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
     asm volatile(
         "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
         "tcgen05.mma.cta_group::2.kind::i8 [%0], [%1], %2, %3, {%5, %6, %7, %8, %9, %10, %11, %12}, p;\n}\n" ::"r"(tmem_d),
         "r"(tmem_a), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(0), "r"(0), "r"(0), "r"(0), "r"(0), "r"(0), "r"(0), "r"(0)
+        : "memory");
+}
+// Both operands from shared memory (the same descriptors are applied in both CTAs of the pair).
+__device__ __forceinline__ void umma_i8_ss_pair(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::2.kind::i8 [%0], %1, %2, %3, {%5, %6, %7, %8, %9, %10, %11, %12}, p;\n}\n" ::"r"(tmem_d),
+        "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(0), "r"(0), "r"(0), "r"(0), "r"(0), "r"(0), "r"(0), "r"(0)
         : "memory");
 }
 // Arrival on `bar` (a shared::cluster address: this CTA's or the partner's barrier) once every UMMA this thread has

@@ -174,6 +174,11 @@ int bgemm_prepare_acts(void* stream, const void* src, int src_dtype, int64_t N, 
  *             Zero it once after allocating it; the library restores the part that must be zero
  *             (arrival counters in its first 64 KiB) before each call returns, so one buffer can serve
  *             calls of any shapes one after another on a stream.
+ *             Optional for wide activation matrices: given bgemm_gemm_balance_workspace_bytes() bytes (same rules: 256-byte
+ *             aligned, zeroed once, reusable), the kernel for N >= 256 splits its work into exactly equal parts per SM
+ *             pair -- tiles that straddle a boundary are accumulated in two places and summed through the workspace --
+ *             instead of whole tiles, which matters when the number of tiles is not a multiple of the SM pairs. The
+ *             results are the same bits (integer sums). One such workspace must not serve two calls that overlap on the GPU.
  *   batch     number of independent problems (A x V heads); problem i uses plane + i*plane_bytes,
  *             acts + i*N*act_ld, colsum + i*N, out + i*M*N elements, alpha + i*M.
  * Replaces bin_pack_linear_kernel + PACK_BGEMM_Kernel + SplitK_Reduction (see file header).           */
@@ -182,6 +187,8 @@ int bgemm_gemm(void* stream, const void* plane, int64_t M, int64_t K,
                int op, void* out, int out_kind, int out_layout, const void* alpha,
                int split_k, void* workspace, size_t workspace_bytes, int64_t batch);
 size_t bgemm_gemm_workspace_bytes(int64_t M, int64_t N, int64_t K, int split_k, int64_t batch);
+/* Size of the optional workspace described above; 0 when the call would not use one. No reference counterpart. */
+size_t bgemm_gemm_balance_workspace_bytes(int64_t M, int64_t N, int64_t K, int split_k, int64_t batch);
 
 /* bgemm_gemm with one promise added by the caller: `plane` was complete in device memory BEFORE the kernel that precedes
  * this call on `stream` was launched -- the normal case for inference, where weights are prepacked when the model is
