@@ -404,7 +404,9 @@ def run_head(cx: Ctx, args, sampler):
                 "peak": i8_peak if bf["bound"] == "tensor" else cx.peaks["hbm_gbs"], "unit": "TFLOP/s" if bf["bound"] == "tensor" else "GB/s",
                 "frac": bf["frac"], "traffic": NCU_TRAFFIC["head"] if cx.world == 1 else None, "peak_source": peak_source,
                 "frac_vs_i8_microbench": bf["tops"] / I8_MICROBENCH_TOPS, "i8_microbench_tops": I8_MICROBENCH_TOPS,
-                "kernel": "gemm_kernel<128> (tcgen05.mma kind::i8, A operand unpacked into tensor memory), one launch per layer shard",
+                "kernel": ("gemm_pair_kernel (tcgen05.mma.cta_group::2 kind::i8, 256 x 256 tiles on SM pairs, exact work split)"
+                           if B.lib.bgemm_gemm_balance_workspace_bytes(rows, N, K, 0, 1) else
+                           "gemm_kernel (tcgen05.mma kind::i8, A operand unpacked into tensor memory)") + ", one launch per layer shard",
                 "launch_us": launch_us, "ops_per_launch": pool.ops(), "bytes_alg_per_launch": pool.bytes_alg(),
                 "kernel_tops": bf["tops"], "kernel_gbs": bf["gbs"], "ops": "integer multiply-adds x 2"}
 
@@ -659,7 +661,8 @@ def run_sweep(cx: Ctx):
     # C5 at every N (the planes are the same pool; activations differ)
     layers5 = max(4, -(-int(1.5 * L2_BYTES) // B.plane_bytes(28672, 8192)))
     for n in (1, 2, 4, 8, 16, 128, 4096):
-        kern = "gemm_stream_kernel (mma.sync int8 from registers)" if n <= 16 else "gemm_kernel (tcgen05)"
+        kern = ("gemm_stream_kernel (mma.sync int8 from registers)" if n <= 16 else
+                "gemm_pair_kernel (tcgen05, cta_group::2)" if B.lib.bgemm_gemm_balance_workspace_bytes(28672, n, 8192, 0, 1) else "gemm_kernel (tcgen05)")
         out.append(sweep_entry(cx, f"c5n{n}", Pool(cx, 28672, 8192, n, "bwta", layers5, 1005), B.OUT_F16_SCALED, B.LAYOUT_NM,
                                steps=20 if n <= 128 else 5, kernel=kern))
         torch.cuda.empty_cache()
