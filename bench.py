@@ -305,14 +305,16 @@ class Pool:
         n1 = self.N if n1 is None else n1
         a_off = i * self.act_row + n0 * B.act_ld(self.K)
         # weights were prepacked and synchronised at set-up: the static-weights promise holds
-        B.check(B.lib.bgemm_gemm_static_weights((stream or self.cx.stream).cuda_stream, self.planes.data_ptr() + i * self.plane_b, self.rows, self.K,
+        B.check(B.lib.bgemm_gemm_ex((stream or self.cx.stream).cuda_stream, self.planes.data_ptr() + i * self.plane_b, self.rows, self.K,
                                  self.acts.data_ptr() + a_off, self.colsum.data_ptr() + 4 * (i * self.N + n0), n1 - n0, self.op, out.data_ptr(),
-                                 out_kind, layout, self.alphas.data_ptr() + 2 * i * self.rows, 0, self.ws.data_ptr(), self.ws.numel(), 1), "gemm")
+                                 out_kind, layout, self.alphas.data_ptr() + 2 * i * self.rows, 0, self.ws.data_ptr(), self.ws.numel(), 1,
+                                 B.FLAG_STATIC_WEIGHTS | B.FLAG_BALANCE_WORKSPACE), "gemm")
 
     def gemm_batched(self, outs, out_kind, layout):
         B = self.cx.B
-        B.check(B.lib.bgemm_gemm_static_weights(self.cx.stream.cuda_stream, self.planes.data_ptr(), self.rows, self.K, self.acts.data_ptr(), self.colsum.data_ptr(),
-                                 self.N, self.op, outs.data_ptr(), out_kind, layout, self.alphas.data_ptr(), 0, self.ws.data_ptr(), self.ws.numel(), self.layers), "gemm")
+        B.check(B.lib.bgemm_gemm_ex(self.cx.stream.cuda_stream, self.planes.data_ptr(), self.rows, self.K, self.acts.data_ptr(), self.colsum.data_ptr(),
+                                 self.N, self.op, outs.data_ptr(), out_kind, layout, self.alphas.data_ptr(), 0, self.ws.data_ptr(), self.ws.numel(), self.layers,
+                                 B.FLAG_STATIC_WEIGHTS | B.FLAG_BALANCE_WORKSPACE), "gemm")
 
     # ---- oracle ---------------------------------------------------------------------------------------------------
     def expect(self, i, out_kind, layout):
@@ -482,7 +484,8 @@ def run_gather(cx: Ctx, args, pool: Pool, outs, layers, rows, ops_layer):
                 a_off = i * pool.act_row
                 B.check(B.lib.bgemm_gemm_multi_out(cx.stream.cuda_stream, pool.planes.data_ptr() + i * pool.plane_b, rows, pool.K,
                                                    pool.acts.data_ptr() + a_off, pool.colsum.data_ptr() + 4 * i * N, N, pool.op, ptrs[i], cx.world, M,
-                                                   B.OUT_F16_SCALED, B.LAYOUT_NM, pool.alphas.data_ptr() + 2 * i * rows, 0, pool.ws.data_ptr(), pool.ws.numel(), 1), "gemm_multi_out")
+                                                   B.OUT_F16_SCALED, B.LAYOUT_NM, pool.alphas.data_ptr() + 2 * i * rows, 0, pool.ws.data_ptr(), pool.ws.numel(),
+                                                   B.FLAG_STATIC_WEIGHTS | B.FLAG_BALANCE_WORKSPACE), "gemm_multi_out")
             hdl.barrier(channel=1)                  # every slab has landed on every rank
         fused = step_fused
     except Exception as exc:                        # symmetric memory unavailable on this box: report, keep the NCCL numbers

@@ -48,6 +48,8 @@ lib.bgemm_pack_weights_host.argtypes = [_vp, _int, _i64, _i64, _i64, _int, _vp, 
 lib.bgemm_prepare_acts.argtypes = [_vp, _vp, _int, _i64, _i64, _i64, _int, _int, _vp, _vp, _i64, _i64]
 lib.bgemm_gemm.argtypes = [_vp, _vp, _i64, _i64, _vp, _vp, _i64, _int, _vp, _int, _int, _vp, _int, _vp, _sz, _i64]
 lib.bgemm_gemm_static_weights.argtypes = lib.bgemm_gemm.argtypes
+lib.bgemm_gemm_ex.argtypes = lib.bgemm_gemm.argtypes + [_int]
+FLAG_STATIC_WEIGHTS, FLAG_BALANCE_WORKSPACE = 1, 2
 lib.bgemm_gemm_multi_out.argtypes = [_vp, _vp, _i64, _i64, _vp, _vp, _i64, _int, _vp, _int, _i64, _int, _int, _vp, _int, _vp, _sz, _int]
 lib.bgemm_w1a16_gemm.argtypes = [_vp, _vp, _i64, _i64, _vp, _i64, _i64, _vp, _int, _int, _vp, _int]
 lib.bgemm_gemm_to_acts.argtypes = [_vp, _vp, _i64, _i64, _vp, _vp, _i64, _int, _vp, _int, _vp, _vp, _int, _vp, _sz, _i64]
@@ -188,10 +190,12 @@ def balance_workspace(device: torch.device, nbytes: int) -> torch.Tensor:
 
 def gemm(plane: torch.Tensor, M: int, K: int, acts: torch.Tensor, colsum: torch.Tensor, op: int, out_kind: int = OUT_I32,
          out_layout: int = LAYOUT_NM, alpha: torch.Tensor | None = None, split_k: int = 0, out: torch.Tensor | None = None,
-         ws: torch.Tensor | None = None, static_weights: bool = False):
+         ws: torch.Tensor | None = None, static_weights: bool = False, balance: bool = True):
     """GEMM on prepared operands. acts: int8 [N, ld] or [B, N, ld]; returns [N, M] / [M, N] (with leading B if batched).
-    static_weights=True calls bgemm_gemm_static_weights: the caller promises that `plane` was complete before the
-    previous kernel on the current stream was launched."""
+    static_weights=True: the caller promises that `plane` was complete before the previous kernel on the current stream
+    was launched. `ws`: the workspace that split_k > 8 needs, or (other calls) a balance workspace -- zeroed once, used for
+    nothing else -- for the exact work split of wide activation matrices; by default one is kept per stream
+    (balance=False: whole tiles only)."""
     _require_cuda(plane, acts, colsum, alpha)
     batched = acts.dim() == 3
     B = acts.shape[0] if batched else 1
@@ -202,17 +206,21 @@ def gemm(plane: torch.Tensor, M: int, K: int, acts: torch.Tensor, colsum: torch.
         shape = (B,) + shape
     if out is None:
         out = torch.empty(shape, dtype=torch.int32 if out_kind == OUT_I32 else torch.float16, device=acts.device)
+    flags = FLAG_STATIC_WEIGHTS if static_weights else 0
     need = lib.bgemm_gemm_workspace_bytes(M, N, K, split_k, B)
     if need and ws is None:
         ws = workspace(acts.device, need)
-    if not need and ws is None:
-        need = lib.bgemm_gemm_balance_workspace_bytes(M, N, K, split_k, B)      # optional: exact work split for wide N
-        if need:
-            ws = balance_workspace(acts.device, need)
+    if not need:
+        bal = lib.bgemm_gemm_balance_workspace_bytes(M, N, K, split_k, B)      # optional: exact work split for wide N
+        if bal and ws is None and balance:
+            ws = balance_workspace(acts.device, bal)
+        if bal and ws is not None and ws.numel() >= bal and balance:
+            flags |= FLAG_BALANCE_WORKSPACE
+        else:
+            ws = None
     with torch.cuda.device(acts.device):
-        fn = lib.bgemm_gemm_static_weights if static_weights else lib.bgemm_gemm
-        check(fn(_stream(), plane.data_ptr(), M, K, acts.data_ptr(), colsum.data_ptr(), N, op, out.data_ptr(), out_kind,
-                 out_layout, _ptr(alpha), split_k, _ptr(ws), ws.numel() if ws is not None else 0, B), "bgemm_gemm")
+        check(lib.bgemm_gemm_ex(_stream(), plane.data_ptr(), M, K, acts.data_ptr(), colsum.data_ptr(), N, op, out.data_ptr(), out_kind,
+                                out_layout, _ptr(alpha), split_k, _ptr(ws), ws.numel() if ws is not None else 0, B, flags), "bgemm_gemm")
     return out
 
 
@@ -225,17 +233,22 @@ def gemm_multi_out(plane: torch.Tensor, M: int, K: int, acts: torch.Tensor, cols
     assert acts.dim() == 2 and acts.shape[-1] == act_ld(K) and acts.is_contiguous() and colsum.is_contiguous()
     N = acts.shape[0]
     ptrs = (ctypes.c_void_p * len(out_ptrs))(*[int(p) for p in out_ptrs])
+    flags = FLAG_STATIC_WEIGHTS if static_weights else 0
     need = lib.bgemm_gemm_workspace_bytes(M, N, K, split_k, 1)
     if need and ws is None:
         ws = workspace(acts.device, need)
-    if not need and ws is None:
-        need = lib.bgemm_gemm_balance_workspace_bytes(M, N, K, split_k, 1)
-        if need:
-            ws = balance_workspace(acts.device, need)
+    if not need:
+        bal = lib.bgemm_gemm_balance_workspace_bytes(M, N, K, split_k, 1)
+        if bal and ws is None:
+            ws = balance_workspace(acts.device, bal)
+        if bal and ws is not None and ws.numel() >= bal:
+            flags |= FLAG_BALANCE_WORKSPACE
+        else:
+            ws = None
     with torch.cuda.device(acts.device):
         check(lib.bgemm_gemm_multi_out(_stream(), plane.data_ptr(), M, K, acts.data_ptr(), colsum.data_ptr(), N, op, ptrs, len(out_ptrs), out_ld,
                                        out_kind, out_layout, _ptr(alpha), split_k, _ptr(ws), ws.numel() if ws is not None else 0,
-                                       1 if static_weights else 0), "bgemm_gemm_multi_out")
+                                       flags), "bgemm_gemm_multi_out")
 
 
 def w1a16_gemm(plane: torch.Tensor, M: int, K: int, x: torch.Tensor, out_kind: int = OUT_F32, out_layout: int = LAYOUT_NM,

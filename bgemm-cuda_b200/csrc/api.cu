@@ -252,7 +252,9 @@ size_t bgemm_gemm_balance_workspace_bytes(int64_t M, int64_t N, int64_t K, int s
 
 static int gemm_entry(void* stream, const void* plane, int64_t M, int64_t K, const int8_t* acts, const int32_t* colsum, int64_t N, int op,
                       void* out, int out_kind, int out_layout, const void* alpha, int split_k, void* workspace, size_t workspace_bytes,
-                      int64_t batch, int weights_static, void* const* more_outs = nullptr, int n_more = 0, int64_t out_ld = 0) {
+                      int64_t batch, int flags, void* const* more_outs = nullptr, int n_more = 0, int64_t out_ld = 0) {
+    const int weights_static = (flags & BGEMM_FLAG_STATIC_WEIGHTS) ? 1 : 0;
+    if (flags & ~(BGEMM_FLAG_STATIC_WEIGHTS | BGEMM_FLAG_BALANCE_WORKSPACE)) return BGEMM_ERR_ENUM;
     if (!plane || !acts || !colsum || !out) return BGEMM_ERR_NULL;
     if (n_more < 0 || n_more > 7 || (n_more > 0 && !more_outs)) return BGEMM_ERR_SHAPE;
     for (int i = 0; i < n_more; i++)
@@ -310,10 +312,13 @@ static int gemm_entry(void* stream, const void* plane, int64_t M, int64_t K, con
         const long long tiles = mtiles * ((N + NT - 1) / NT) * batch;
         p.ws_counters = static_cast<unsigned int*>(workspace);
         p.ws_partial = reinterpret_cast<int32_t*>(static_cast<char*>(workspace) + counter_bytes(tiles));
-    } else if (s == 1 && workspace && aligned(workspace, 256)) {
-        // optional: room for the pair kernel's exact work split
+    } else if (s == 1 && (flags & BGEMM_FLAG_BALANCE_WORKSPACE)) {
+        // the caller declared `workspace` to be a balance workspace (zeroed once, used for nothing else): room for the
+        // pair kernel's exact work split, if this shape takes that kernel
         const size_t want = pair_balance_workspace_bytes(M, N, K, batch);
-        if (want && workspace_bytes >= want) {
+        if (want) {
+            if (!workspace || workspace_bytes < want) return BGEMM_ERR_WORKSPACE;
+            if (!aligned(workspace, 256)) return BGEMM_ERR_ALIGN;
             p.ws_counters = static_cast<unsigned int*>(workspace);
             p.ws_partial = reinterpret_cast<int32_t*>(static_cast<char*>(workspace) + 65536);
         }
@@ -330,15 +335,21 @@ int bgemm_gemm(void* stream, const void* plane, int64_t M, int64_t K, const int8
 int bgemm_gemm_static_weights(void* stream, const void* plane, int64_t M, int64_t K, const int8_t* acts, const int32_t* colsum, int64_t N,
                               int op, void* out, int out_kind, int out_layout, const void* alpha, int split_k, void* workspace,
                               size_t workspace_bytes, int64_t batch) {
-    return gemm_entry(stream, plane, M, K, acts, colsum, N, op, out, out_kind, out_layout, alpha, split_k, workspace, workspace_bytes, batch, 1);
+    return gemm_entry(stream, plane, M, K, acts, colsum, N, op, out, out_kind, out_layout, alpha, split_k, workspace, workspace_bytes, batch,
+                      BGEMM_FLAG_STATIC_WEIGHTS);
+}
+
+int bgemm_gemm_ex(void* stream, const void* plane, int64_t M, int64_t K, const int8_t* acts, const int32_t* colsum, int64_t N, int op, void* out,
+                  int out_kind, int out_layout, const void* alpha, int split_k, void* workspace, size_t workspace_bytes, int64_t batch, int flags) {
+    return gemm_entry(stream, plane, M, K, acts, colsum, N, op, out, out_kind, out_layout, alpha, split_k, workspace, workspace_bytes, batch, flags);
 }
 
 int bgemm_gemm_multi_out(void* stream, const void* plane, int64_t M, int64_t K, const int8_t* acts, const int32_t* colsum, int64_t N, int op,
                          void* const* outs_host, int n_outs, int64_t out_ld, int out_kind, int out_layout, const void* alpha, int split_k,
-                         void* workspace, size_t workspace_bytes, int weights_static) {
+                         void* workspace, size_t workspace_bytes, int flags) {
     if (!outs_host || n_outs < 1 || n_outs > 8) return outs_host ? BGEMM_ERR_SHAPE : BGEMM_ERR_NULL;
     return gemm_entry(stream, plane, M, K, acts, colsum, N, op, outs_host[0], out_kind, out_layout, alpha, split_k, workspace, workspace_bytes, 1,
-                      weights_static ? 1 : 0, outs_host + 1, n_outs - 1, out_ld);
+                      flags, outs_host + 1, n_outs - 1, out_ld);
 }
 
 int bgemm_w1a16_gemm(void* stream, const void* plane, int64_t M, int64_t K, const void* x_f16, int64_t x_ld, int64_t N, void* out, int out_kind,

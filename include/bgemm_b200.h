@@ -174,11 +174,6 @@ int bgemm_prepare_acts(void* stream, const void* src, int src_dtype, int64_t N, 
  *             Zero it once after allocating it; the library restores the part that must be zero
  *             (arrival counters in its first 64 KiB) before each call returns, so one buffer can serve
  *             calls of any shapes one after another on a stream.
- *             Optional for wide activation matrices: given bgemm_gemm_balance_workspace_bytes() bytes (same rules: 256-byte
- *             aligned, zeroed once, reusable), the kernel for N >= 256 splits its work into exactly equal parts per SM
- *             pair -- tiles that straddle a boundary are accumulated in two places and summed through the workspace --
- *             instead of whole tiles, which matters when the number of tiles is not a multiple of the SM pairs. The
- *             results are the same bits (integer sums). One such workspace must not serve two calls that overlap on the GPU.
  *   batch     number of independent problems (A x V heads); problem i uses plane + i*plane_bytes,
  *             acts + i*N*act_ld, colsum + i*N, out + i*M*N elements, alpha + i*M.
  * Replaces bin_pack_linear_kernel + PACK_BGEMM_Kernel + SplitK_Reduction (see file header).           */
@@ -187,7 +182,26 @@ int bgemm_gemm(void* stream, const void* plane, int64_t M, int64_t K,
                int op, void* out, int out_kind, int out_layout, const void* alpha,
                int split_k, void* workspace, size_t workspace_bytes, int64_t batch);
 size_t bgemm_gemm_workspace_bytes(int64_t M, int64_t N, int64_t K, int split_k, int64_t batch);
-/* Size of the optional workspace described above; 0 when the call would not use one. No reference counterpart. */
+
+/* bgemm_gemm with flags (an OR of the values below; 0 = bgemm_gemm).
+ *   BGEMM_FLAG_STATIC_WEIGHTS     the promise of bgemm_gemm_static_weights (next entry point).
+ *   BGEMM_FLAG_BALANCE_WORKSPACE  `workspace` is a BALANCE workspace: bgemm_gemm_balance_workspace_bytes() bytes, 256-byte
+ *       aligned, zeroed once after allocation and never written by anybody but this library (its first 64 KiB are flags
+ *       that every launch leaves at zero). With it the kernel for wide activation matrices (N >= 256) splits its work
+ *       into exactly equal parts per SM pair -- tiles that straddle a boundary are accumulated in two or more places and
+ *       summed through the workspace -- instead of whole tiles, which matters whenever the number of 256 x 256 tiles is
+ *       not a multiple of the SM pairs (28672 x 8192 x 1024: 171 -> 158 us). Results are the same bits (integer sums).
+ *       One balance workspace must not serve two calls that overlap on the GPU; calls on one stream may share it.
+ *       bgemm_gemm_balance_workspace_bytes() returns 0 for calls that would not use one (the flag is then ignored);
+ *       a workspace that is missing or too small for a call that would is refused with BGEMM_ERR_WORKSPACE.
+ *       The flag cannot be combined with split_k > 8 (whose workspace has another layout).
+ * No reference counterpart.                                                                                         */
+#define BGEMM_FLAG_STATIC_WEIGHTS 1
+#define BGEMM_FLAG_BALANCE_WORKSPACE 2
+int bgemm_gemm_ex(void* stream, const void* plane, int64_t M, int64_t K,
+                  const int8_t* acts, const int32_t* colsum, int64_t N,
+                  int op, void* out, int out_kind, int out_layout, const void* alpha,
+                  int split_k, void* workspace, size_t workspace_bytes, int64_t batch, int flags);
 size_t bgemm_gemm_balance_workspace_bytes(int64_t M, int64_t N, int64_t K, int split_k, int64_t batch);
 
 /* bgemm_gemm with one promise added by the caller: `plane` was complete in device memory BEFORE the kernel that precedes
@@ -212,12 +226,12 @@ int bgemm_gemm_static_weights(void* stream, const void* plane, int64_t M, int64_
  * 16-byte piece of the slab then leaves the SM once per destination as an ordinary global store (remote ones travel
  * over NVLink) while the tensor cores work on the next tile. No TMA and no multicast is involved. The caller makes
  * the stores visible to the other ranks' later kernels the usual way (a cross-rank barrier after the launch).
- * One problem per call (no batch). `weights_static` != 0 adds the promise of bgemm_gemm_static_weights.
+ * One problem per call (no batch). `flags`: as in bgemm_gemm_ex (1 = the promise of bgemm_gemm_static_weights).
  * The reference has no multi-GPU path; this entry point has no counterpart there.                                  */
 int bgemm_gemm_multi_out(void* stream, const void* plane, int64_t M, int64_t K,
                          const int8_t* acts, const int32_t* colsum, int64_t N, int op,
                          void* const* outs_host, int n_outs, int64_t out_ld, int out_kind, int out_layout,
-                         const void* alpha, int split_k, void* workspace, size_t workspace_bytes, int weights_static);
+                         const void* alpha, int split_k, void* workspace, size_t workspace_bytes, int flags);
 
 /* Binary weight x fp16 activation ("W1A16", listed as to-do in the reference's README.md:29; no counterpart in its code):
  *   C[n, m] = sum_k sgn(w[m, k]) * x[n, k]   (* alpha[m] when alpha != NULL),   sgn by the sign bit as everywhere else,

@@ -89,6 +89,17 @@ def test_a_refused_call_enqueues_nothing(lib):
     assert lib.bgemm_gemm_to_acts(None, fake, 64, 8192, fake, fake, 8, 1, None, 0, fake, fake, 16, fake + 16, big, 1) == -3
     # general int8 activations on narrow tiles beyond the exact range
     assert lib.bgemm_gemm(None, fake, 128, 70000, fake, fake, 16, 4, fake, 0, 0, None, 1, None, 0, 1) == -6
+    # flags of bgemm_gemm_ex: unknown bits; a balance workspace that a wide problem would use but that is missing, too small
+    # or misaligned (2 = BGEMM_FLAG_BALANCE_WORKSPACE)
+    lib.bgemm_gemm_ex.argtypes = [vp, vp, i64, i64, vp, vp, i64, ci, vp, ci, ci, vp, ci, vp, sz, i64, ci]
+    lib.bgemm_gemm_balance_workspace_bytes.restype = sz
+    lib.bgemm_gemm_balance_workspace_bytes.argtypes = [i64, i64, i64, ci, i64]
+    assert lib.bgemm_gemm_ex(None, fake, 128, 512, fake, fake, 32, 1, fake, 0, 0, None, 1, None, 0, 1, 4) == -4
+    want = lib.bgemm_gemm_balance_workspace_bytes(28672, 1024, 8192, 0, 1)
+    assert want > 65536 and lib.bgemm_gemm_balance_workspace_bytes(28672, 128, 8192, 0, 1) == 0
+    assert lib.bgemm_gemm_ex(None, fake, 28672, 8192, fake, fake, 1024, 3, fake, 1, 0, None, 0, None, 0, 1, 2) == -5
+    assert lib.bgemm_gemm_ex(None, fake, 28672, 8192, fake, fake, 1024, 3, fake, 1, 0, None, 0, fake, want - 1, 1, 2) == -5
+    assert lib.bgemm_gemm_ex(None, fake, 28672, 8192, fake, fake, 1024, 3, fake, 1, 0, None, 0, fake + 16, want, 1, 2) == -3
     assert lib.bgemm_launch_count() == before
 
 

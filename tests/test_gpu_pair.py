@@ -58,8 +58,7 @@ def _run(B, M, K, N, op=O.OP_BWTA, batch=1, layouts=(0, 1), kinds=(O.OUT_I32, O.
             if layout == 1:
                 want = want.transpose(-1, -2)
             for rep in range(2):                    # the second call finds the workspace as the first one left it
-                ws = None if use_ws else torch.zeros(256, dtype=torch.uint8, device="cuda")      # too small: whole tiles only
-                got = B.gemm(plane, M, K, acts, colsum, op, kind, layout, None if a is None else a.cuda(), 0, ws=ws).cpu()
+                got = B.gemm(plane, M, K, acts, colsum, op, kind, layout, None if a is None else a.cuda(), 0, balance=use_ws).cpu()
                 assert got.shape == want.shape and torch.equal(got, want), (op, M, K, N, batch, layout, kind, rep, int((got != want).sum()))
     assert B.lib.bgemm_device_status(1) == 0
 
