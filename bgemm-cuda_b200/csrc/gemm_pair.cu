@@ -48,6 +48,9 @@ constexpr int kQSets = 4;
 constexpr int kQEpiThreads = 256;
 constexpr int kQWarpEpi = 4 * kQSets, kQWarpMma = kQWarpEpi + 8, kQWarpW = kQWarpMma + 1, kQWarpB = kQWarpMma + 2;
 constexpr int kQThreads = 32 * (kQWarpB + 1);
+// 864 threads start with 72 registers each; the unpack warps (16 of 27) release down to 48, which lets the 8 epilogue
+// warps hold 120: 16 * 32 * 24 registers change hands.
+constexpr int kQUnpackRegs = 48, kQEpiRegs = 120;
 constexpr long long kQCopyDrainClocks = 4000000;   // ~2 ms: far beyond any TMA copy of a 32 KB tile
 
 struct QCfg {
@@ -374,6 +377,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_acts, const GemmParams
         }
     } else if (warp < 4 * kQSets) {
         // ---------------- unpack: set s = warps 4 s .. 4 s + 3 takes the K blocks g of the stream with g % kQSets == s ----
+        regs_release<kQUnpackRegs>();                         // the epilogue warps get what these sixteen warps do not need
         const int set = warp >> 2;
         const int r = (warp & 3) * 32 + lane;                 // weight row of this CTA's half tile == tensor-memory lane
         const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
@@ -420,6 +424,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_acts, const GemmParams
         // block writes its accumulator to this CTA's slot of the workspace and raises the slot's flag; the item that
         // ends a tile begun by other clusters waits for their flags (they took those items FIRST), adds their slots
         // while it reads its own accumulator, and clears the flags for the next launch.
+        regs_request<kQEpiRegs>();
         const int h = (warp - kQWarpEpi) >> 2;
         const int et = (warp & 3) * 32 + lane;                // accumulator row == tensor-memory lane
         const int eall = h * 128 + et;
@@ -478,10 +483,11 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_acts, const GemmParams
             if (warp == kQWarpEpi && lane == 0) BGEMM_TRACE(6, item * 4);
             tc_fence_after();
             // this thread's 32 accumulator values of columns h * 128 + c0 .. + 31, plus the other clusters' parts
-            auto load32 = [&](int c0, uint32_t (&v0)[16], uint32_t (&v1)[16]) {
+            auto issue32 = [&](int c0, uint32_t (&v0)[16], uint32_t (&v1)[16]) {
                 tmem_ld16(tmem_d + lane_base + h * 128 + c0, v0);
                 tmem_ld16(tmem_d + lane_base + h * 128 + c0 + 16, v1);
-                tmem_wait_ld();
+            };
+            auto add_parts32 = [&](int c0, uint32_t (&v0)[16], uint32_t (&v1)[16]) {
                 for (int q = 0; q < nparts; q++) {
                     const int* part = p.ws_partial + (size_t)(2 * (cid - 1 - q) + rank) * C::PART_INTS + (h * 128 + c0) * 128 + et;
 #pragma unroll
@@ -489,6 +495,11 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_acts, const GemmParams
 #pragma unroll
                     for (int i = 0; i < 16; i++) v1[i] += (uint32_t)ld_global_hint(part + (16 + i) * 128, keep);
                 }
+            };
+            auto load32 = [&](int c0, uint32_t (&v0)[16], uint32_t (&v1)[16]) {
+                issue32(c0, v0, v1);
+                tmem_wait_ld();
+                add_parts32(c0, v0, v1);
             };
             auto release_accumulator = [&]() {
                 tc_fence_before();
@@ -517,17 +528,15 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_acts, const GemmParams
                 continue;
             }
             int lo16 = 0, hi16 = 0;                               // value range of this thread's part of the accumulator
-#pragma unroll 1
-            for (int c0 = 0; c0 < 128; c0 += 32) {
-                uint32_t v0[16], v1[16];
-                load32(c0, v0, v1);
+            auto stage32 = [&](int c0, uint32_t (&v0)[16], uint32_t (&v1)[16]) {
+                add_parts32(c0, v0, v1);
 #pragma unroll
                 for (int q = 0; q < 16; q++) { lo16 = min(lo16, min((int)v0[q], (int)v1[q])); hi16 = max(hi16, max((int)v0[q], (int)v1[q])); }
                 uint32_t w0[8], w1[8];
 #pragma unroll
                 for (int q = 0; q < 8; q++) {
-                    w0[q] = (v0[2 * q] & 0xffffu) | (v0[2 * q + 1] << 16);
-                    w1[q] = (v1[2 * q] & 0xffffu) | (v1[2 * q + 1] << 16);
+                    w0[q] = __byte_perm(v0[2 * q], v0[2 * q + 1], 0x5410);      // low halves of two values in one word
+                    w1[q] = __byte_perm(v1[2 * q], v1[2 * q + 1], 0x5410);
                 }
                 if (rowmajor) {
                     uint4* dst = reinterpret_cast<uint4*>(sS + et * C::ROW_PITCH + (c0 >> 1));
@@ -537,6 +546,20 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_acts, const GemmParams
 #pragma unroll
                     for (int q = 0; q < 8; q++) { sS[((c0 >> 1) + q) * 128 + et] = w0[q]; sS[((c0 >> 1) + 8 + q) * 128 + et] = w1[q]; }
                 }
+            };
+            {
+                // 128 columns in four loads of 32, two in flight: the second pair is requested while the first is packed
+                uint32_t a0[16], a1[16], b0[16], b1[16];
+                issue32(0, a0, a1);
+                issue32(32, b0, b1);
+                tmem_wait_ld();
+                stage32(0, a0, a1);
+                issue32(64, a0, a1);
+                stage32(32, b0, b1);
+                issue32(96, b0, b1);
+                tmem_wait_ld();
+                stage32(64, a0, a1);
+                stage32(96, b0, b1);
             }
             // One answer per half: did every value fit 16 bits? (The barrier also publishes the staging tile.)
             const bool wide = named_bar_or(3 + h, 128, lo16 < -32768 || hi16 > 32767);

@@ -173,6 +173,14 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
         : "r"(taddr)
         : "memory");
 }
+// ---- register reallocation between the warp groups of a CTA --------------------------------------------------------
+// Every warp of a group of four consecutive warps (0-3, 4-7, ...) must execute the same one of these. Registers that one
+// group gives up become available to the groups that ask for more (they block until enough have been released).
+template <int N>
+__device__ __forceinline__ void regs_release() { asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N)); }
+template <int N>
+__device__ __forceinline__ void regs_request() { asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N)); }
+
 // ---- L2 residency hints ------------------------------------------------------------------------------------------
 // Policy for data that is written early in a kernel and read back at its end (partial sums handed between CTAs): keep
 // it in L2 while the kernel streams its operands and results through.
