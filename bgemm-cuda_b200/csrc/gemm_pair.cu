@@ -678,12 +678,26 @@ int launch_gemm_pair(cudaStream_t stream, const void* tensor_map, const GemmPara
     }
     const long long total_tiles = (long long)(p.mtiles / 2) * p.ntiles * batch;
     const long long units = total_tiles * p.kblocks;
-    const long long pairs = sm_count() / 2;
+    // clusters that can be resident at once (normally one per SM pair): the exact split needs all of its clusters
+    // running, because a cluster waits for the partial sums of its predecessors
+    static int resident[64] = {};
+    if (dev < 64 && !resident[dev]) {
+        cudaLaunchConfig_t q = {};
+        q.gridDim = dim3((unsigned)(sm_count() / 2 * 2), 1, 1);
+        q.blockDim = dim3(kQThreads, 1, 1);
+        q.dynamicSmemBytes = C::SMEM_BYTES;
+        int n = 0;
+        resident[dev] = (cudaOccupancyMaxActiveClusters(&n, gemm_pair_kernel, &q) == cudaSuccess && n > 0) ? n : -1;
+        cudaGetLastError();
+    }
+    long long pairs = sm_count() / 2;
+    if (dev < 64 && resident[dev] > 0 && resident[dev] < pairs) pairs = resident[dev];
+    const bool can_wait = dev < 64 && resident[dev] > 0;       // unknown residency: whole tiles only
     // exact ranges need the workspace and every cluster resident at once (a cluster waits for its successors' parts):
     // one cluster per SM pair, at least four K blocks each
     // -- and it pays when every cluster has at least a tile's worth of work and the tiles do not divide evenly anyway
-    int exact = (p.ws_partial && p.ws_counters && units >= 4 * pairs && total_tiles >= pairs && total_tiles % pairs != 0) ? 1 : 0;
-    if (pair_forced() == 1 && p.ws_partial && p.ws_counters && units >= 4 * pairs) exact = 1;      // tuning / tests: whenever possible
+    int exact = (can_wait && p.ws_partial && p.ws_counters && units >= 4 * pairs && total_tiles >= pairs && total_tiles % pairs != 0) ? 1 : 0;
+    if (pair_forced() == 1 && can_wait && p.ws_partial && p.ws_counters && units >= 4 * pairs) exact = 1;      // tuning / tests: whenever possible
     static const int no_exact = env_int_q("BGEMM_PAIR_EXACT");     // tuning override: 0 = whole tiles only
     if (no_exact == 0) exact = 0;
     const long long clusters = exact ? pairs : (total_tiles < pairs ? total_tiles : pairs);
