@@ -664,7 +664,7 @@ def run_sweep(cx: Ctx):
     # C5 at every N (the planes are the same pool; activations differ)
     layers5 = max(4, -(-int(1.5 * L2_BYTES) // B.plane_bytes(28672, 8192)))
     for n in (1, 2, 4, 8, 16, 128, 4096):
-        kern = ("gemm_stream_kernel (mma.sync int8 from registers)" if n <= 16 else
+        kern = ("gemm_skinny_kernel (popcount on the CUDA cores)" if n == 1 else "gemm_stream_kernel (mma.sync int8 from registers)" if n <= 16 else
                 "gemm_pair_kernel (tcgen05, cta_group::2)" if B.lib.bgemm_gemm_balance_workspace_bytes(28672, n, 8192, 0, 1) else "gemm_kernel (tcgen05)")
         out.append(sweep_entry(cx, f"c5n{n}", Pool(cx, 28672, 8192, n, "bwta", layers5, 1005), B.OUT_F16_SCALED, B.LAYOUT_NM,
                                steps=20 if n <= 128 else 5, kernel=kern))

@@ -1,7 +1,9 @@
-"""GPU parity tests of the weight-streaming kernel that serves N <= 4 (gemm_skinny.cu): both of its arithmetic paths
-(bit planes + popcount for ternary activations, dp4a for anything else), the fallback it takes when activations turn
-out not to be ternary, and the tensor-core kernels on the same small shapes with the streaming kernel switched off.
-Every result is compared bit for bit with the CPU oracle."""
+"""GPU parity tests at N <= 4. The dispatcher gives a single ternary activation row to the CUDA-core weight-streaming
+kernel (gemm_skinny.cu: bit planes + popcount) and the other shapes here to the register-fed streaming kernel
+(gemm_stream.cu), falling back to gemm_skinny.cu where that one does not apply (K beyond 65536); tests/test_gpu_stream.py
+runs a child process with the register-fed kernel switched off, which keeps the CUDA-core kernel's dp4a path and its
+fallback for non-ternary activations covered, and the child process below switches both off to cover the tensor-core
+kernels on the same small shapes. Every result is compared bit for bit with the CPU oracle."""
 import os
 import subprocess
 import sys
