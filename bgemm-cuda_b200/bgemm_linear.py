@@ -272,11 +272,34 @@ class _LazyScaledLinear(nn.Linear):
             out += self.bias.view(1, -1).expand_as(out)
         return out
 
+    def _inference(self, x) -> bool:
+        """No gradient will be asked for: the packed weight plane can be kept between calls."""
+        return not (torch.is_grad_enabled() and (x.requires_grad or self.weight.requires_grad))
+
+    def _cached_plane(self):
+        """Packed sign plane of (weight - zpw), re-packed only when the weight has been written since (its version
+        counter) or replaced. The reference packs the fp16 weight inside the kernel on every call."""
+        key = (self.weight._version, self.weight.data_ptr(), self.weight.device)
+        if getattr(self, "_plane_key", None) != key:
+            w = (self.weight.detach() - self.zpw).to(torch.half)
+            self._plane = lowbit_kernel.binary_weight_prepacking_cuda(w, 0)
+            self._plane_key = key
+        return self._plane
+
+    def _forward_cached(self, x):
+        """sign(x - zpa) @ sign(weight - zpw).T through the prepacked plane: the same bits as the drop-in call."""
+        lead, K, M = x.shape[:-1], self.in_features, self.out_features
+        x2 = (x - self.zpa).to(torch.half).reshape(-1, K)
+        out = lowbit_kernel.bgemm_linear_forward_packed(x2, self._cached_plane(), M, K, None, 0, XOR_POP, _OUT_F16)
+        return out.reshape(*lead, M)
+
 
 class BGEMMLinear(_LazyScaledLinear):
     def forward(self, x):
         if not self.initialized:
             self._initialize(x, self.weight)
+        if self._inference(x):
+            return self._add_bias(self._forward_cached(x) * self.sw * self.sa)
         out = bgemm_linear.apply(x - self.zpa, self.weight - self.zpw) * self.sw * self.sa
         return self._add_bias(out)
 
@@ -285,6 +308,8 @@ class BGEMMLinear_bireal(_LazyScaledLinear):
     def forward(self, x):
         if not self.initialized:
             self._initialize(x, self.weight)
+        if self._inference(x):
+            return self._add_bias(self._forward_cached(x) * self.sw * self.sa)
         out = bgemm_linear_bireal.apply(x - self.zpa, self.weight - self.zpw) * self.sw * self.sa
         return self._add_bias(out)
 

@@ -206,3 +206,27 @@ def test_binary_linear_state_dict_is_versioned(L):
         b.load_state_dict(newer)
     with pytest.raises(RuntimeError):                              # a 300 x 520 bundle does not fit a 128 x 520 layer
         L.BinaryLinear(torch.zeros(128, 520, dtype=torch.half, device="cuda")).load_state_dict(sd)
+
+
+@pytest.mark.parametrize("cls", ["BGEMMLinear", "BGEMMLinear_bireal"])
+def test_inference_path_keeps_the_packed_plane_and_equals_the_dropin_path(L, cls):
+    """Under torch.no_grad() the drop-in layers keep the packed plane of sign(weight - zpw) between calls (the reference
+    packs the fp16 weight inside the kernel on every call): same bits as the autograd path, re-packed after the weight
+    has been written."""
+    g = O._gen(77)
+    layer = getattr(L, cls)(1024, 384, True).cuda()
+    x = torch.randn((96, 1024), generator=g).cuda()
+    y_train = layer(x)                                   # initialises the scales; autograd path (drop-in extension call)
+    with torch.no_grad():
+        y0 = layer(x)
+        plane0 = layer._plane
+        y1 = layer(x)
+        assert layer._plane is plane0                    # second call: no re-pack
+        assert torch.equal(y0, y_train.detach()) and torch.equal(y1, y0)
+        layer.weight.mul_(-1.0)                          # in-place write: the version counter moves
+        y2 = layer(x)
+        assert layer._plane is not plane0
+    y2_train = layer(x)
+    assert torch.equal(y2, y2_train.detach()) and not torch.equal(y2, y0)
+    y2_train.sum().backward()                            # the autograd path still produces gradients
+    assert layer.weight.grad is not None
