@@ -46,7 +46,7 @@ for _p in (ROOT / "bgemm-cuda_b200", ROOT / "oracle"):
 HEAD = dict(M=28672, K=8192, N=1024, op="bwta", desc="LLM projection: binary W[28672,8192] x ternary X[8192,1024] (P(0)=0.3), fp16 alpha epilogue, rows sharded over the GPUs")
 C2 = dict(M=4096, K=4096, N=128, op="bwta", desc="BWTA GEMM: binary W[4096,4096] x ternary X[4096,128], fp16 alpha epilogue")
 L2_BYTES = 126 * 1024 * 1024
-I8_MICROBENCH_TOPS = 3873.0          # tcgen05.mma kind::i8 128x256x32 issue-rate microbenchmark on this pool
+I8_MICROBENCH_TOPS = 3873.0          # tcgen05.mma kind::i8 128x256x32 issue-rate microbenchmark measured on this pool of B200s
 # dram__bytes_read.sum + dram__bytes_write.sum per launch from the ncu captures summarised under profiles/
 NCU_TRAFFIC = {"head": 66.84e6,                 # profiles/gemm_pair_kernel_bwta_28672x8192x1024.md (one launch = one unsharded layer)
                "c2_pool_per_layer": 270.15e6 / 80}   # profiles/gemm_persist_kernel_bwta_4096x4096x128_batched80.md
