@@ -9,12 +9,13 @@
 //
 // Tensor memory (all 512 columns): two accumulators of NT columns (tile t is accumulated into buffer t & 1 while the
 // epilogue drains the other one) and a ring of u8 weight operand stages of 64 columns.
-//   warps 0-7    unpack, two sets taking alternate K blocks of the CTA's whole K-block stream
-//   warps 8-11   epilogue: accumulator -> shared memory staging tile -> scaled / converted 16-byte stores
-//   warp 12      tensor-memory allocation; one lane issues the UMMAs of the even K blocks of the stream
-//   warp 15      one lane issues the UMMAs of the odd K blocks
-//   warp 13      one lane streams the packed weight tiles (cp.async.bulk)
-//   warp 14      one lane loads the activation tiles (TMA, 128B swizzle)
+//   warps 0-15   unpack, sets of four warps taking the K blocks of the CTA's whole K-block stream in turn (four sets with
+//                128-column tiles, two with 64-column tiles)
+//   warps 16-19  epilogue: accumulator -> shared memory staging tile -> scaled / converted 16-byte stores
+//   warp 20      tensor-memory allocation; one lane issues the UMMAs of the even K blocks of the stream
+//   warp 23      one lane issues the UMMAs of the odd K blocks
+//   warp 21      one lane streams the packed weight tiles (cp.async.bulk)
+//   warp 22      one lane loads the activation tiles (TMA, 128B swizzle)
 // All rings are indexed by the running K-block number g of the CTA, so nothing drains between tiles.
 #include <cuda.h>
 #include <cuda_fp16.h>
@@ -26,9 +27,13 @@
 
 namespace bgemm {
 
-constexpr int kPThreads = 512;
+// Warp roles: up to 16 unpack warps (sets of four; warps 4 * NSETS .. 15 exit at once when a variant uses fewer sets),
+// 4 epilogue warps, two UMMA issuers, two copy producers.
+constexpr int kPThreads = 768;
 constexpr int kPEpiThreads = 128;
-constexpr int kPWarpEpi = 8, kPWarpMma0 = 12, kPWarpW = 13, kPWarpB = 14, kPWarpMma1 = 15;
+constexpr int kPWarpEpi = 16, kPWarpMma0 = 20, kPWarpW = 21, kPWarpB = 22, kPWarpMma1 = 23;
+// 768 threads start with 80 registers each; the unpack warps release down to 48 and the four epilogue warps take 160
+constexpr int kPUnpackRegs = 48, kPEpiRegs = 160;
 constexpr long long kCopyDrainClocks = 4000000;   // ~2 ms: far beyond any TMA copy of a 32 KB tile
 
 template <int NT>
@@ -44,7 +49,12 @@ struct PCfg {
     static constexpr int STAGES = S_FIT > 6 ? 6 : S_FIT;
     static constexpr int A_COL0 = 2 * NT;
     static constexpr int B_STAGE_BYTES = NT * 256;
-    static constexpr int W_STAGES = 6;
+    // Unpack sets of four warps; set s takes the K blocks g of the stream with g % NSETS == s (always the same operand
+    // stage). A set's tensor-memory stores complete only between UMMAs, so a set needs ~2100 clocks per K block whatever
+    // the tile width: with 128-column tiles (512 clocks of UMMA per K block) two sets cap the kernel at ~1050 clocks per
+    // K block; four sets lift that cap.
+    static constexpr int NSETS = NT == 128 ? 4 : 2;
+    static constexpr int W_STAGES = NSETS == 4 ? 4 : 6;
     static constexpr int STAGE_TILE_BYTES = NT * 128 * 4;
     // w_full/w_empty, full/empty, d_full[2], d_empty[2], first_done[2], drained
     static constexpr int NBARS = 2 * W_STAGES + 2 * STAGES + 7;
@@ -53,7 +63,7 @@ struct PCfg {
     // K block g of the CTA's stream uses stage g % STAGES, is unpacked by set g % 2 and issued by issuer g % 2:
     // with even stage counts a stage and its barriers always meet the same set and the same issuer, so every
     // parity wait has seen the previous phase of its barrier.
-    static_assert(W_STAGES % 2 == 0 && STAGES % 2 == 0 && STAGES >= 2, "stage -> unpack set / issuer must stay fixed");
+    static_assert(W_STAGES % NSETS == 0 && STAGES % NSETS == 0 && STAGES % 2 == 0 && STAGES >= 2, "stage -> unpack set / issuer must stay fixed");
     static_assert(NBARS * 8 <= 512, "barrier area");
     static_assert(SMEM_BYTES <= 227 * 1024, "shared memory budget");
     // More than half of an SM's shared memory: at most one CTA per SM, so the 512-column allocation never waits
@@ -230,8 +240,9 @@ __global__ void __launch_bounds__(kPThreads, 1) gemm_persist_kernel(const __grid
             umma_commit(drained);
             if (me == 0) { BGEMM_PUT(16, twf); BGEMM_PUT(24, clock64() - tloop0); BGEMM_PUT(27, twd); }
         }
-    } else if (warp < 8) {
-        // ---------------- unpack: set 0 = warps 0-3 takes even K blocks of the stream, set 1 = warps 4-7 odd ones ----
+    } else if (warp < 16) {
+        // ---------------- unpack: set s = warps 4 s .. 4 s + 3 takes the K blocks g of the stream with g % NSETS == s ----
+        regs_release<kPUnpackRegs>();
         const int set = warp >> 2;
         const int r = (warp & 3) * 32 + lane;                 // weight row of the tile == tensor-memory lane
         const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
@@ -239,7 +250,7 @@ __global__ void __launch_bounds__(kPThreads, 1) gemm_persist_kernel(const __grid
         bool ok = true;
         BGEMM_TUNING_ONLY(long long tww = 0, twe = 0;)
         BGEMM_TUNING_ONLY(const long long tloop0 = clock64();)
-        for (long long g = set; g < total_kb && ok; g += 2) {
+        for (long long g = set; g < total_kb && ok && set < C::NSETS; g += C::NSETS) {
             const int ws = (int)(g % C::W_STAGES);
             BGEMM_TIMED(tww, ok = mbar_wait(w_full + 8 * ws, (uint32_t)(g / C::W_STAGES) & 1, abort_flag, p.status, 27));
             ok = __all_sync(0xffffffffu, ok);
@@ -274,6 +285,7 @@ __global__ void __launch_bounds__(kPThreads, 1) gemm_persist_kernel(const __grid
         if (tid == 128) { BGEMM_PUT(22, tww); BGEMM_PUT(23, twe); }
     } else if (warp >= kPWarpEpi && warp < kPWarpEpi + 4) {
         // ---------------- epilogue: overlaps the mainloop of the next tile ----------------
+        regs_request<kPEpiRegs>();
         const int et = tid - kPWarpEpi * 32;                  // 0..127 == accumulator row == tensor-memory lane
         const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
         TileOut tout;
