@@ -49,7 +49,7 @@ L2_BYTES = 126 * 1024 * 1024
 I8_MICROBENCH_TOPS = 3873.0          # tcgen05.mma kind::i8 128x256x32 issue-rate microbenchmark measured on this pool of B200s
 # dram__bytes_read.sum + dram__bytes_write.sum per launch from the ncu captures summarised under profiles/
 NCU_TRAFFIC = {"head": 66.84e6,                 # profiles/gemm_pair_kernel_bwta_28672x8192x1024.md (one launch = one unsharded layer)
-               "c2_pool_per_layer": 270.15e6 / 80}   # profiles/gemm_persist_kernel_bwta_4096x4096x128_batched80.md
+               "c2_pool_per_layer": 323.15e6 / 95}   # profiles/gemm_persist_kernel_bwta_4096x4096x128_batched95.md
 METRIC = "bwta_effective_tops"
 UNIT = "TOPS (2*M*N*K/s)"
 
