@@ -67,91 +67,146 @@ __device__ __forceinline__ uint32_t weight_bits_x2(uint32_t w, int mode) {
 }
 
 // ---- weights -> tiled plane (+ rowpop, alpha) ---------------------------------------------------------------
-// One warp per row of the padded matrix. Lane L reads elements k = 256 kb + 8 L + e (e = 0..7): slice
-// j = L / 4, words c = 2 (L % 4) + e / 4, byte b = e % 4 -> bit 8 b + j. Words are completed by OR-ing
-// across the eight lanes that share L % 4.
+// Bit 8 b + j of word c of a row's K block is element k = 32 j + 4 c + b of that block, so the words 2 cp and 2 cp + 1
+// are made of the eight 8-element pieces k = 32 j + 8 cp ... + 7 (j = 0..7; 16 bytes of a 2-byte type each) and of
+// nothing else. A warp therefore packs one K block of EIGHT consecutive rows per step: lane = 4 * (row in the group)
+// + cp loads its eight pieces (eight independent 16-byte streaming loads; the four lanes of a row cover 64 contiguous
+// bytes per load), builds its two words without any exchange between lanes, and stores them as 8 bytes (the eight
+// rows of the group are 128 contiguous bytes in each half of the tile). For the two sign modes the sign bits of four
+// elements come out of one byte permute (the high bytes of four 16-bit floats) and one shift-and-mask.
+// `ksplit` (1, 2, 4 or 8) warps of a CTA share a row group by K blocks, so that a matrix with few rows still puts
+// loads from every SM in flight; their row sums meet in shared memory.
+template <typename T>
+struct RawBlock {
+    T v[8][8];      // [piece j][element e]
+};
+
+template <typename T>
+__device__ __forceinline__ void load_block(RawBlock<T>& raw, const T* __restrict__ rp, long long k0, long long K, bool live, bool vec_ok) {
+#pragma unroll
+    for (int j = 0; j < 8; j++) {
+        const long long k = k0 + 32 * j;
+        if (sizeof(T) == 2 && live && vec_ok && k + 8 <= K) {
+            *reinterpret_cast<uint4*>(raw.v[j]) = __ldcs(reinterpret_cast<const uint4*>(rp + k));
+        } else {
+#pragma unroll
+            for (int e = 0; e < 8; e++) raw.v[j][e] = (live && k + e < K) ? rp[k + e] : T();
+        }
+    }
+}
+
+template <typename T>
+__device__ __forceinline__ void bits_of_block(const RawBlock<T>& raw, long long k0, long long K, bool live, bool vec_ok, int mode, bool want_mag,
+                                              uint32_t& w0, uint32_t& w1, float& mag) {
+    w0 = 0;
+    w1 = 0;
+    if (!live) return;
+    if (sizeof(T) == 2 && vec_ok && k0 + 32 * 7 + 8 <= K) {         // all eight pieces complete
+        if (mode == BGEMM_WBIT_NEGATIVE || mode == BGEMM_WBIT_NONNEGATIVE) {
+#pragma unroll
+            for (int j = 0; j < 8; j++) {
+                const uint4 q = *reinterpret_cast<const uint4*>(raw.v[j]);
+                const uint32_t hi0 = __byte_perm(q.x, q.y, 0x7531), hi1 = __byte_perm(q.z, q.w, 0x7531);   // high bytes of e0..e3, e4..e7
+                w0 |= (hi0 >> (7 - j)) & (0x01010101u << j);
+                w1 |= (hi1 >> (7 - j)) & (0x01010101u << j);
+            }
+            if (mode == BGEMM_WBIT_NONNEGATIVE) {
+                w0 = ~w0;
+                w1 = ~w1;
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < 8; j++) {
+                const uint4 q = *reinterpret_cast<const uint4*>(raw.v[j]);
+                const uint32_t q0 = weight_bits_x2(q.x, mode), q1 = weight_bits_x2(q.y, mode);
+                const uint32_t q2 = weight_bits_x2(q.z, mode), q3 = weight_bits_x2(q.w, mode);
+                w0 |= ((((q0 | (q0 >> 8)) & 0x101u) | (((q1 | (q1 >> 8)) & 0x101u) << 16))) << j;
+                w1 |= ((((q2 | (q2 >> 8)) & 0x101u) | (((q3 | (q3 >> 8)) & 0x101u) << 16))) << j;
+            }
+        }
+        if (want_mag) {
+#pragma unroll
+            for (int j = 0; j < 8; j++)
+#pragma unroll
+                for (int e = 0; e < 8; e++) mag += Elem<T>::mag(raw.v[j][e]);
+        }
+    } else {
+#pragma unroll
+        for (int j = 0; j < 8; j++) {
+#pragma unroll
+            for (int e = 0; e < 8; e++) {
+                if (k0 + 32 * j + e < K) {
+                    const uint32_t bit = (uint32_t)weight_bit<T>(raw.v[j][e], mode);
+                    if (e < 4) w0 |= bit << (8 * e + j); else w1 |= bit << (8 * (e - 4) + j);
+                    if (want_mag) mag += Elem<T>::mag(raw.v[j][e]);
+                }
+            }
+        }
+    }
+}
+
 template <typename T>
 __global__ void __launch_bounds__(256) pack_weights_kernel(const T* __restrict__ src, long long M, long long K, long long ld, int mode,
                                                            uint8_t* __restrict__ plane, int32_t* __restrict__ rowpop,
                                                            __half* __restrict__ alpha, long long src_batch_stride,
-                                                           long long plane_batch_bytes) {
+                                                           long long plane_batch_bytes, int ksplit) {
     grid_launch_dependents();
     grid_dependency_wait();
-    const int lane = threadIdx.x & 31;
-    const long long row = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    __shared__ int s_pop[8][8];         // [warp][row of the group]: partial row sums of the warps that share a group
+    __shared__ float s_mag[8][8];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int kpart = warp % ksplit, rg = lane >> 2, cp = lane & 3;
+    const long long group = (long long)blockIdx.x * (8 / ksplit) + warp / ksplit;
+    const long long row = group * 8 + rg;
     const long long batch = blockIdx.y;
     const long long mtiles = (M + 127) / 128, kblocks = (K + 255) / 256;
-    if (row >= mtiles * 128) return;
+    const bool in_plane = row < mtiles * 128;
+    const bool live = row < M;
     src += batch * src_batch_stride;
     plane += batch * plane_batch_bytes;
-    const bool live = row < M;
     const T* rp = src + row * ld;
-    const int j = lane >> 2;
+    const bool vec_ok = (sizeof(T) == 2) && ((reinterpret_cast<uintptr_t>(rp) & 15) == 0);
+    const bool want_mag = alpha != nullptr;
+    uint8_t* dst = plane + (row / 128) * kblocks * 4096 + (cp >> 1) * 2048 + (int)(row % 128) * 16 + (cp & 1) * 8;
     int pop = 0;
     float mag = 0.f;
-    uint8_t* tile_row = plane + (row / 128) * kblocks * 4096;
-    const int r = (int)(row % 128);
-    const bool vec_ok = (sizeof(T) == 2) && ((reinterpret_cast<uintptr_t>(rp) & 15) == 0);
-    constexpr int U = 4;        // K blocks in flight per warp: four independent 16-byte streaming loads per lane
-    for (long long kb0 = 0; kb0 < kblocks; kb0 += U) {
-        T v[U][8];
+    constexpr int U = sizeof(T) == 2 ? 2 : 1;       // K blocks in flight per warp (16 loads of 16 bytes per lane)
+    for (long long kb0 = kpart; kb0 < kblocks; kb0 += (long long)ksplit * U) {
+        RawBlock<T> raw[U];
 #pragma unroll
         for (int u = 0; u < U; u++) {
-            const long long k0 = (kb0 + u) * 256 + lane * 8;
-            if (live && k0 < K) {
-                if (vec_ok && k0 + 8 <= K) {
-                    *reinterpret_cast<uint4*>(v[u]) = __ldcs(reinterpret_cast<const uint4*>(rp + k0));
-                } else {
-#pragma unroll
-                    for (int e = 0; e < 8; e++) v[u][e] = (k0 + e < K) ? rp[k0 + e] : T();
-                }
-            }
+            const long long kb = kb0 + (long long)u * ksplit;
+            if (kb < kblocks) load_block(raw[u], rp, kb * 256 + 8 * cp, K, live, vec_ok);
         }
 #pragma unroll
         for (int u = 0; u < U; u++) {
-            const long long kb = kb0 + u;
+            const long long kb = kb0 + (long long)u * ksplit;
             if (kb >= kblocks) break;
-            const long long k0 = kb * 256 + lane * 8;
-            uint32_t w0 = 0, w1 = 0;
-            if (live && vec_ok && k0 + 8 <= K) {
-                // element e of the lane -> bit 8 (e % 4) + j of word e / 4, two elements per operation
-                const uint4 raw = *reinterpret_cast<const uint4*>(v[u]);
-                const uint32_t q0 = weight_bits_x2(raw.x, mode), q1 = weight_bits_x2(raw.y, mode);
-                const uint32_t q2 = weight_bits_x2(raw.z, mode), q3 = weight_bits_x2(raw.w, mode);
-                w0 = ((((q0 | (q0 >> 8)) & 0x101u) | (((q1 | (q1 >> 8)) & 0x101u) << 16))) << j;
-                w1 = ((((q2 | (q2 >> 8)) & 0x101u) | (((q3 | (q3 >> 8)) & 0x101u) << 16))) << j;
-                if (alpha) {
-#pragma unroll
-                    for (int e = 0; e < 8; e++) mag += Elem<T>::mag(v[u][e]);
-                }
-            } else if (live && k0 < K) {
-#pragma unroll
-                for (int e = 0; e < 8; e++) {
-                    if (k0 + e < K) {
-                        const uint32_t bit = (uint32_t)weight_bit<T>(v[u][e], mode);
-                        if (e < 4) w0 |= bit << (8 * e + j); else w1 |= bit << (8 * (e - 4) + j);
-                        if (alpha) mag += Elem<T>::mag(v[u][e]);
-                    }
-                }
-            }
-#pragma unroll
-            for (int off = 4; off < 32; off <<= 1) {
-                w0 |= __shfl_xor_sync(0xffffffffu, w0, off);
-                w1 |= __shfl_xor_sync(0xffffffffu, w1, off);
-            }
-            if (lane < 4) {
-                pop += __popc(w0) + __popc(w1);
-                *reinterpret_cast<uint2*>(tile_row + kb * 4096 + tile_word_offset(r, 2 * lane)) = make_uint2(w0, w1);
-            }
+            uint32_t w0, w1;
+            bits_of_block(raw[u], kb * 256 + 8 * cp, K, live, vec_ok, mode, want_mag, w0, w1, mag);
+            pop += __popc(w0) + __popc(w1);
+            if (in_plane) *reinterpret_cast<uint2*>(dst + kb * 4096) = make_uint2(w0, w1);
         }
     }
-    if (live && (rowpop || alpha)) {
-#pragma unroll
-        for (int off = 16; off > 0; off >>= 1) {
-            pop += __shfl_xor_sync(0xffffffffu, pop, off);
-            mag += __shfl_xor_sync(0xffffffffu, mag, off);
+    if (rowpop || alpha) {
+        pop += __shfl_xor_sync(0xffffffffu, pop, 1);
+        pop += __shfl_xor_sync(0xffffffffu, pop, 2);
+        mag += __shfl_xor_sync(0xffffffffu, mag, 1);
+        mag += __shfl_xor_sync(0xffffffffu, mag, 2);
+        if (ksplit > 1) {
+            if (cp == 0) {
+                s_pop[warp][rg] = pop;
+                s_mag[warp][rg] = mag;
+            }
+            __syncthreads();
+            if (kpart == 0 && cp == 0) {
+                for (int i = 1; i < ksplit; i++) {
+                    pop += s_pop[warp + i][rg];
+                    mag += s_mag[warp + i][rg];
+                }
+            }
         }
-        if (lane == 0) {
+        if (kpart == 0 && cp == 0 && live) {
             if (rowpop) rowpop[batch * M + row] = pop;
             if (alpha) alpha[batch * M + row] = __float2half_rn(mag / (float)K);
         }
@@ -298,46 +353,89 @@ __global__ void __launch_bounds__(256, 4) prepare_acts_kernel(const T* __restric
     }
 }
 
-// Transposing variant: source is [K, N]; a block owns 32 output rows (n) and walks K in 32-wide tiles.
+// Transposing variant: source is [K, N]. A CTA owns 64 output rows (n) and walks K in tiles of 128. Thread (kq, nc)
+// reads four source rows k = 4 kq .. 4 kq + 3 at columns 8 nc .. 8 nc + 7 (one 16-byte load per row for 2-byte types; the
+// eight threads of a row cover 128 contiguous bytes), converts them, transposes the 4 x 8 bytes in registers with byte
+// permutes and writes eight 32-bit words (four consecutive k of one n each) into a [64][32 + 1]-word tile; the tile
+// leaves as 16-byte stores, 128 contiguous bytes per output row. Column sums are kept per thread (dp4a over each word)
+// and meet in shared memory. With `kparts` > 1 the K tiles are divided over gridDim.z and the sums are added to a
+// zeroed `colsum` atomically (integers: the result does not depend on the order).
 template <typename T>
 __global__ void __launch_bounds__(256) prepare_acts_t_kernel(const T* __restrict__ src, long long N, long long K, long long ld, int mode,
                                                              int8_t* __restrict__ dst, int32_t* __restrict__ colsum,
-                                                             long long src_batch_stride) {
-    __shared__ int8_t tile[32][33];
-    __shared__ int part[8][32];
+                                                             long long src_batch_stride, int kparts) {
+    __shared__ uint32_t tile[64][33];
+    __shared__ int s_col[64];
     grid_launch_dependents();
     grid_dependency_wait();
-    const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
-    const long long n0 = (long long)blockIdx.x * 32;
+    const int t = threadIdx.x, nc = t & 7, kq = t >> 3;
+    const long long n0 = (long long)blockIdx.x * 64;
     const long long batch = blockIdx.y;
-    const long long kld = (K + 255) / 256 * 256;
+    const long long kld = (K + 255) / 256 * 256, ktiles = kld / 128;
+    const long long kt_begin = ktiles * blockIdx.z / kparts, kt_end = ktiles * (blockIdx.z + 1) / kparts;
     const T* sp = src + batch * src_batch_stride;
     int8_t* dp = dst + batch * N * kld;
-    int sum = 0;
-    for (long long k0 = 0; k0 < kld; k0 += 32) {
+    const bool vec_ok = sizeof(T) == 2 && (reinterpret_cast<uintptr_t>(sp) & 15) == 0 && (ld * (long long)sizeof(T)) % 16 == 0;
+    const long long nbase = n0 + 8 * nc;
+    if (t < 64) s_col[t] = 0;
+    int acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    for (long long kt = kt_begin; kt < kt_end; kt++) {
+        const long long k0 = kt * 128, kbase = k0 + 4 * kq;
+        uint2 b[4];
 #pragma unroll
         for (int i = 0; i < 4; i++) {
-            const long long k = k0 + ty + 8 * i, n = n0 + tx;
-            int8_t v = 0;
-            if (k < K && n < N) v = act_value<T>(sp[k * ld + n], mode);
-            sum += v;
-            tile[ty + 8 * i][tx] = v;
+            const long long k = kbase + i;
+            if (sizeof(T) == 2 && vec_ok && k < K && nbase + 8 <= N) {
+                int unused = 0;
+                b[i] = act_values_x8(__ldcs(reinterpret_cast<const uint4*>(sp + k * ld + nbase)), mode, unused);
+            } else {
+                uint32_t w[2] = {0u, 0u};
+#pragma unroll
+                for (int e = 0; e < 8; e++) {
+                    if (k < K && nbase + e < N) w[e >> 2] |= (uint32_t)(uint8_t)act_value<T>(sp[k * ld + nbase + e], mode) << (8 * (e & 3));
+                }
+                b[i] = make_uint2(w[0], w[1]);
+            }
+        }
+        uint32_t out[8];
+        {
+            const uint32_t lo01 = __byte_perm(b[0].x, b[1].x, 0x5140), hi01 = __byte_perm(b[0].x, b[1].x, 0x7362);
+            const uint32_t lo23 = __byte_perm(b[2].x, b[3].x, 0x5140), hi23 = __byte_perm(b[2].x, b[3].x, 0x7362);
+            out[0] = __byte_perm(lo01, lo23, 0x5410);
+            out[1] = __byte_perm(lo01, lo23, 0x7632);
+            out[2] = __byte_perm(hi01, hi23, 0x5410);
+            out[3] = __byte_perm(hi01, hi23, 0x7632);
+        }
+        {
+            const uint32_t lo01 = __byte_perm(b[0].y, b[1].y, 0x5140), hi01 = __byte_perm(b[0].y, b[1].y, 0x7362);
+            const uint32_t lo23 = __byte_perm(b[2].y, b[3].y, 0x5140), hi23 = __byte_perm(b[2].y, b[3].y, 0x7362);
+            out[4] = __byte_perm(lo01, lo23, 0x5410);
+            out[5] = __byte_perm(lo01, lo23, 0x7632);
+            out[6] = __byte_perm(hi01, hi23, 0x5410);
+            out[7] = __byte_perm(hi01, hi23, 0x7632);
+        }
+#pragma unroll
+        for (int e = 0; e < 8; e++) {
+            acc[e] = __dp4a((int)out[e], 0x01010101, acc[e]);
+            tile[8 * nc + e][kq] = out[e];
         }
         __syncthreads();
 #pragma unroll
-        for (int i = 0; i < 4; i++) {
-            const long long n = n0 + ty + 8 * i;
-            if (n < N) dp[n * kld + k0 + tx] = tile[tx][ty + 8 * i];
+        for (int h = 0; h < 2; h++) {
+            const int idx = t + 256 * h, nl = idx >> 3, c = idx & 7;
+            if (n0 + nl < N)
+                *reinterpret_cast<uint4*>(dp + (n0 + nl) * kld + k0 + 16 * c) =
+                    make_uint4(tile[nl][4 * c], tile[nl][4 * c + 1], tile[nl][4 * c + 2], tile[nl][4 * c + 3]);
         }
         __syncthreads();
     }
-    part[ty][tx] = sum;
     __syncthreads();
-    if (ty == 0 && n0 + tx < N) {
-        int s = 0;
 #pragma unroll
-        for (int i = 0; i < 8; i++) s += part[i][tx];
-        colsum[batch * N + n0 + tx] = s;
+    for (int e = 0; e < 8; e++) atomicAdd(&s_col[8 * nc + e], acc[e]);
+    __syncthreads();
+    if (t < 64 && n0 + t < N) {
+        if (kparts > 1) atomicAdd(&colsum[batch * N + n0 + t], s_col[t]);
+        else colsum[batch * N + n0 + t] = s_col[t];
     }
 }
 
@@ -395,12 +493,16 @@ __global__ void __launch_bounds__(256) retile_kernel(const uint32_t* __restrict_
 
 int launch_pack_weights(cudaStream_t stream, const void* src, int dtype, long long M, long long K, long long ld, int wbit_mode,
                         void* plane, int32_t* rowpop, void* alpha, long long batch, long long src_batch_stride) {
-    const long long rows = (M + 127) / 128 * 128;
-    dim3 grid((unsigned)((rows + 7) / 8), (unsigned)batch);
+    // Groups of eight rows, one warp each; with fewer groups than fill the GPU, up to eight warps share a group by K blocks.
+    const long long groups = (M + 127) / 128 * 16, kblocks = (K + 255) / 256;
+    int ksplit = 1;
+    while (ksplit < 8 && groups * batch * ksplit < 16LL * sm_count() && 2 * ksplit <= kblocks) ksplit *= 2;
+    dim3 grid((unsigned)(groups / (8 / ksplit)), (unsigned)batch);
     const long long pbytes = (long long)bgemm_plane_bytes(M, K);
     cudaError_t e = cudaSuccess;
     BGEMM_DISPATCH_DTYPE(dtype, (e = launch_pdl(pack_weights_kernel<T>, grid, dim3(256), stream, static_cast<const T*>(src), M, K, ld, wbit_mode,
-                                                static_cast<uint8_t*>(plane), rowpop, static_cast<__half*>(alpha), src_batch_stride, pbytes)));
+                                                static_cast<uint8_t*>(plane), rowpop, static_cast<__half*>(alpha), src_batch_stride, pbytes,
+                                                ksplit)));
     count_launch();
     return (int)(e != cudaSuccess ? e : cudaGetLastError());
 }
@@ -409,9 +511,17 @@ int launch_prepare_acts(cudaStream_t stream, const void* src, int dtype, long lo
                         int transpose, int8_t* dst, int32_t* colsum, long long batch, long long src_batch_stride) {
     cudaError_t e = cudaSuccess;
     if (transpose) {
-        dim3 grid((unsigned)((N + 31) / 32), (unsigned)batch);
+        // One CTA per 64 output rows and problem; with fewer CTAs than SMs the K tiles are divided over gridDim.z as well.
+        const long long ctas = (N + 63) / 64 * batch, ktiles = (K + 255) / 256 * 2;
+        int kparts = 1;
+        while (kparts < 32 && ctas * kparts < sm_count() && 2 * kparts <= ktiles) kparts *= 2;
+        if (kparts > 1) {
+            e = cudaMemsetAsync(colsum, 0, sizeof(int32_t) * (size_t)(N * batch), stream);
+            if (e != cudaSuccess) return (int)e;
+        }
+        dim3 grid((unsigned)((N + 63) / 64), (unsigned)batch, (unsigned)kparts);
         BGEMM_DISPATCH_DTYPE(dtype, (e = launch_pdl(prepare_acts_t_kernel<T>, grid, dim3(256), stream, static_cast<const T*>(src), N, K, ld, act_mode,
-                                                    dst, colsum, src_batch_stride)));
+                                                    dst, colsum, src_batch_stride, kparts)));
     } else {
         // At most one resident wave of 8-warp CTAs (4 per SM): longer launches give every warp several rows, launches
         // far below a wave split every row over 2, 4 or 8 warps.
