@@ -11,7 +11,8 @@
 // epilogue drains the other one) and a ring of u8 weight operand stages of 64 columns.
 //   warps 0-15   unpack, sets of four warps taking the K blocks of the CTA's whole K-block stream in turn (four sets with
 //                128-column tiles, two with 64-column tiles)
-//   warps 16-19  epilogue: accumulator -> shared memory staging tile -> scaled / converted 16-byte stores
+//   warps 16-19  epilogue: accumulator -> shared memory staging tile -> scaled / converted 16-byte stores (with
+//                64-column tiles warps 8-11 are a second epilogue group: each group drains one of the two accumulators)
 //   warp 20      tensor-memory allocation; one lane issues the UMMAs of the even K blocks of the stream
 //   warp 23      one lane issues the UMMAs of the odd K blocks
 //   warp 21      one lane streams the packed weight tiles (cp.async.bulk)
@@ -27,13 +28,14 @@
 
 namespace bgemm {
 
-// Warp roles: up to 16 unpack warps (sets of four; warps 4 * NSETS .. 15 exit at once when a variant uses fewer sets),
-// 4 epilogue warps, two UMMA issuers, two copy producers.
+// Warp roles: up to 16 unpack warps (sets of four; with two sets warps 8-11 are a second epilogue group and 12-15 exit
+// at once), 4 epilogue warps, two UMMA issuers, two copy producers.
 constexpr int kPThreads = 768;
-constexpr int kPEpiThreads = 128;
+constexpr int kPEpiThreads = 128;                 // per epilogue group
 constexpr int kPWarpEpi = 16, kPWarpMma0 = 20, kPWarpW = 21, kPWarpB = 22, kPWarpMma1 = 23;
 // 768 threads start with 80 registers each; the unpack warps release down to 48 and the four epilogue warps take 160
-constexpr int kPUnpackRegs = 48, kPEpiRegs = 160;
+// (with two epilogue groups: 128 each, and the four warps without a role release down to 24)
+constexpr int kPUnpackRegs = 48, kPIdleRegs = 24;
 constexpr long long kCopyDrainClocks = 4000000;   // ~2 ms: far beyond any TMA copy of a 32 KB tile
 
 template <int NT>
@@ -54,12 +56,19 @@ struct PCfg {
     // the tile width: with 128-column tiles (512 clocks of UMMA per K block) two sets cap the kernel at ~1050 clocks per
     // K block; four sets lift that cap.
     static constexpr int NSETS = NT == 128 ? 4 : 2;
+    // Epilogue groups of four warps (a warp reaches the tensor-memory lanes 32 (warp % 4) ... + 31 only). With two
+    // unpack sets warps 8-11 form a second group: group g drains accumulator buffer g, i.e. the tiles lt of the CTA with
+    // lt % 2 == g, with its own staging tile, scales and barriers. One group alone (four warps, one per scheduler, one
+    // dependent instruction every ~5 clocks) needs ~3200 clocks for a 128 x 64 tile -- more than the two K blocks of an
+    // attention tile take -- and was what the batched attention product waited for.
+    static constexpr int EPI_GROUPS = NSETS == 2 ? 2 : 1;
+    static constexpr int EPI_REGS = EPI_GROUPS == 2 ? 128 : 160;
     static constexpr int W_STAGES = NSETS == 4 ? 4 : 6;
     static constexpr int STAGE_TILE_BYTES = NT * 128 * 4;
     // w_full/w_empty, full/empty, d_full[2], d_empty[2], first_done[2], drained
     static constexpr int NBARS = 2 * W_STAGES + 2 * STAGES + 7;
-    static constexpr int MISC_BYTES = 512 /*barriers*/ + 512 /*alpha*/ + 1024 /*colsum*/ + 512 /*flags*/;
-    static constexpr int SMEM_BYTES = STAGES * B_STAGE_BYTES + W_STAGES * 4096 + STAGE_TILE_BYTES + MISC_BYTES + 1024 /*align*/;
+    static constexpr int MISC_BYTES = 512 /*barriers*/ + 512 /*alpha*/ + 1024 /*colsum, per group*/ + 512 /*flags*/ + 512 /*alpha, second group*/;
+    static constexpr int SMEM_BYTES = STAGES * B_STAGE_BYTES + W_STAGES * 4096 + EPI_GROUPS * STAGE_TILE_BYTES + MISC_BYTES + 1024 /*align*/;
     // K block g of the CTA's stream uses stage g % STAGES, is unpacked by set g % 2 and issued by issuer g % 2:
     // with even stage counts a stage and its barriers always meet the same set and the same issuer, so every
     // parity wait has seen the previous phase of its barrier.
@@ -82,7 +91,7 @@ __global__ void __launch_bounds__(kPThreads, 1) gemm_persist_kernel(const __grid
     uint8_t* sB = smem;
     uint8_t* sW = sB + C::STAGES * C::B_STAGE_BYTES;
     int* sP = reinterpret_cast<int*>(sW + C::W_STAGES * 4096);
-    uint8_t* misc = reinterpret_cast<uint8_t*>(sP) + C::STAGE_TILE_BYTES;
+    uint8_t* misc = reinterpret_cast<uint8_t*>(sP) + C::EPI_GROUPS * C::STAGE_TILE_BYTES;
     uint64_t* bars = reinterpret_cast<uint64_t*>(misc);
     float* s_alpha = reinterpret_cast<float*>(misc + 512);
     int* s_colsum = reinterpret_cast<int*>(misc + 1024);
@@ -240,7 +249,7 @@ __global__ void __launch_bounds__(kPThreads, 1) gemm_persist_kernel(const __grid
             umma_commit(drained);
             if (me == 0) { BGEMM_PUT(16, twf); BGEMM_PUT(24, clock64() - tloop0); BGEMM_PUT(27, twd); }
         }
-    } else if (warp < 16) {
+    } else if (warp < 4 * C::NSETS) {
         // ---------------- unpack: set s = warps 4 s .. 4 s + 3 takes the K blocks g of the stream with g % NSETS == s ----
         regs_release<kPUnpackRegs>();
         const int set = warp >> 2;
@@ -250,7 +259,7 @@ __global__ void __launch_bounds__(kPThreads, 1) gemm_persist_kernel(const __grid
         bool ok = true;
         BGEMM_TUNING_ONLY(long long tww = 0, twe = 0;)
         BGEMM_TUNING_ONLY(const long long tloop0 = clock64();)
-        for (long long g = set; g < total_kb && ok && set < C::NSETS; g += C::NSETS) {
+        for (long long g = set; g < total_kb && ok; g += C::NSETS) {
             const int ws = (int)(g % C::W_STAGES);
             BGEMM_TIMED(tww, ok = mbar_wait(w_full + 8 * ws, (uint32_t)(g / C::W_STAGES) & 1, abort_flag, p.status, 27));
             ok = __all_sync(0xffffffffu, ok);
@@ -283,19 +292,26 @@ __global__ void __launch_bounds__(kPThreads, 1) gemm_persist_kernel(const __grid
         }
         if (tid == 0) { BGEMM_PUT(18, tww); BGEMM_PUT(19, twe); BGEMM_PUT(25, clock64() - tloop0); }
         if (tid == 128) { BGEMM_PUT(22, tww); BGEMM_PUT(23, twe); }
-    } else if (warp >= kPWarpEpi && warp < kPWarpEpi + 4) {
+    } else if ((warp >= kPWarpEpi && warp < kPWarpEpi + 4) || (C::EPI_GROUPS == 2 && warp >= 8 && warp < 12)) {
         // ---------------- epilogue: overlaps the mainloop of the next tile ----------------
-        regs_request<kPEpiRegs>();
-        const int et = tid - kPWarpEpi * 32;                  // 0..127 == accumulator row == tensor-memory lane
+        regs_request<C::EPI_REGS>();
+        const int ge = warp >= kPWarpEpi ? 0 : 1;             // epilogue group
+        const int et = (warp & 3) * 32 + lane;                // 0..127 == accumulator row == tensor-memory lane
         const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
+        if (ge) {                                             // the second group's staging tile, scales and column sums
+            sP += C::STAGE_TILE_BYTES / 4;
+            s_alpha = reinterpret_cast<float*>(misc + 2560);
+            s_colsum += 128;
+        }
+        const int bar_a = 2 + 2 * ge, bar_b = 3 + 2 * ge;     // named barriers of the group
         TileOut tout;
         tout.p = &p; tout.s_alpha = s_alpha; tout.s_colsum = s_colsum;
         // [M, N] results are stored straight from registers (the same for [N, M] results -- 2-byte stores a row pitch
         // apart -- measured 2.4 x slower than the staged path: 381 against 158 us on the 95-layer pool)
         const bool direct = p.out_layout == BGEMM_LAYOUT_MN && p.out_kind != kOutActs;
         BGEMM_TUNING_ONLY(long long twd = 0, tbusy = 0;)
-        long long lt = 0;
-        for (long long t = blockIdx.x; t < total_tiles; t += gridDim.x, lt++) {
+        long long lt = ge;
+        for (long long t = blockIdx.x + (long long)ge * gridDim.x; t < total_tiles; t += (long long)C::EPI_GROUPS * gridDim.x, lt += C::EPI_GROUPS) {
             const int nt = (int)(t % p.ntiles);
             const long long bm = t / p.ntiles;
             const int mt = (int)(bm % p.mtiles), batch = (int)(bm / p.mtiles);
@@ -319,7 +335,7 @@ __global__ void __launch_bounds__(kPThreads, 1) gemm_persist_kernel(const __grid
                 // [M, N] results: an accumulator row leaves tensor memory as consecutive columns, which are consecutive
                 // addresses of the result row -- they are converted and stored straight from registers (no staging, no
                 // second pass); the barrier makes this tile's scales and column sums visible to all four warps.
-                if (named_bar_or(2, kPEpiThreads, !ok)) break;
+                if (named_bar_or(bar_a, kPEpiThreads, !ok)) break;
                 tc_fence_after();
 #pragma unroll 1
                 for (int n0 = 0; n0 < NT; n0 += 32) {
@@ -361,15 +377,17 @@ __global__ void __launch_bounds__(kPThreads, 1) gemm_persist_kernel(const __grid
                 if (lane == 0) mbar_arrive(d_empty + 8 * buf);   // the accumulator may be overwritten from here on
             }
             // One answer for all four warps: either everybody stores this tile or everybody leaves.
-            if (named_bar_or(2, kPEpiThreads, !ok)) break;
+            if (named_bar_or(bar_a, kPEpiThreads, !ok)) break;
             write_tile<false>(tout, sP, 1, 0, 0, NT, et, kPEpiThreads);
             }
-            named_bar_sync(3, kPEpiThreads);                      // staging tile and scales are free for the next tile
+            named_bar_sync(bar_b, kPEpiThreads);                      // staging tile and scales are free for the next tile
 #ifdef BGEMM_TUNING
             if (p.prof) tbusy += clock64() - tb0;
 #endif
         }
-        if (et == 0) { BGEMM_PUT(28, twd); BGEMM_PUT(29, tbusy); }
+        if (et == 0 && ge == 0) { BGEMM_PUT(28, twd); BGEMM_PUT(29, tbusy); }
+    } else if (warp < 16) {
+        regs_release<kPIdleRegs>();     // no role in this variant: the registers go to the epilogue warps
     }
     if (tid == 0) BGEMM_STAMP(8);
     tc_fence_before();
