@@ -29,7 +29,7 @@ def _case(M, K, N, batch, seed):
 
 
 @pytest.mark.parametrize("M,K,N,batch,codes", [(128, 4096, 64, 1, range(11, 19)),       # one CTA of the tile-per-CTA kernel
-                                               (256, 2048, 128, 100, range(21, 30))])   # persistent kernel, every CTA
+                                               (256, 2048, 128, 160, range(21, 30))])   # persistent kernel, every CTA
 def test_withheld_weight_tile_makes_the_wait_run_out_and_the_kernel_return(B, M, K, N, batch, codes):
     w, x = _case(M, K, N, batch, 5)
     ref = O.ref_acc(w, x, O.OP_BWTA)
