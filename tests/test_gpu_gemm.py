@@ -145,6 +145,18 @@ def test_gemm_all_tile_widths(B, op, N):
     assert torch.equal(got, O.ref_acc(w, x, op))
 
 
+@pytest.mark.parametrize("M,K,N", [(19200, 512, 24), (19300, 768, 32), (38400, 300, 17)])
+def test_few_columns_on_more_row_tiles_than_sms(B, M, K, N):
+    """17-32 activation rows with more 128-row tiles than SMs run on 64-column tiles (half of them padding): two CTAs per
+    SM, or the persistent kernel beyond two tiles per SM."""
+    g = O._gen(M + K + N)
+    for op in (O.OP_XOR, O.OP_BWTA):
+        w = _rand_w(M, K, g, "randn")
+        x = _acts_for(op, N, K, g)
+        assert torch.equal(_run(B, w, x, op, split_k=1), O.ref_acc(w, x, op)), (op, M, K, N)
+        assert torch.equal(_run(B, w, x, op, split_k=0), O.ref_acc(w, x, op)), (op, M, K, N)
+
+
 @pytest.mark.parametrize("M,K", [(128, 256), (130, 384), (10, 4096), (257, 1000), (640, 129), (1, 1), (300, 8192)])
 @pytest.mark.parametrize("N", [3, 24, 64, 130])
 @pytest.mark.parametrize("split_k", [1, 0, 3, 8, 12])
