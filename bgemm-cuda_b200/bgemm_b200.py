@@ -55,6 +55,8 @@ lib.bgemm_w1a16_gemm.argtypes = [_vp, _vp, _i64, _i64, _vp, _i64, _i64, _vp, _in
 lib.bgemm_gemm_to_acts.argtypes = [_vp, _vp, _i64, _i64, _vp, _vp, _i64, _int, _vp, _int, _vp, _vp, _int, _vp, _sz, _i64]
 lib.bgemm_gemm_workspace_bytes.restype = _sz
 lib.bgemm_gemm_workspace_bytes.argtypes = [_i64, _i64, _i64, _int, _i64]
+lib.bgemm_debug_set_pair_kernel.restype = None
+lib.bgemm_debug_set_pair_kernel.argtypes = [_int]
 lib.bgemm_gemm_balance_workspace_bytes.restype = _sz
 lib.bgemm_gemm_balance_workspace_bytes.argtypes = [_i64, _i64, _i64, _int, _i64]
 lib.bgemm_gemm_auto_split_k.argtypes = [_i64, _i64, _i64, _i64]

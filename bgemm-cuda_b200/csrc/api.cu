@@ -165,6 +165,8 @@ void bgemm_debug_set_wait_test(int64_t wait_budget_clocks, int skip_kblock) {
     g_test_skip_kblock.store(skip_kblock >= 0 ? skip_kblock : -1, std::memory_order_relaxed);
 }
 
+void bgemm_debug_set_pair_kernel(int mode) { set_pair_mode(mode); }
+
 int bgemm_device_status(int reset) {
     int* w = device_status_word();
     if (!w) return BGEMM_ERR_DRIVER;

@@ -30,6 +30,8 @@
 // of the same name in both CTAs. Every wait is bounded as in the other kernels, and both CTAs meet in a cluster
 // barrier before either frees tensor memory or exits, so no signal is ever sent to a CTA that has left.
 #include <cuda.h>
+
+#include <atomic>
 #include <cuda_fp16.h>
 
 #include <cstdlib>
@@ -639,29 +641,50 @@ static int env_int_q(const char* name) {
     const char* e = std::getenv(name);
     return e ? std::atoi(e) : -1;
 }
-static int pair_forced() { static const int v = env_int_q("BGEMM_PAIR"); return v; }       // 0: never, 1: whenever the shape allows
+// BGEMM_PAIR in the environment, or bgemm_debug_set_pair_kernel at run time (which wins): 0 = never, 1 = whenever the
+// shape allows, anything else = the rule below.
+static std::atomic<int> g_pair_mode{-2};        // -2: not set by the hook
+static int pair_forced() {
+    static const int env = env_int_q("BGEMM_PAIR");
+    const int m = g_pair_mode.load(std::memory_order_relaxed);
+    return m == -2 ? env : m;
+}
+void set_pair_mode(int mode) { g_pair_mode.store(mode < -1 || mode > 1 ? -2 : mode, std::memory_order_relaxed); }
 
-// Shapes the pair kernel takes: wide activation matrices (at least one full 256-column tile), an even number of
-// 128-row tiles, no K partitioning by the caller, no activation-producing epilogue.
+// Shapes the pair kernel CAN take: at least one full 256-column tile, an even number of 128-row tiles, two K blocks.
+static bool pair_possible(long long mtiles, long long N, long long kblocks) { return !(mtiles & 1) && N >= QCfg::NT && kblocks >= 2; }
+
+// ... and those it is given. Measured against the tile-per-CTA kernel (128-column tiles, two CTAs per SM) inside single
+// runs: a 256 x 256 tile costs ~8k clocks beyond its K blocks (1024 clocks each), so short K loses (K = 512 / 1024 /
+// 2048: 241 against 192, 248 against 218, 28.7 against 25.0 us; from K = 2560 on it wins: 145 against 165 us at
+// 28672 x 2560 x 2048); up to two tiles across N it is level or behind (28672 x 8192 x 512: 98.4 against 96.1; 12288 x
+// 4096 x 512: 36.3 against 30.3), from three on ahead (28672 x 8192 x 768: 120 against 134; x 1024: 158 against 172;
+// 11008 x 4096 x 2048: 74 against 91); a last tile that is mostly padding costs more than the pairing gains (N = 640:
+// 118 against 112, N = 320: 95 against 73); and with fewer than ~1.5 tiles per SM pair the cut into equal ranges no
+// longer covers the per-tile cost (8192 x 8192 x 768, 96 tiles: 54 against 48).
+static bool pair_worthwhile(long long mtiles, long long N, long long kblocks, long long batch) {
+    const long long n256 = (N + 255) / 256 * 256, n128 = (N + 127) / 128 * 128;
+    const long long tiles = (mtiles / 2) * (n256 / 256) * batch;
+    return kblocks >= 10 && N > 512 && n256 * 100 <= n128 * 107 && tiles * 4 >= (long long)sm_count() * 3;
+}
+
 bool pair_supported(const GemmParams& p, long long batch) {
     const int forced = pair_forced();
     if (forced == 0) return false;
-    if (p.split_k != 1 || (p.mtiles & 1) || p.N < QCfg::NT || p.out_kind == kOutActs || p.kblocks < 2) return false;
+    if (p.split_k != 1 || p.out_kind == kOutActs || !pair_possible(p.mtiles, p.N, p.kblocks)) return false;
     if (forced == 1) return true;
     if (p.test_skip_kblock >= 0) return false;
-    // worth it when every pair of SMs gets at least one tile
-    const long long tiles = (long long)(p.mtiles / 2) * ((p.N + QCfg::NT - 1) / QCfg::NT) * batch;
-    return tiles >= sm_count() / 2;
+    return pair_worthwhile(p.mtiles, p.N, p.kblocks, batch);
 }
 
 // Workspace with which the pair kernel cuts its work into exactly equal ranges: the 64 KiB counter area (flags; zeroed
 // once, left zero by every launch) and one partial accumulator per CTA. 0 when the shape would not use it.
 size_t pair_balance_workspace_bytes(long long M, long long N, long long K, long long batch) {
-    if (pair_forced() == 0) return 0;
+    const int forced = pair_forced();
+    if (forced == 0) return 0;
     const long long mtiles = (M + 127) / 128, kblocks = (K + 255) / 256;
-    if ((mtiles & 1) || N < QCfg::NT || kblocks < 2) return 0;
-    const long long tiles = (mtiles / 2) * ((N + QCfg::NT - 1) / QCfg::NT) * batch;
-    if (pair_forced() != 1 && tiles < sm_count() / 2) return 0;
+    if (!pair_possible(mtiles, N, kblocks)) return 0;
+    if (forced != 1 && !pair_worthwhile(mtiles, N, kblocks, batch)) return 0;
     return (size_t)65536 + (size_t)sm_count() * QCfg::PART_INTS * 4;
 }
 

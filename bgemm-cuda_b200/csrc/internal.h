@@ -70,6 +70,7 @@ int launch_gemm_persistent(cudaStream_t stream, const void* tensor_map, const Ge
 // Persistent kernel on CTA pairs, 256 x 256 tiles (gemm_pair.cu); `tensor_map` must have boxes of 128 activation rows
 // and p.ntiles must count 256-column tiles. With p.ws_counters / p.ws_partial set (64 KiB of zeroed flags, one partial
 // accumulator per CTA) it splits the work exactly.
+void set_pair_mode(int mode);      // bgemm_debug_set_pair_kernel
 bool pair_supported(const GemmParams& p, long long batch);
 int launch_gemm_pair(cudaStream_t stream, const void* tensor_map, const GemmParams& p, long long batch);
 size_t pair_balance_workspace_bytes(long long M, long long N, long long K, long long batch);   // 0: the shape would not use it

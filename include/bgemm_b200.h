@@ -322,6 +322,12 @@ int bgemm_device_status(int reset);
  * code through bgemm_device_status; its results are undefined. Nothing faults or hangs.                     */
 void bgemm_debug_set_wait_test(int64_t wait_budget_clocks, int skip_kblock);
 
+/* Test and tuning hook (no counterpart in the reference): which launches the kernel on SM pairs (256 x 256 tiles,
+ * tcgen05 cta_group::2) takes. 1 = every launch whose shape it can take (N >= 256, an even number of 128-row tiles,
+ * K > 256, no K partitioning), however small; 0 = none; -1 = the library's own rule (the default; the BGEMM_PAIR
+ * environment variable sets the same at load time). Process-wide; results never depend on it.             */
+void bgemm_debug_set_pair_kernel(int mode);
+
 #ifdef __cplusplus
 }
 #endif

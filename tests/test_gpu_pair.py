@@ -3,7 +3,9 @@ matrices): whole-tile and exact work splits (tiles accumulated in parts by sever
 workspace, including tiles cut into many parts), both output layouts, every output kind, every op, ragged M / N / K,
 batches, general int8 activations (accumulators beyond 16 bits take the int32 path of its epilogue), several
 destinations, repeated calls on one workspace, and replay from a CUDA graph. Every result is compared bit for bit with
-the CPU oracle. A child process forces the kernel onto small shapes that the dispatcher would give to other kernels."""
+the CPU oracle. The module switches the dispatcher to "the pair kernel wherever the shape allows it"
+(bgemm_debug_set_pair_kernel), since its own rule keeps short K and few tiles on other kernels; a child process does the
+same through the environment."""
 import os
 import subprocess
 import sys
@@ -22,7 +24,9 @@ ROOT = Path(__file__).resolve().parent.parent
 def B():
     import bgemm_b200
 
-    return bgemm_b200
+    bgemm_b200.lib.bgemm_debug_set_pair_kernel(1)
+    yield bgemm_b200
+    bgemm_b200.lib.bgemm_debug_set_pair_kernel(-1)           # back to the library's own rule
 
 
 def _inputs(op, batch, M, K, N, g, wide=False):
@@ -64,10 +68,21 @@ def _run(B, M, K, N, op=O.OP_BWTA, batch=1, layouts=(0, 1), kinds=(O.OUT_I32, O.
 
 
 def test_pair_kernel_is_what_runs(B):
-    """The shapes below reach the pair kernel through the normal dispatch: it reports a workspace for them."""
-    assert B.lib.bgemm_gemm_balance_workspace_bytes(2560, 2048, 1024, 0, 1) > 0
-    assert B.lib.bgemm_gemm_balance_workspace_bytes(2560, 128, 1024, 0, 1) == 0       # narrow: other kernels
-    assert B.lib.bgemm_gemm_balance_workspace_bytes(2432, 2048, 1024, 0, 1) == 0      # odd number of 128-row tiles
+    """Forced, every shape the kernel can take reports its workspace; by the library's own rule only long K, three or
+    more tiles across N without a mostly empty last one, and enough tiles for every SM pair do."""
+    ws = B.lib.bgemm_gemm_balance_workspace_bytes
+    assert ws(2560, 2048, 1024, 0, 1) > 0
+    assert ws(2560, 128, 1024, 0, 1) == 0            # narrow: other kernels
+    assert ws(2432, 2048, 1024, 0, 1) == 0           # odd number of 128-row tiles
+    B.lib.bgemm_debug_set_pair_kernel(-1)
+    try:
+        assert ws(28672, 1024, 8192, 0, 1) > 0 and ws(7168, 1024, 8192, 0, 1) > 0 and ws(28672, 768, 2560, 0, 1) > 0
+        assert ws(2560, 2048, 1024, 0, 1) == 0       # 4 K blocks
+        assert ws(28672, 512, 8192, 0, 1) == 0       # two tiles across N
+        assert ws(28672, 640, 8192, 0, 1) == 0       # the third tile would be half empty
+        assert ws(3584, 1024, 8192, 0, 1) == 0       # 56 tiles on 74 SM pairs
+    finally:
+        B.lib.bgemm_debug_set_pair_kernel(1)
 
 
 @pytest.mark.parametrize("M,K,N", [(2560, 1024, 2048),      # 80 tiles x 4 K blocks on 74 pairs: every tile boundary is cut
