@@ -81,6 +81,12 @@ static int resolve_split_k(long long M, long long N, long long K, long long batc
     if (s > kblocks / 2) s = kblocks / 2;
     if (s < 1) s = 1;
     if (s > kMaxClusterSplit) s = kMaxClusterSplit;
+    // every cluster resident at once: a launch that needs a second wave of clusters takes twice as long
+    while (s > 1) {
+        const int fit = max_resident_clusters(NT, (int)s, tiles * s <= sm_count());
+        if (fit < 0 || tiles <= fit) break;
+        s--;
+    }
     return (int)s;
 }
 

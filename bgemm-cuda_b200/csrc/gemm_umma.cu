@@ -30,6 +30,7 @@
 #include <cuda_fp16.h>
 
 #include <cstdlib>
+#include <mutex>
 
 #include "epilogue.cuh"
 #include "internal.h"
@@ -499,6 +500,60 @@ static int launch_variant(cudaStream_t stream, const CUtensorMap& tmap, const Ge
     const cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_kernel<NT, POW2, DEEP>, tmap, p);
     count_launch();
     return (int)(e != cudaSuccess ? e : cudaGetLastError());
+}
+
+// How many clusters of `split` CTAs of a kernel variant the device holds at once (-1: unknown, e.g. no device). A
+// cluster lives inside one GPC, so large clusters leave SMs unused: sixteen clusters of eight do not all fit, and a
+// launch that needs them runs in two waves (2048 x 8192 x 128: 18.3 us with 8 K partitions, 10.7 with 6).
+template <int NT, bool POW2, bool DEEP>
+static int resident_clusters_of(int split) {
+    using C = Cfg<NT, POW2, DEEP>;
+    if (cudaFuncSetAttribute(gemm_kernel<NT, POW2, DEEP>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES) != cudaSuccess) {
+        cudaGetLastError();
+        return -1;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(1, (unsigned)split, 1);
+    cfg.blockDim = dim3(kGemmThreads, 1, 1);
+    cfg.dynamicSmemBytes = C::SMEM_BYTES;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 1;
+    attr[0].val.clusterDim.y = (unsigned)split;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, gemm_kernel<NT, POW2, DEEP>, &cfg) != cudaSuccess) {
+        cudaGetLastError();
+        return -1;
+    }
+    return n;
+}
+
+int max_resident_clusters(int NT, int split, bool deep) {
+    static int cache[64][5][9][2];          // [device][tile width][cluster size][deep]: 0 = not asked yet
+    static std::mutex lock;
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64 || split < 2 || split > 8) {
+        cudaGetLastError();
+        return -1;
+    }
+    const int w = NT == 16 ? 0 : NT == 32 ? 1 : NT == 64 ? 2 : NT == 128 ? 3 : 4;
+    std::lock_guard<std::mutex> g(lock);
+    int& c = cache[dev][w][split][deep ? 1 : 0];
+    if (c == 0) {
+        int n;
+        switch (NT) {
+            case 16: n = deep ? resident_clusters_of<16, true, true>(split) : resident_clusters_of<16, true, false>(split); break;
+            case 32: n = resident_clusters_of<32, true, true>(split); break;
+            case 64: n = deep ? resident_clusters_of<64, false, true>(split) : resident_clusters_of<64, false, false>(split); break;
+            case 128: n = deep ? resident_clusters_of<128, false, true>(split) : resident_clusters_of<128, false, false>(split); break;
+            default: n = resident_clusters_of<256, false, true>(split); break;
+        }
+        c = n > 0 ? n : -1;
+    }
+    return c;
 }
 
 // Tuning overrides (read once): BGEMM_FORCE_NT = 16|32|64|128|256 forces the tile width, BGEMM_FORCE_DEEP = 0|1 the

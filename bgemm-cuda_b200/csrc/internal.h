@@ -60,6 +60,7 @@ void apply_test_hooks(GemmParams& p);   // copies the process-wide test settings
 
 int sm_count();                   // SMs of the current device (cached)
 int gemm_tile_n(long long N);
+int max_resident_clusters(int NT, int split, bool deep);   // clusters of `split` CTAs of gemm_kernel the device holds at once; -1: unknown
 int launch_gemm(cudaStream_t stream, GemmParams p, const int8_t* acts, long long act_ld, long long batch);
 
 // Persistent variant (gemm_persist.cu); `tensor_map` points to the CUtensorMap of the activations.
