@@ -622,13 +622,16 @@ int launch_gemm(cudaStream_t stream, GemmParams p, const int8_t* acts, long long
 
     // A pool of narrow problems (one tile across N, many more tiles than SMs, no K partitioning): one persistent CTA
     // per SM walks over the tiles and overlaps every tile's epilogue with the next tile's mainloop (measured 2.46 vs
-    // 2.27 POP/s on 95 x [4096 x 4096 x 128]). With several tiles across N the tile-per-CTA kernel, two CTAs per
-    // SM, measured 3-4 % faster (co-resident CTAs share activation tiles in L2), so it keeps those. It also keeps the
-    // launches whose tiles are all resident at once at two CTAs per SM: there the persistent kernel runs two tiles in
-    // a row on some SMs and one on the others (28672 x 8192, 224 tiles: N = 128 33.0 against 34.2 us, N = 64 26.1
-    // against 29.0).
+    // 2.27 POP/s on 95 x [4096 x 4096 x 128]). The tile-per-CTA kernel keeps the launches whose tiles are all resident
+    // at once at two CTAs per SM: there the persistent kernel runs two tiles in a row on some SMs and one on the others
+    // (28672 x 8192, 224 tiles: N = 128 33.0 against 34.2 us, N = 64 26.1 against 29.0).
+    // With several tiles across N the persistent kernel is ahead at 12-16 K blocks per tile (16384 x 4096 x 512: 34.1
+    // against 36.9 us; 16 x [4096 x 4096 x 256]: 57 against 64), level or slightly behind at 32 (28672 x 8192 x 256: 58.7
+    // against 57.0) and behind with short K (8192 x 2048 x 1024: 27.8 against 25.0).
     const long long total_tiles = (long long)p.ntiles * p.mtiles * batch;
-    const int persist = forced_persist() >= 0 ? forced_persist() : (p.ntiles == 1 && total_tiles > 2LL * sm_count() ? 1 : 0);
+    const bool many_tiles = total_tiles > 2LL * sm_count();
+    const int persist = forced_persist() >= 0 ? forced_persist()
+                                              : (many_tiles && (p.ntiles == 1 || (p.kblocks >= 12 && p.kblocks < 32)) ? 1 : 0);
     if (persist && p.split_k == 1 && persistent_supported(NT) && total_tiles > sm_count() && p.kblocks >= persist_min_kblocks() &&
         persistent_kblocks_ok(NT, p.kblocks))
         return launch_gemm_persistent(stream, &tmap, p, NT, total_tiles, sm_count());

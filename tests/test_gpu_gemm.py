@@ -305,6 +305,23 @@ def test_pools_on_the_persistent_kernel(B, M, K, N, batch, layout):
     assert B.lib.bgemm_device_status(1) == 0
 
 
+@pytest.mark.parametrize("M,K,N,batch", [(12800, 3072, 300, 1), (1024, 3328, 256, 20)])
+def test_persistent_kernel_with_several_tiles_across_n(B, M, K, N, batch):
+    """More than two tiles per SM, 12 or more K blocks per tile, two or three tiles across N (the last one ragged)."""
+    g = O._gen(M + K + N + batch)
+    shape_w, shape_x = ((batch, M, K), (batch, N, K)) if batch > 1 else ((M, K), (N, K))
+    w = O.rand_pm1(shape_w, g)
+    x = O.rand_ternary(shape_x, g)
+    acc = O.ref_acc(w, x, O.OP_BWTA)
+    plane, _, _ = B.pack_weights(w.cuda(), B.WBIT_OF_OP[O.OP_BWTA])
+    acts, colsum = B.prepare_acts(x.cuda(), B.ACT_MODE_OF_OP[O.OP_BWTA])
+    for layout in (0, 1):
+        want = acc if layout == 0 else acc.transpose(-1, -2)
+        got = B.gemm(plane, M, K, acts, colsum, O.OP_BWTA, O.OUT_I32, layout, None, 1).cpu()
+        assert torch.equal(got, want), (layout, int((got != want).sum()))
+    assert B.lib.bgemm_device_status(1) == 0
+
+
 def test_persistent_kernel_under_graph_replay(B):
     """The persistent kernel's barrier rings across many tiles, replayed back to back from a CUDA graph."""
     M, K, N, batch = 1024, 2304, 128, 60
