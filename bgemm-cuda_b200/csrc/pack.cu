@@ -86,13 +86,29 @@ __device__ __forceinline__ void load_block(RawBlock<T>& raw, const T* __restrict
 #pragma unroll
     for (int j = 0; j < 8; j++) {
         const long long k = k0 + 32 * j;
-        if (sizeof(T) == 2 && live && vec_ok && k + 8 <= K) {
-            *reinterpret_cast<uint4*>(raw.v[j]) = __ldcs(reinterpret_cast<const uint4*>(rp + k));
+        if (live && vec_ok && k + 8 <= K) {         // one piece = 8 elements: 8, 16 or 32 bytes
+            if (sizeof(T) == 1) {
+                *reinterpret_cast<uint2*>(raw.v[j]) = __ldcs(reinterpret_cast<const uint2*>(rp + k));
+            } else if (sizeof(T) == 2) {
+                *reinterpret_cast<uint4*>(raw.v[j]) = __ldcs(reinterpret_cast<const uint4*>(rp + k));
+            } else {
+                reinterpret_cast<uint4*>(raw.v[j])[0] = __ldcs(reinterpret_cast<const uint4*>(rp + k));
+                reinterpret_cast<uint4*>(raw.v[j])[1] = __ldcs(reinterpret_cast<const uint4*>(rp + k) + 1);
+            }
         } else {
 #pragma unroll
             for (int e = 0; e < 8; e++) raw.v[j][e] = (live && k + e < K) ? rp[k + e] : T();
         }
     }
+}
+
+// The weight-slot bits of four int8 elements held in one word, at bit 0 of their bytes (no -0 among integers: "negative
+// and non-zero" is "negative").
+__device__ __forceinline__ uint32_t weight_bits_i8x4(uint32_t x, int mode) {
+    const uint32_t neg = (x >> 7) & 0x01010101u;
+    if (mode == BGEMM_WBIT_NEGATIVE) return neg;
+    if (mode == BGEMM_WBIT_NONNEGATIVE) return neg ^ 0x01010101u;
+    return mode == BGEMM_WBIT_NONZERO ? (__vcmpne4(x, 0u) & 0x01010101u) : neg;
 }
 
 template <typename T>
@@ -101,7 +117,8 @@ __device__ __forceinline__ void bits_of_block(const RawBlock<T>& raw, long long 
     w0 = 0;
     w1 = 0;
     if (!live) return;
-    if (sizeof(T) == 2 && vec_ok && k0 + 32 * 7 + 8 <= K) {         // all eight pieces complete
+    const bool whole = vec_ok && k0 + 32 * 7 + 8 <= K;               // all eight pieces complete
+    if (sizeof(T) == 2 && whole) {
         if (mode == BGEMM_WBIT_NEGATIVE || mode == BGEMM_WBIT_NONNEGATIVE) {
 #pragma unroll
             for (int j = 0; j < 8; j++) {
@@ -130,6 +147,19 @@ __device__ __forceinline__ void bits_of_block(const RawBlock<T>& raw, long long 
 #pragma unroll
                 for (int e = 0; e < 8; e++) mag += Elem<T>::mag(raw.v[j][e]);
         }
+    } else if (sizeof(T) == 1 && whole) {
+        uint32_t abs_sum = 0;
+#pragma unroll
+        for (int j = 0; j < 8; j++) {
+            const uint2 q = *reinterpret_cast<const uint2*>(raw.v[j]);
+            w0 |= weight_bits_i8x4(q.x, mode) << j;
+            w1 |= weight_bits_i8x4(q.y, mode) << j;
+            if (want_mag) {     // |v| <= 128 per byte, summed as integers: exact, like the element-wise fp32 sum below
+                abs_sum = __dp4a(__vabsdiffs4(q.x, 0u), 0x01010101u, abs_sum);
+                abs_sum = __dp4a(__vabsdiffs4(q.y, 0u), 0x01010101u, abs_sum);
+            }
+        }
+        mag += (float)abs_sum;
     } else {
 #pragma unroll
         for (int j = 0; j < 8; j++) {
@@ -165,12 +195,12 @@ __global__ void __launch_bounds__(256) pack_weights_kernel(const T* __restrict__
     src += batch * src_batch_stride;
     plane += batch * plane_batch_bytes;
     const T* rp = src + row * ld;
-    const bool vec_ok = (sizeof(T) == 2) && ((reinterpret_cast<uintptr_t>(rp) & 15) == 0);
+    const bool vec_ok = (reinterpret_cast<uintptr_t>(rp) & (sizeof(T) == 1 ? 7 : 15)) == 0;     // a piece is loaded as one or two vectors
     const bool want_mag = alpha != nullptr;
     uint8_t* dst = plane + (row / 128) * kblocks * 4096 + (cp >> 1) * 2048 + (int)(row % 128) * 16 + (cp & 1) * 8;
     int pop = 0;
     float mag = 0.f;
-    constexpr int U = sizeof(T) == 2 ? 2 : 1;       // K blocks in flight per warp (16 loads of 16 bytes per lane)
+    constexpr int U = sizeof(T) <= 2 ? 2 : 1;       // K blocks in flight per warp (16 loads of 8 or 16 bytes per lane; fp32: 16 of 16)
     for (long long kb0 = kpart; kb0 < kblocks; kb0 += (long long)ksplit * U) {
         RawBlock<T> raw[U];
 #pragma unroll

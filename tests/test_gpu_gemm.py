@@ -81,6 +81,25 @@ def test_pack_weights_dtypes_and_host_twin(B, dtype):
     assert np.array_equal(host_plane, ref_plane) and np.array_equal(host_pop, ref_pop)
 
 
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16, torch.float32, torch.int8])
+@pytest.mark.parametrize("mode", [0, 1, 2, 3])
+@pytest.mark.parametrize("M,K,offset", [(130, 520, 0), (70, 515, 0), (300, 1024, 0), (200, 768, 1)])
+def test_pack_weights_every_mode_dtype_and_alignment(B, dtype, mode, M, K, offset):
+    """Vector and element-wise paths of the packing kernel (whole and ragged K blocks, rows that start off a 16-byte
+    boundary) for every source type and weight-bit mode, with row sums and scales."""
+    g = O._gen(M + K + mode)
+    base = torch.randint(-3, 4, (M, K + 8), generator=g)
+    wide = base.to(dtype).cuda()
+    w = wide[:, offset:offset + K]                       # a view: row pitch K + 8, rows misaligned when offset is odd
+    plane, rowpop, alpha = B.pack_weights(w, mode, want_rowpop=True, want_alpha=True)
+    ref = base[:, offset:offset + K].float() - 0.0      # zero -> +0 -> sign bit clear, like int8 0
+    ref_plane, ref_pop = O.np_pack_weights(ref, mode)
+    assert np.array_equal(plane.cpu().numpy(), ref_plane)
+    assert np.array_equal(rowpop.cpu().numpy(), ref_pop)
+    want_alpha = ref.abs().mean(dim=1).numpy()
+    assert np.all(np.abs(alpha.cpu().float().numpy() - want_alpha) <= 1e-3 * want_alpha + 1e-7)
+
+
 @pytest.mark.parametrize("mode", [0, 1, 2])
 @pytest.mark.parametrize("N,K", [(1, 256), (5, 300), (64, 4096), (33, 1000)])
 def test_prepare_acts(B, mode, N, K):
