@@ -187,8 +187,8 @@ size_t bgemm_gemm_workspace_bytes(int64_t M, int64_t N, int64_t K, int split_k, 
  *   BGEMM_FLAG_STATIC_WEIGHTS     the promise of bgemm_gemm_static_weights (next entry point).
  *   BGEMM_FLAG_BALANCE_WORKSPACE  `workspace` is a BALANCE workspace: bgemm_gemm_balance_workspace_bytes() bytes, 256-byte
  *       aligned, zeroed once after allocation and never written by anybody but this library (its first 64 KiB are flags
- *       that every launch leaves at zero). With it the kernel for wide activation matrices (N >= 256) splits its work
- *       into exactly equal parts per SM pair -- tiles that straddle a boundary are accumulated in two or more places and
+ *       that every launch leaves at zero). With it the kernel for wide activation matrices (N > 512 and K >= 2560; the
+ *       size query below says for which calls) splits its work into exactly equal parts per SM pair -- tiles that straddle a boundary are accumulated in two or more places and
  *       summed through the workspace -- instead of whole tiles, which matters whenever the number of 256 x 256 tiles is
  *       not a multiple of the SM pairs (28672 x 8192 x 1024: 171 -> 158 us). Results are the same bits (integer sums).
  *       One balance workspace must not serve two calls that overlap on the GPU; calls on one stream may share it.
