@@ -53,6 +53,8 @@ FLAG_STATIC_WEIGHTS, FLAG_BALANCE_WORKSPACE = 1, 2
 lib.bgemm_gemm_multi_out.argtypes = [_vp, _vp, _i64, _i64, _vp, _vp, _i64, _int, _vp, _int, _i64, _int, _int, _vp, _int, _vp, _sz, _int]
 lib.bgemm_w1a16_gemm.argtypes = [_vp, _vp, _i64, _i64, _vp, _i64, _i64, _vp, _int, _int, _vp, _int]
 lib.bgemm_gemm_to_acts.argtypes = [_vp, _vp, _i64, _i64, _vp, _vp, _i64, _int, _vp, _int, _vp, _vp, _int, _vp, _sz, _i64]
+lib.bgemm_gemm_to_acts_ex.argtypes = [_vp, _vp, _i64, _i64, _vp, _vp, _i64, _int, _vp, _int, _vp, _vp, _int, _vp, _sz, _i64, _int]
+FLAG_SUMS_ZEROED = 4
 lib.bgemm_gemm_workspace_bytes.restype = _sz
 lib.bgemm_gemm_workspace_bytes.argtypes = [_i64, _i64, _i64, _int, _i64]
 lib.bgemm_debug_set_pair_kernel.restype = None
@@ -269,8 +271,9 @@ def w1a16_gemm(plane: torch.Tensor, M: int, K: int, x: torch.Tensor, out_kind: i
 
 
 def gemm_to_acts(plane: torch.Tensor, M: int, K: int, acts: torch.Tensor, colsum: torch.Tensor, op: int, next_act_mode: int,
-                 alpha: torch.Tensor | None = None, split_k: int = 0, ws: torch.Tensor | None = None):
-    """GEMM whose result becomes the next layer's prepared activations: (int8 [.., N, act_ld(M)], colsum int32 [.., N])."""
+                 alpha: torch.Tensor | None = None, split_k: int = 0, ws: torch.Tensor | None = None, sums: torch.Tensor | None = None):
+    """GEMM whose result becomes the next layer's prepared activations: (int8 [.., N, act_ld(M)], colsum int32 [.., N]).
+    `sums`: an int32 tensor the caller has zeroed on the current stream; it receives the row sums (BGEMM_FLAG_SUMS_ZEROED)."""
     _require_cuda(plane, acts, colsum, alpha)
     batched = acts.dim() == 3
     B = acts.shape[0] if batched else 1
@@ -278,13 +281,18 @@ def gemm_to_acts(plane: torch.Tensor, M: int, K: int, acts: torch.Tensor, colsum
     assert acts.shape[-1] == act_ld(K) and acts.is_contiguous() and colsum.is_contiguous()
     lead = (B,) if batched else ()
     nxt = torch.empty(lead + (N, act_ld(M)), dtype=torch.int8, device=acts.device)
-    ncs = torch.empty(lead + (N,), dtype=torch.int32, device=acts.device)
+    if sums is not None:        # zeroed by the caller on the current stream: the call enqueues nothing but its kernel
+        assert sums.dtype == torch.int32 and sums.is_contiguous() and sums.numel() == B * N and sums.device == acts.device
+        ncs = sums.view(lead + (N,))
+    else:
+        ncs = torch.empty(lead + (N,), dtype=torch.int32, device=acts.device)
     need = lib.bgemm_gemm_workspace_bytes(M, N, K, split_k, B)
     if need and ws is None:
         ws = workspace(acts.device, need)
     with torch.cuda.device(acts.device):
-        check(lib.bgemm_gemm_to_acts(_stream(), plane.data_ptr(), M, K, acts.data_ptr(), colsum.data_ptr(), N, op, _ptr(alpha), next_act_mode,
-                                     nxt.data_ptr(), ncs.data_ptr(), split_k, _ptr(ws) if need else None, ws.numel() if need else 0, B),
+        check(lib.bgemm_gemm_to_acts_ex(_stream(), plane.data_ptr(), M, K, acts.data_ptr(), colsum.data_ptr(), N, op, _ptr(alpha), next_act_mode,
+                                        nxt.data_ptr(), ncs.data_ptr(), split_k, _ptr(ws) if need else None, ws.numel() if need else 0, B,
+                                        FLAG_SUMS_ZEROED if sums is not None else 0),
               "bgemm_gemm_to_acts")
     return nxt, ncs
 

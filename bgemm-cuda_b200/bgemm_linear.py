@@ -434,15 +434,17 @@ class BinaryLinear(nn.Module):
         """fp16 [N, in_features] -> this layer's prepared activations (int8 rows, row sums)."""
         return lowbit_kernel.prepare_acts(x.reshape(-1, self.in_features), self.act_mode, False)
 
-    def forward_prepared(self, acts: torch.Tensor, colsum: torch.Tensor, next_layer: "BinaryLinear | None" = None):
+    def forward_prepared(self, acts: torch.Tensor, colsum: torch.Tensor, next_layer: "BinaryLinear | None" = None, sums: "torch.Tensor | None" = None):
         """GEMM on prepared activations. With next_layer the scaled result is turned into that layer's prepared
-        activations inside the GEMM epilogue (no fp16 round trip) and (acts, colsum) is returned; else fp16 [N, out]."""
+        activations inside the GEMM epilogue (no fp16 round trip) and (acts, colsum) is returned; else fp16 [N, out].
+        `sums`: an int32 tensor, zeroed by the caller on the current stream, that receives the new row sums (the call
+        then enqueues nothing but its kernel)."""
         if next_layer is None:
             return lowbit_kernel.gemm_prepared(self.plane, self.out_features, self.in_features, acts, colsum, self.op, _OUT_F16_SCALED, 0,
                                                self.alpha, 0, True)
         assert next_layer.in_features == self.out_features
         return lowbit_kernel.gemm_prepared_to_acts(self.plane, self.out_features, self.in_features, acts, colsum, self.op,
-                                                   next_layer.act_mode, self.alpha, 0)
+                                                   next_layer.act_mode, self.alpha, 0, sums)
 
 
 class BinaryMLP(nn.Module):
@@ -469,9 +471,12 @@ class BinaryMLP(nn.Module):
             return x
         # one activation pass for the input, then every hidden layer hands int8 activations to the next one
         lead = x.shape[:-1]
+        # the row sums of all hidden layers' activations live in one array, zeroed by one fill ahead of the chain: nothing
+        # but kernels stands between the GEMMs
+        sums = torch.zeros((len(self.layers) - 1, x.numel() // x.shape[-1]), dtype=torch.int32, device=x.device) if len(self.layers) > 1 else None
         acts, colsum = self.layers[0].prepare(x)
         for i, layer in enumerate(self.layers[:-1]):
-            acts, colsum = layer.forward_prepared(acts, colsum, self.layers[i + 1])
+            acts, colsum = layer.forward_prepared(acts, colsum, self.layers[i + 1], sums[i])
         y = self.layers[-1].forward_prepared(acts, colsum)
         return y.reshape(*lead, self.layers[-1].out_features)
 

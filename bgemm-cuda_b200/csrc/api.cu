@@ -396,6 +396,14 @@ int bgemm_w1a16_gemm(void* stream, const void* plane, int64_t M, int64_t K, cons
 int bgemm_gemm_to_acts(void* stream, const void* plane, int64_t M, int64_t K, const int8_t* acts, const int32_t* colsum, int64_t N, int op,
                        const void* alpha, int next_act_mode, int8_t* next_acts, int32_t* next_colsum, int split_k, void* workspace,
                        size_t workspace_bytes, int64_t batch) {
+    return bgemm_gemm_to_acts_ex(stream, plane, M, K, acts, colsum, N, op, alpha, next_act_mode, next_acts, next_colsum, split_k, workspace,
+                                 workspace_bytes, batch, 0);
+}
+
+int bgemm_gemm_to_acts_ex(void* stream, const void* plane, int64_t M, int64_t K, const int8_t* acts, const int32_t* colsum, int64_t N, int op,
+                          const void* alpha, int next_act_mode, int8_t* next_acts, int32_t* next_colsum, int split_k, void* workspace,
+                          size_t workspace_bytes, int64_t batch, int flags) {
+    if (flags & ~(BGEMM_FLAG_STATIC_WEIGHTS | BGEMM_FLAG_SUMS_ZEROED)) return BGEMM_ERR_ENUM;
     if (!plane || !acts || !colsum || !next_acts || !next_colsum) return BGEMM_ERR_NULL;
     if (op < BGEMM_OP_AND || op > BGEMM_OP_BWTA || next_act_mode < BGEMM_ACT_SIGN || next_act_mode > BGEMM_ACT_NEG01) return BGEMM_ERR_ENUM;
     if (M < 1 || N < 1 || K < 1 || batch < 1 || batch > 65535 || M > kMaxDim || N > kMaxDim || K > kMaxDim || split_k < 0 ||
@@ -415,7 +423,8 @@ int bgemm_gemm_to_acts(void* stream, const void* plane, int64_t M, int64_t K, co
         if (!aligned(workspace, 256)) return BGEMM_ERR_ALIGN;
     }
     // the kernel adds row sums with atomics and writes whole 8-column chunks: sums and the padding beyond them start at zero
-    cudaError_t e = cudaMemsetAsync(next_colsum, 0, (size_t)N * (size_t)batch * sizeof(int32_t), st);
+    cudaError_t e = cudaSuccess;
+    if (!(flags & BGEMM_FLAG_SUMS_ZEROED)) e = cudaMemsetAsync(next_colsum, 0, (size_t)N * (size_t)batch * sizeof(int32_t), st);
     const long long written = (M + 7) / 8 * 8;
     if (e == cudaSuccess && written < ld)
         e = cudaMemset2DAsync(next_acts + written, (size_t)ld, 0, (size_t)(ld - written), (size_t)N * (size_t)batch, st);
@@ -444,6 +453,7 @@ int bgemm_gemm_to_acts(void* stream, const void* plane, int64_t M, int64_t K, co
     p.colsum_next = next_colsum;
     p.out_ld = ld;
     p.act_mode = next_act_mode;
+    p.weights_static = (flags & BGEMM_FLAG_STATIC_WEIGHTS) ? 1 : 0;
     if (s > kMaxClusterSplit) {
         const int NT = gemm_tile_n(N);
         const long long tiles = mtiles * ((N + NT - 1) / NT) * batch;

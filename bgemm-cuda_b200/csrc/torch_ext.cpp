@@ -234,8 +234,11 @@ torch::Tensor gemm_prepared(torch::Tensor plane, int64_t M, int64_t K, torch::Te
 
 // GEMM on prepared operands whose result becomes the next layer's prepared activations (see bgemm_gemm_to_acts):
 // returns (int8 [N, act_ld(M)], colsum int32 [N]) = prepare_acts(fp16 result, next_act_mode) without the round trip.
+// `sums` (optional): an int32 tensor of the row sums' shape that the caller has ZEROED on the current stream; it receives the
+// row sums and is returned as the second result, and the library skips its own memset (see BGEMM_FLAG_SUMS_ZEROED).
 std::vector<torch::Tensor> gemm_prepared_to_acts(torch::Tensor plane, int64_t M, int64_t K, torch::Tensor acts, torch::Tensor colsum,
-                                                 int64_t op, int64_t next_act_mode, c10::optional<torch::Tensor> alpha, int64_t splitK) {
+                                                 int64_t op, int64_t next_act_mode, c10::optional<torch::Tensor> alpha, int64_t splitK,
+                                                 c10::optional<torch::Tensor> sums) {
     TORCH_CHECK(plane.is_cuda() && acts.is_cuda() && colsum.is_cuda(), "gemm_prepared_to_acts: CUDA tensors required");
     TORCH_CHECK(acts.is_contiguous() && colsum.is_contiguous() && plane.is_contiguous(), "gemm_prepared_to_acts: contiguous tensors required");
     TORCH_CHECK(acts.scalar_type() == at::kChar && colsum.scalar_type() == at::kInt, "gemm_prepared_to_acts: acts int8 / colsum int32 required");
@@ -247,7 +250,15 @@ std::vector<torch::Tensor> gemm_prepared_to_acts(torch::Tensor plane, int64_t M,
     std::vector<int64_t> ashape = batched ? std::vector<int64_t>{B, N, bgemm_act_ld(M)} : std::vector<int64_t>{N, bgemm_act_ld(M)};
     std::vector<int64_t> cshape = batched ? std::vector<int64_t>{B, N} : std::vector<int64_t>{N};
     auto next_acts = torch::empty(ashape, torch::TensorOptions().dtype(at::kChar).device(acts.device()));
-    auto next_colsum = torch::empty(cshape, torch::TensorOptions().dtype(at::kInt).device(acts.device()));
+    torch::Tensor next_colsum;
+    if (sums.has_value()) {
+        next_colsum = *sums;
+        TORCH_CHECK(next_colsum.is_cuda() && next_colsum.device() == acts.device() && next_colsum.scalar_type() == at::kInt &&
+                        next_colsum.is_contiguous() && next_colsum.numel() == B * N,
+                    "gemm_prepared_to_acts: sums must be a contiguous int32 CUDA tensor with one value per activation row");
+    } else {
+        next_colsum = torch::empty(cshape, torch::TensorOptions().dtype(at::kInt).device(acts.device()));
+    }
     const void* alpha_ptr = nullptr;
     torch::Tensor a;
     if (alpha.has_value()) {
@@ -258,11 +269,11 @@ std::vector<torch::Tensor> gemm_prepared_to_acts(torch::Tensor plane, int64_t M,
     const size_t need = bgemm_gemm_workspace_bytes(M, N, K, (int)splitK, B);
     torch::Tensor ws;
     if (need) ws = workspace(acts.device(), need, true);
-    check(bgemm_gemm_to_acts(stream_of(acts), plane.data_ptr(), M, K, acts.data_ptr<int8_t>(), colsum.data_ptr<int>(), N, (int)op, alpha_ptr,
-                             (int)next_act_mode, next_acts.data_ptr<int8_t>(), next_colsum.data_ptr<int>(), (int)splitK,
-                             need ? ws.data_ptr() : nullptr, need ? (size_t)ws.numel() : 0, B),
+    check(bgemm_gemm_to_acts_ex(stream_of(acts), plane.data_ptr(), M, K, acts.data_ptr<int8_t>(), colsum.data_ptr<int>(), N, (int)op, alpha_ptr,
+                                (int)next_act_mode, next_acts.data_ptr<int8_t>(), next_colsum.data_ptr<int>(), (int)splitK,
+                                need ? ws.data_ptr() : nullptr, need ? (size_t)ws.numel() : 0, B, sums.has_value() ? BGEMM_FLAG_SUMS_ZEROED : 0),
           "bgemm_gemm_to_acts");
-    return {next_acts, next_colsum};
+    return {next_acts, sums.has_value() ? next_colsum.view(cshape) : next_colsum};
 }
 
 // x [N, K] unpacked x prepacked weights -> [N, M]. INSTR as in the reference; out_kind 1 = fp16, 0 = int32,
@@ -339,7 +350,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
           py::arg("splitK") = 0, py::arg("static_weights") = false);
     m.def("gemm_prepared_to_acts", &gemm_prepared_to_acts, "GEMM whose result becomes the next layer's prepared activations.", py::arg("plane"),
           py::arg("M"), py::arg("K"), py::arg("acts"), py::arg("colsum"), py::arg("op"), py::arg("next_act_mode"), py::arg("alpha") = py::none(),
-          py::arg("splitK") = 0);
+          py::arg("splitK") = 0, py::arg("sums") = py::none());
     m.def("bgemm_linear_forward_packed", &bgemm_linear_forward_packed, "x x prepacked weights.", py::arg("x"), py::arg("plane"), py::arg("M"),
           py::arg("K"), py::arg("alpha") = py::none(), py::arg("splitK") = 0, py::arg("INSTR") = 1, py::arg("out_kind") = 1,
           py::arg("static_weights") = false);

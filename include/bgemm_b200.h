@@ -258,6 +258,18 @@ int bgemm_gemm_to_acts(void* stream, const void* plane, int64_t M, int64_t K,
                        const int8_t* acts, const int32_t* colsum, int64_t N, int op, const void* alpha,
                        int next_act_mode, int8_t* next_acts, int32_t* next_colsum,
                        int split_k, void* workspace, size_t workspace_bytes, int64_t batch);
+
+/* bgemm_gemm_to_acts with flags: BGEMM_FLAG_STATIC_WEIGHTS as in bgemm_gemm_ex, and
+ *   BGEMM_FLAG_SUMS_ZEROED   the caller has set next_colsum to zero on `stream` before this call (for instance one
+ *       memset over the row-sum buffers of all layers of a chain at the start of a forward pass): the library adds
+ *       the row sums to it without its own memset, so that nothing but kernels stands between the GEMMs of the chain
+ *       (in a CUDA graph a memset node costs about as much as a small kernel and ends the overlap of consecutive
+ *       launches). Sums that do not start at zero give wrong row sums, nothing worse.                              */
+#define BGEMM_FLAG_SUMS_ZEROED 4
+int bgemm_gemm_to_acts_ex(void* stream, const void* plane, int64_t M, int64_t K,
+                          const int8_t* acts, const int32_t* colsum, int64_t N, int op,
+                          const void* alpha, int next_act_mode, int8_t* next_acts, int32_t* next_colsum,
+                          int split_k, void* workspace, size_t workspace_bytes, int64_t batch, int flags);
 /* The split_k the library would pick for split_k = 0.                                                 */
 int bgemm_gemm_auto_split_k(int64_t M, int64_t N, int64_t K, int64_t batch);
 

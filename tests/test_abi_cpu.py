@@ -86,6 +86,9 @@ def test_a_refused_call_enqueues_nothing(lib):
     assert lib.bgemm_linear_forward(None, fake, fake, fake + 2, 64, 8, 256, 1, 0, 0, None, 1, fake, big) == -3  # int32 out misaligned
     assert lib.bgemm_linear_forward(None, fake, fake, fake, 64, 8, 256, 1, 1, 0, None, 1, fake + 8, big) == -3  # workspace misaligned
     assert lib.bgemm_gemm_to_acts(None, fake, 64, 8192, fake, fake, 8, 1, None, 0, fake, fake, 16, None, 0, 1) == -5   # needs a workspace
+    lib.bgemm_gemm_to_acts_ex.argtypes = [vp, vp, i64, i64, vp, vp, i64, ci, vp, ci, vp, vp, ci, vp, sz, i64, ci]
+    assert lib.bgemm_gemm_to_acts_ex(None, fake, 64, 8192, fake, fake, 8, 1, None, 0, fake, fake, 1, None, 0, 1, 8) == -4     # unknown flag
+    assert lib.bgemm_gemm_to_acts_ex(None, fake, 64, 8192, fake, fake, 8, 1, None, 0, fake, fake, 16, None, 0, 1, 4) == -5    # needs a workspace
     assert lib.bgemm_gemm_to_acts(None, fake, 64, 8192, fake, fake, 8, 1, None, 0, fake, fake, 16, fake + 16, big, 1) == -3
     # general int8 activations on narrow tiles beyond the exact range
     assert lib.bgemm_gemm(None, fake, 128, 70000, fake, fake, 16, 4, fake, 0, 0, None, 1, None, 0, 1) == -6

@@ -388,6 +388,10 @@ def test_gemm_to_acts_equals_gemm_then_prepare(B, M, K, N, batch, split_k, next_
         assert got_acts.shape == want_acts.shape
         assert torch.equal(got_acts, want_acts)
         assert torch.equal(got_cs, want_cs)
+        # row sums added to an array the caller has zeroed (no memset by the library)
+        sums = torch.zeros(want_cs.numel(), dtype=torch.int32, device="cuda")
+        got_acts, got_cs = B.gemm_to_acts(plane, M, K, acts, colsum, O.OP_BWTA, next_mode, a, split_k, sums=sums)
+        assert torch.equal(got_acts, want_acts) and torch.equal(got_cs, want_cs) and got_cs.data_ptr() == sums.data_ptr()
     # and against the oracle's definition of the activation mapping
     acc = O.ref_acc(w, x, O.OP_BWTA)
     yref = O.ref_out(acc, O.OUT_F16_SCALED, alpha.unsqueeze(-2) if batch > 1 else alpha)
