@@ -541,10 +541,11 @@ int launch_prepare_acts(cudaStream_t stream, const void* src, int dtype, long lo
                         int transpose, int8_t* dst, int32_t* colsum, long long batch, long long src_batch_stride) {
     cudaError_t e = cudaSuccess;
     if (transpose) {
-        // One CTA per 64 output rows and problem; with fewer CTAs than SMs the K tiles are divided over gridDim.z as well.
+        // One CTA per 64 output rows and problem; with fewer CTAs than SMs the K tiles of a source of some size (2^20
+        // elements or more: the memset of the sums costs about as much as a small kernel) are divided over gridDim.z as well.
         const long long ctas = (N + 63) / 64 * batch, ktiles = (K + 255) / 256 * 2;
         int kparts = 1;
-        while (kparts < 32 && ctas * kparts < sm_count() && 2 * kparts <= ktiles) kparts *= 2;
+        while (N * K * batch >= (1LL << 20) && kparts < 32 && ctas * kparts < sm_count() && 2 * kparts <= ktiles) kparts *= 2;
         if (kparts > 1) {
             e = cudaMemsetAsync(colsum, 0, sizeof(int32_t) * (size_t)(N * batch), stream);
             if (e != cudaSuccess) return (int)e;
