@@ -101,7 +101,7 @@ def test_pack_weights_every_mode_dtype_and_alignment(B, dtype, mode, M, K, offse
 
 
 @pytest.mark.parametrize("mode", [0, 1, 2])
-@pytest.mark.parametrize("N,K", [(1, 256), (5, 300), (64, 4096), (33, 1000)])
+@pytest.mark.parametrize("N,K", [(1, 256), (5, 300), (64, 4096), (33, 1000), (300, 4096)])
 def test_prepare_acts(B, mode, N, K):
     g = O._gen(N + K + mode)
     x = O.rand_ternary((N, K), g) if mode == 1 else torch.randn(N, K, generator=g).to(torch.float16)
