@@ -471,12 +471,15 @@ class BinaryMLP(nn.Module):
             return x
         # one activation pass for the input, then every hidden layer hands int8 activations to the next one
         lead = x.shape[:-1]
-        # the row sums of all hidden layers' activations live in one array, zeroed by one fill ahead of the chain: nothing
-        # but kernels stands between the GEMMs
-        sums = torch.zeros((len(self.layers) - 1, x.numel() // x.shape[-1]), dtype=torch.int32, device=x.device) if len(self.layers) > 1 else None
+        # Under stream capture the row sums of all hidden layers' activations live in one array, zeroed by one fill ahead of
+        # the chain: nothing but kernels stands between the GEMMs of the graph (a memset node there costs ~4 us per layer).
+        # Eager calls are bound by host time, and the library's own memset per layer is the cheaper call there.
+        sums = None
+        if len(self.layers) > 1 and torch.cuda.is_current_stream_capturing():
+            sums = torch.zeros((len(self.layers) - 1, x.numel() // x.shape[-1]), dtype=torch.int32, device=x.device)
         acts, colsum = self.layers[0].prepare(x)
         for i, layer in enumerate(self.layers[:-1]):
-            acts, colsum = layer.forward_prepared(acts, colsum, self.layers[i + 1], sums[i])
+            acts, colsum = layer.forward_prepared(acts, colsum, self.layers[i + 1], None if sums is None else sums[i])
         y = self.layers[-1].forward_prepared(acts, colsum)
         return y.reshape(*lead, self.layers[-1].out_features)
 
