@@ -68,7 +68,7 @@ static size_t counter_bytes(long long) { return kCounterBytes; }
 
 static int resolve_split_k(long long M, long long N, long long K, long long batch, int split_k) {
     const long long kblocks = (K + 255) / 256;
-    const int NT = gemm_tile_n(N);
+    const int NT = gemm_tile_n(M, N, K, batch);
     const long long tiles = ((M + 127) / 128) * ((N + NT - 1) / NT) * batch;
     if (split_k >= 1) {
         if (split_k > kMaxClusterSplit && tiles > kMaxCounterTiles) split_k = kMaxClusterSplit;
@@ -245,7 +245,7 @@ size_t bgemm_gemm_workspace_bytes(int64_t M, int64_t N, int64_t K, int split_k, 
     if (M < 1 || N < 1 || K < 1 || batch < 1) return 0;
     const int s = resolve_split_k(M, N, K, batch, split_k);
     if (s <= kMaxClusterSplit) return 0;          // cluster / DSMEM reduction needs no global memory
-    const int NT = gemm_tile_n(N);
+    const int NT = gemm_tile_n(M, N, K, batch);
     const long long tiles = ((M + 127) / 128) * ((N + NT - 1) / NT) * batch;
     return counter_bytes(tiles) + (size_t)tiles * (size_t)s * (size_t)NT * 128 * 4;
 }
@@ -316,7 +316,7 @@ static int gemm_entry(void* stream, const void* plane, int64_t M, int64_t K, con
         const size_t need = bgemm_gemm_workspace_bytes(M, N, K, s, batch);
         if (!workspace || workspace_bytes < need) return BGEMM_ERR_WORKSPACE;
         if (!aligned(workspace, 256)) return BGEMM_ERR_ALIGN;
-        const int NT = gemm_tile_n(N);
+        const int NT = gemm_tile_n(M, N, K, batch);
         const long long tiles = mtiles * ((N + NT - 1) / NT) * batch;
         p.ws_counters = static_cast<unsigned int*>(workspace);
         p.ws_partial = reinterpret_cast<int32_t*>(static_cast<char*>(workspace) + counter_bytes(tiles));
@@ -455,7 +455,7 @@ int bgemm_gemm_to_acts_ex(void* stream, const void* plane, int64_t M, int64_t K,
     p.act_mode = next_act_mode;
     p.weights_static = (flags & BGEMM_FLAG_STATIC_WEIGHTS) ? 1 : 0;
     if (s > kMaxClusterSplit) {
-        const int NT = gemm_tile_n(N);
+        const int NT = gemm_tile_n(M, N, K, batch);
         const long long tiles = mtiles * ((N + NT - 1) / NT) * batch;
         p.ws_counters = static_cast<unsigned int*>(workspace);
         p.ws_partial = reinterpret_cast<int32_t*>(static_cast<char*>(workspace) + counter_bytes(tiles));

@@ -568,12 +568,17 @@ static int forced_persist() { static const int v = env_int("BGEMM_PERSIST"); ret
 // Fewest K blocks per tile for the persistent kernel (tuning override: BGEMM_PERSIST_MIN_KB).
 static int persist_min_kblocks() { static const int v = env_int("BGEMM_PERSIST_MIN_KB"); return v > 0 ? v : 2; }
 
-int gemm_tile_n(long long N) {
+int gemm_tile_n(long long M, long long N, long long K, long long batch) {
     const int f = forced_nt();
     if (f == 16 || f == 32 || f == 64 || f == 128 || f == 256) return f;
     if (N <= 16) return 16;
     if (N <= 32) return 32;
     if (N <= 64) return 64;
+    // 65-128 activation rows on few row tiles: two 64-column tiles with half as many K partitions each are faster than
+    // one 128-column tile (half the partial sums to exchange per CTA; 4096 x 4096 x 128: 9.35 against 9.87 us, 2048 x
+    // 4096 x 128: 7.9 against 9.2, 4096 x 1024 x 128: 6.9 against 8.3) as long as the K range per partition stays short
+    // (4096 x 8192 x 128: 12.5 against 11.7) and both fill the SMs once.
+    if (N <= 128 && batch == 1 && (M + 127) / 128 * 4 <= sm_count() && (K + 255) / 256 <= 16) return 64;
     // 128-wide tiles with two CTAs per SM and two UMMA issuers measured faster than 256-wide ones at every N
     // (686 vs 733 us at 28672 x 8192 x 4096); the 256-wide variant stays available through BGEMM_FORCE_NT.
     return 128;
@@ -591,7 +596,7 @@ int launch_gemm(cudaStream_t stream, GemmParams p, const int8_t* acts, long long
     if (skinny_supported(p, batch, !p.acts_general)) return launch_gemm_skinny(stream, p, acts, act_ld, batch);
     EncodeTiledFn encode = get_encode_fn();
     if (!encode) return BGEMM_ERR_DRIVER;
-    int NT = gemm_tile_n(p.N);
+    int NT = gemm_tile_n(p.M, p.N, p.K, batch);
     // One partial wave: with 128-wide tiles on more than one but at most two CTAs per SM, some SMs run two tiles side by
     // side while the others run one, and the launch lasts as long as the pairs (3584 x 8192 x 1024, the 8-GPU shard of the
     // 28672-row layer: 32.5 us); 256-wide tiles, one CTA per SM, finish sooner when they all fit at once (28.9 us).

@@ -59,7 +59,7 @@ int* device_status_word();        // per-device status word, lazily created (cud
 void apply_test_hooks(GemmParams& p);   // copies the process-wide test settings (normally: none) into the launch parameters
 
 int sm_count();                   // SMs of the current device (cached)
-int gemm_tile_n(long long N);
+int gemm_tile_n(long long M, long long N, long long K, long long batch);
 int max_resident_clusters(int NT, int split, bool deep);   // clusters of `split` CTAs of gemm_kernel the device holds at once; -1: unknown
 int launch_gemm(cudaStream_t stream, GemmParams p, const int8_t* acts, long long act_ld, long long batch);
 
