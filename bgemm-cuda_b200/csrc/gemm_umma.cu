@@ -574,11 +574,11 @@ int gemm_tile_n(long long M, long long N, long long K, long long batch) {
     if (N <= 16) return 16;
     if (N <= 32) return 32;
     if (N <= 64) return 64;
-    // 65-128 activation rows on few row tiles: two 64-column tiles with half as many K partitions each are faster than
-    // one 128-column tile (half the partial sums to exchange per CTA; 4096 x 4096 x 128: 9.35 against 9.87 us, 2048 x
-    // 4096 x 128: 7.9 against 9.2, 4096 x 1024 x 128: 6.9 against 8.3) as long as the K range per partition stays short
-    // (4096 x 8192 x 128: 12.5 against 11.7) and both fill the SMs once.
-    if (N <= 128 && batch == 1 && (M + 127) / 128 * 4 <= sm_count() && (K + 255) / 256 <= 16) return 64;
+    // 65-256 activation rows on few row tiles: 64-column tiles, all resident at once, with half as many K partitions each
+    // are faster than 128-column ones (half the partial sums to exchange per CTA, or none; 4096 x 4096 x 128: 9.35 against
+    // 9.87 us, 2048 x 4096 x 128: 7.9 against 9.2, 4096 x 1024 x 256: 6.75 against 8.5, 1024 x 4096 x 256: 7.8 against 9.2;
+    // level at 4096 x 4096 x 256) as long as the K range per partition stays short (4096 x 8192 x 128: 12.5 against 11.7).
+    if (N <= 256 && batch == 1 && (M + 127) / 128 * ((N + 63) / 64) <= sm_count() && (K + 255) / 256 <= 16) return 64;
     // 128-wide tiles with two CTAs per SM and two UMMA issuers measured faster than 256-wide ones at every N
     // (686 vs 733 us at 28672 x 8192 x 4096); the 256-wide variant stays available through BGEMM_FORCE_NT.
     return 128;
